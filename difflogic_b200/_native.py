@@ -1,0 +1,96 @@
+"""ctypes binding of the C ABI declared in include/difflogic_b200.h.
+
+The library is loaded from difflogic_b200/_lib/libdifflogic_b200.so (built in-tree by
+`python -m difflogic_b200.build`).  There is no CPU or eager stand-in for these kernels: if
+the library is missing, every CUDA code path of the package raises.
+"""
+import ctypes
+import os
+
+import torch
+
+from . import build as _build
+
+_i64 = ctypes.c_int64
+_ptr = ctypes.c_void_p
+_int = ctypes.c_int
+_f32 = ctypes.c_float
+
+DL_OK, DL_ERR_INVALID_ARG, DL_ERR_BAD_BIT_COUNT, DL_ERR_NOT_DIVISIBLE, DL_ERR_CUDA, DL_ERR_TOO_LARGE = range(6)
+W_LOGITS, W_PROBS, W_ARGMAX = 0, 1, 2
+
+# name -> (restype, argtypes); mirrors include/difflogic_b200.h one to one
+SIGNATURES = {
+    "dl_version": (_int, []),
+    "dl_last_error_string": (ctypes.c_char_p, []),
+    "dl_forward_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _ptr]),
+    "dl_coefs_f32": (_int, [_ptr, _int, _ptr, _i64, _ptr]),
+    "dl_backward_w_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _int, _ptr, _i64, _i64, _i64, _ptr]),
+    "dl_backward_x_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, _i64, _i64, _i64, _ptr]),
+    "dl_build_backward_plan": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr]),
+    "dl_eval_packed": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr]),
+    "dl_argmax_gate_u8": (_int, [_ptr, _ptr, _i64, _ptr]),
+    "dl_packbits": (_int, [_ptr, _ptr, _i64, _i64, _int, _ptr]),
+    "dl_packbits_batch_major": (_int, [_ptr, _ptr, _i64, _i64, _int, _ptr]),
+    "dl_groupbitsum": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
+    "dl_groupsum_workspace_bytes": (ctypes.c_size_t, [_i64, _i64, _i64]),
+    "dl_groupsum_f32": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),
+    "dl_groupsum_backward_f32": (_int, [_ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),
+}
+
+_lib = None
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+def library_path():
+    return _build.LIB_PATH
+
+
+def lib():
+    """The loaded library; raises NativeLibraryMissing when it has not been built."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise NativeLibraryMissing(
+                "difflogic_b200: %s not found. Build it with `python -m difflogic_b200.build` "
+                "(needs nvcc); there is no fallback implementation of the CUDA path." % path)
+        handle = ctypes.CDLL(path)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def last_error():
+    return lib().dl_last_error_string().decode("utf-8", "replace")
+
+
+def check(status):
+    """Maps a status code to the exception type the reference raises for the same mistake:
+    ValueError for a bad bit_count or a non-divisible group count, RuntimeError otherwise."""
+    if status == DL_OK:
+        return
+    msg = last_error()
+    if status in (DL_ERR_BAD_BIT_COUNT, DL_ERR_NOT_DIVISIBLE):
+        raise ValueError(msg)
+    raise RuntimeError("difflogic_b200 (status %d): %s" % (status, msg))
+
+
+def stream_of(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("difflogic_b200: expected a CUDA tensor, got one on %s" % t.device)

@@ -1,0 +1,64 @@
+// Version, error reporting and the two per-neuron helper kernels (coefficients, arg-max gate).
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+#include "gates.cuh"
+
+namespace dl {
+
+static thread_local char g_error[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int launch_status(const char *what) {
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) {
+        cudaGetLastError();  // clear the sticky launch error so that later calls are not blamed
+        return fail(DL_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    }
+    return DL_OK;
+}
+
+__global__ void __launch_bounds__(kThreads) coefs_kernel(const float *__restrict__ w, int w_mode,
+                                                         float4 *__restrict__ coef, int64_t n_out) {
+    const int64_t j = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (j < n_out) coef[j] = neuron_coef(w + j * 16, w_mode);
+}
+
+__global__ void __launch_bounds__(kThreads) argmax_kernel(const float *__restrict__ w, uint8_t *__restrict__ gate,
+                                                          int64_t n_out) {
+    const int64_t j = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (j < n_out) gate[j] = (uint8_t)first_argmax16(w + j * 16);
+}
+
+}  // namespace dl
+
+extern "C" DL_API int dl_version(void) { return 100; }
+
+extern "C" DL_API const char *dl_last_error_string(void) { return dl::g_error; }
+
+extern "C" DL_API int dl_coefs_f32(const float *w, int w_mode, float *coef, int64_t n_out, void *stream) {
+    DL_REQUIRE(w && coef, DL_ERR_INVALID_ARG, "dl_coefs_f32: null pointer");
+    DL_REQUIRE(n_out >= 0, DL_ERR_INVALID_ARG, "dl_coefs_f32: negative size");
+    DL_REQUIRE(w_mode >= DL_W_LOGITS && w_mode <= DL_W_ARGMAX, DL_ERR_INVALID_ARG, "dl_coefs_f32: unknown w_mode %d", w_mode);
+    DL_REQUIRE(dl::aligned_to(coef, 16), DL_ERR_INVALID_ARG, "dl_coefs_f32: coef must be 16-byte aligned");
+    if (n_out == 0) return DL_OK;
+    dl::coefs_kernel<<<(unsigned)dl::ceil_div(n_out, dl::kThreads), dl::kThreads, 0, dl::as_stream(stream)>>>(
+        w, w_mode, reinterpret_cast<float4 *>(coef), n_out);
+    return dl::launch_status("dl_coefs_f32");
+}
+
+extern "C" DL_API int dl_argmax_gate_u8(const float *w, uint8_t *gate, int64_t n_out, void *stream) {
+    DL_REQUIRE(w && gate, DL_ERR_INVALID_ARG, "dl_argmax_gate_u8: null pointer");
+    DL_REQUIRE(n_out >= 0, DL_ERR_INVALID_ARG, "dl_argmax_gate_u8: negative size");
+    if (n_out == 0) return DL_OK;
+    dl::argmax_kernel<<<(unsigned)dl::ceil_div(n_out, dl::kThreads), dl::kThreads, 0, dl::as_stream(stream)>>>(w, gate, n_out);
+    return dl::launch_status("dl_argmax_gate_u8");
+}

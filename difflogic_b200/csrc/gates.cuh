@@ -1,0 +1,88 @@
+// The 16 two-input gates: truth-table algebra shared by the training and the packed kernels.
+//
+// Gate id i encodes its truth table as  i = 8*f(0,0) + 4*f(0,1) + 2*f(1,0) + f(1,1)
+// (reference: difflogic/functional.py:7-24).  Every real-valued relaxation of the reference
+// (functional.py:31-62) is the multilinear extension of that table,
+//     f(A,B) = t00 + (t10-t00) A + (t01-t00) B + (t00-t01-t10+t11) A B,
+// so a probability mix over the gates collapses to four coefficients per neuron.
+#pragma once
+
+#include "common.cuh"
+
+namespace dl {
+
+// {c0, ca, cb, cab} of  sum_i p[i] * gate_i(A,B) = c0 + ca A + cb B + cab A B.
+__device__ __forceinline__ float4 coef_from_mix(const float (&p)[16]) {
+    float c0 = 0.f, ca = 0.f, cb = 0.f, cab = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int t00 = (i >> 3) & 1, t01 = (i >> 2) & 1, t10 = (i >> 1) & 1, t11 = i & 1;
+        c0 += p[i] * (float)t00;
+        ca += p[i] * (float)(t10 - t00);
+        cb += p[i] * (float)(t01 - t00);
+        cab += p[i] * (float)(t00 - t01 - t10 + t11);
+    }
+    return make_float4(c0, ca, cb, cab);
+}
+
+__device__ __forceinline__ int first_argmax16(const float *__restrict__ w) {
+    int best = 0;
+    float m = __ldg(w);
+#pragma unroll
+    for (int i = 1; i < 16; ++i) {
+        const float v = __ldg(w + i);
+        if (v > m) { m = v; best = i; }
+    }
+    return best;
+}
+
+// Coefficients of one neuron from its 16 weights, read as `w_mode` says.
+__device__ __forceinline__ float4 neuron_coef(const float *__restrict__ w, int w_mode) {
+    float p[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) p[i] = __ldg(w + i);
+    if (w_mode == DL_W_LOGITS) {
+        float m = p[0];
+#pragma unroll
+        for (int i = 1; i < 16; ++i) m = fmaxf(m, p[i]);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { p[i] = expf(p[i] - m); s += p[i]; }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) p[i] = p[i] / s;
+    } else if (w_mode == DL_W_ARGMAX) {
+        int best = 0;
+        float m = p[0];
+#pragma unroll
+        for (int i = 1; i < 16; ++i) if (p[i] > m) { m = p[i]; best = i; }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) p[i] = (i == best) ? 1.f : 0.f;
+    }
+    return coef_from_mix(p);
+}
+
+// dL/dp_i from the four batch sums S = {sum g, sum A g, sum B g, sum A B g}.
+__device__ __forceinline__ float gate_grad_from_sums(int i, float s0, float sa, float sb, float sab) {
+    const int t00 = (i >> 3) & 1, t01 = (i >> 2) & 1, t10 = (i >> 1) & 1, t11 = i & 1;
+    return (float)t00 * s0 + (float)(t10 - t00) * sa + (float)(t01 - t00) * sb + (float)(t00 - t01 - t10 + t11) * sab;
+}
+
+// Bitwise gate in algebraic normal form: y = m0 ^ (ma & A) ^ (mb & B) ^ (mab & A & B),
+// each mask all-ones or zero (reference gate list: difflogic_kernel.cu:437-472).
+struct GateMasks {
+    uint32_t m0, ma, mb, mab;
+};
+__device__ __forceinline__ GateMasks gate_masks(int op) {
+    const uint32_t t00 = (op >> 3) & 1, t01 = (op >> 2) & 1, t10 = (op >> 1) & 1, t11 = op & 1;
+    GateMasks g;
+    g.m0 = 0u - t00;
+    g.ma = 0u - (t00 ^ t10);
+    g.mb = 0u - (t00 ^ t01);
+    g.mab = 0u - (t00 ^ t01 ^ t10 ^ t11);
+    return g;
+}
+__device__ __forceinline__ uint32_t gate32(uint32_t a, uint32_t b, const GateMasks &g) {
+    return g.m0 ^ (g.ma & a) ^ (g.mb & b) ^ (g.mab & a & b);
+}
+
+}  // namespace dl

@@ -1,0 +1,167 @@
+// Float GroupSum on the feature-major activation of the last layer, forward and backward.
+//
+//   out[s][c]    = inv_tau * sum_{r < m} x[c*m + r][s]          m = n / k
+//   grad_x[i][s] = inv_tau * grad_out[s][i / m]
+//
+// Forward.  The rows of a class are split into `chunks` pieces; a CTA sums one piece for a
+// block of 128 batch columns (32 lanes x float4, 8 warps striding the rows, shared-memory
+// merge) and stores the partial sum in the caller's workspace.  The CTA that finishes a
+// (class, column block) last adds the pieces in a fixed order and writes the result, so the
+// sum does not depend on scheduling and no float atomics are used.
+#include "common.cuh"
+
+namespace dl {
+
+constexpr int kGsCols = 128;          // batch columns per CTA
+constexpr int kGsCounterBytes = 4096;  // counters at the head of the workspace
+constexpr int kGsMaxCounters = kGsCounterBytes / 4;
+
+static int64_t groupsum_chunks(int64_t n, int64_t batch, int64_t k) {
+    const int64_t m = n / k;
+    const int64_t colblocks = ceil_div(batch, kGsCols);
+    // aim at ~4 CTAs per SM over 148 SMs, at least 16 rows per piece
+    int64_t chunks = ceil_div(592, k * colblocks);
+    if (chunks > ceil_div(m, 16)) chunks = ceil_div(m, 16);
+    if (chunks < 1) chunks = 1;
+    return chunks;
+}
+
+__global__ void __launch_bounds__(kThreads)
+groupsum_kernel(const float *__restrict__ x, float *__restrict__ out, unsigned int *__restrict__ counters,
+                float *__restrict__ partial, int64_t batch, int k, int m, int chunks, float inv_tau) {
+    __shared__ float s_part[8][kGsCols];
+    __shared__ bool s_last;
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int colblock = blockIdx.x, c = blockIdx.y, q = blockIdx.z;
+    const int64_t col0 = (int64_t)colblock * kGsCols + lane * 4;
+    const int64_t rbeg = (int64_t)c * m + ((int64_t)m * q) / chunks;
+    const int64_t rend = (int64_t)c * m + ((int64_t)m * (q + 1)) / chunks;
+
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const bool vec = (batch % 4 == 0) && col0 + 3 < batch;
+    if (vec) {
+#pragma unroll 4
+        for (int64_t r = rbeg + warp; r < rend; r += 8) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(x + r * batch + col0));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    } else {
+        for (int64_t r = rbeg + warp; r < rend; r += 8) {
+            const float *p = x + r * batch + col0;
+            if (col0 + 0 < batch) acc.x += __ldg(p + 0);
+            if (col0 + 1 < batch) acc.y += __ldg(p + 1);
+            if (col0 + 2 < batch) acc.z += __ldg(p + 2);
+            if (col0 + 3 < batch) acc.w += __ldg(p + 3);
+        }
+    }
+    s_part[warp][lane * 4 + 0] = acc.x;
+    s_part[warp][lane * 4 + 1] = acc.y;
+    s_part[warp][lane * 4 + 2] = acc.z;
+    s_part[warp][lane * 4 + 3] = acc.w;
+    __syncthreads();
+
+    const int64_t gcol = (int64_t)colblock * kGsCols + tid;
+    float sum = 0.f;
+    if (tid < kGsCols) {
+#pragma unroll
+        for (int wv = 0; wv < 8; ++wv) sum += s_part[wv][tid];
+    }
+    if (chunks == 1) {
+        if (tid < kGsCols && gcol < batch) out[gcol * k + c] = sum * inv_tau;
+        return;
+    }
+    // partial[(c * chunks + q)][batch]
+    if (tid < kGsCols && gcol < batch) partial[((int64_t)c * chunks + q) * batch + gcol] = sum;
+    __threadfence();
+    __syncthreads();
+    unsigned int *counter = counters + ((int64_t)c * gridDim.x + colblock) % kGsMaxCounters;
+    if (tid == 0) {
+        const unsigned int done = atomicAdd(counter, 1u);
+        s_last = (done == (unsigned)chunks - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid < kGsCols && gcol < batch) {
+        float total = 0.f;
+        for (int qq = 0; qq < chunks; ++qq) total += __ldcg(partial + ((int64_t)c * chunks + qq) * batch + gcol);
+        out[gcol * k + c] = total * inv_tau;
+    }
+    if (tid == 0) *counter = 0u;  // ready for the next call
+}
+
+__global__ void __launch_bounds__(kThreads)
+groupsum_backward_kernel(const float *__restrict__ grad_out, float *__restrict__ grad_x, int64_t n, int64_t batch, int k,
+                         int m, float inv_tau) {
+    // a warp per row, lanes along the batch
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const bool vec = (batch % 4 == 0);
+    for (int64_t row = (int64_t)blockIdx.x * 8 + warp; row < n; row += (int64_t)gridDim.x * 8) {
+        const int c = (int)(row / m);
+        float *dst = grad_x + row * batch;
+        if (vec) {
+            for (int64_t col = lane * 4; col < batch; col += 128) {
+                float4 v;
+                v.x = __ldg(grad_out + (col + 0) * k + c) * inv_tau;
+                v.y = __ldg(grad_out + (col + 1) * k + c) * inv_tau;
+                v.z = __ldg(grad_out + (col + 2) * k + c) * inv_tau;
+                v.w = __ldg(grad_out + (col + 3) * k + c) * inv_tau;
+                *reinterpret_cast<float4 *>(dst + col) = v;
+            }
+        } else {
+            for (int64_t col = lane; col < batch; col += 32) dst[col] = __ldg(grad_out + col * k + c) * inv_tau;
+        }
+    }
+}
+
+}  // namespace dl
+
+using namespace dl;
+
+static int groupsum_check(const char *who, int64_t n, int64_t batch, int64_t k) {
+    DL_REQUIRE(n >= 0 && batch >= 0 && k > 0, DL_ERR_INVALID_ARG, "%s: bad size (n=%lld batch=%lld k=%lld)", who,
+               (long long)n, (long long)batch, (long long)k);
+    DL_REQUIRE(n % k == 0, DL_ERR_NOT_DIVISIBLE, "%s: n (%lld) has to be divisible by k (%lld)", who, (long long)n, (long long)k);
+    DL_REQUIRE(k <= 65535 && n / k <= INT32_MAX, DL_ERR_TOO_LARGE, "%s: k or rows per class too large", who);
+    return DL_OK;
+}
+
+extern "C" DL_API size_t dl_groupsum_workspace_bytes(int64_t n, int64_t batch, int64_t k) {
+    if (n <= 0 || batch <= 0 || k <= 0 || n % k != 0) return kGsCounterBytes;
+    const int64_t chunks = groupsum_chunks(n, batch, k);
+    return (size_t)kGsCounterBytes + (size_t)(k * chunks * batch) * sizeof(float);
+}
+
+extern "C" DL_API int dl_groupsum_f32(const float *x, float *out, void *workspace, int64_t n, int64_t batch, int64_t k, float inv_tau,
+                               void *stream) {
+    if (int s = groupsum_check("dl_groupsum_f32", n, batch, k)) return s;
+    if (batch == 0) return DL_OK;
+    DL_REQUIRE(out && workspace && (x || n == 0), DL_ERR_INVALID_ARG, "dl_groupsum_f32: null pointer");
+    DL_REQUIRE(aligned_to(workspace, 256), DL_ERR_INVALID_ARG, "dl_groupsum_f32: workspace must be 256-byte aligned");
+    DL_REQUIRE(batch % 4 != 0 || aligned_to(x, 16), DL_ERR_INVALID_ARG, "dl_groupsum_f32: x must be 16-byte aligned");
+    const int64_t chunks = groupsum_chunks(n, batch, k);
+    const int64_t colblocks = ceil_div(batch, kGsCols);
+    DL_REQUIRE(colblocks <= INT32_MAX && chunks <= 65535, DL_ERR_TOO_LARGE, "dl_groupsum_f32: batch too large");
+    DL_REQUIRE(chunks == 1 || k * colblocks <= kGsMaxCounters, DL_ERR_TOO_LARGE,
+               "dl_groupsum_f32: k * ceil(batch/128) = %lld exceeds %d", (long long)(k * colblocks), kGsMaxCounters);
+    unsigned int *counters = reinterpret_cast<unsigned int *>(workspace);
+    float *partial = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + kGsCounterBytes);
+    const dim3 grid((unsigned)colblocks, (unsigned)k, (unsigned)chunks);
+    groupsum_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(x, out, counters, partial, batch, (int)k, (int)(n / k),
+                                                              (int)chunks, inv_tau);
+    return launch_status("dl_groupsum_f32");
+}
+
+extern "C" DL_API int dl_groupsum_backward_f32(const float *grad_out, float *grad_x, int64_t n, int64_t batch, int64_t k,
+                                        float inv_tau, void *stream) {
+    if (int s = groupsum_check("dl_groupsum_backward_f32", n, batch, k)) return s;
+    if (batch == 0 || n == 0) return DL_OK;
+    DL_REQUIRE(grad_out && grad_x, DL_ERR_INVALID_ARG, "dl_groupsum_backward_f32: null pointer");
+    DL_REQUIRE(batch % 4 != 0 || aligned_to(grad_x, 16), DL_ERR_INVALID_ARG,
+               "dl_groupsum_backward_f32: grad_x must be 16-byte aligned");
+    int64_t blocks = ceil_div(n, 8);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    groupsum_backward_kernel<<<(unsigned)blocks, kThreads, 0, as_stream(stream)>>>(grad_out, grad_x, n, batch, (int)k,
+                                                                                  (int)(n / k), inv_tau);
+    return launch_status("dl_groupsum_backward_f32");
+}

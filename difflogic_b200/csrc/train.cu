@@ -1,0 +1,376 @@
+// Training kernels of the logic layer: forward, backward_w, backward_x (+ the backward plan).
+//
+// Activations are feature-major, x[n_in][batch] with the batch contiguous, so one neuron
+// reads two whole input rows and writes one output row.  A row is covered by a group of G
+// lanes (G a power of two <= 32, picked from the batch size) that each move 16 bytes
+// (float4) per access; a CTA of 256 threads holds 256/G such groups.  When the batch is not
+// a multiple of four floats, or a base pointer is not 16-byte aligned, the same kernels run
+// with scalar accesses.  Columns are split into slabs of G vectors that are walked by
+// blockIdx.y, so that all CTAs resident at one time work on the same few slabs and the
+// gathered input rows of a slab stay in L2 for their second reader.
+//
+// No tensor cores: the work is a gather plus a handful of FMAs per element.
+#include "common.cuh"
+#include "gates.cuh"
+
+namespace dl {
+
+template <bool VEC4>
+struct Vec;
+template <>
+struct Vec<true> {
+    using type = float4;
+    static constexpr int width = 4;
+};
+template <>
+struct Vec<false> {
+    using type = float;
+    static constexpr int width = 1;
+};
+
+__device__ __forceinline__ float4 ldv(const float4 *p) { return __ldg(p); }
+__device__ __forceinline__ float ldv(const float *p) { return __ldg(p); }
+
+__device__ __forceinline__ float4 mixv(const float4 c, const float4 a, const float4 b) {
+    float4 r;
+    r.x = fmaf(c.w, a.x * b.x, fmaf(c.y, a.x, fmaf(c.z, b.x, c.x)));
+    r.y = fmaf(c.w, a.y * b.y, fmaf(c.y, a.y, fmaf(c.z, b.y, c.x)));
+    r.z = fmaf(c.w, a.z * b.z, fmaf(c.y, a.z, fmaf(c.z, b.z, c.x)));
+    r.w = fmaf(c.w, a.w * b.w, fmaf(c.y, a.w, fmaf(c.z, b.w, c.x)));
+    return r;
+}
+__device__ __forceinline__ float mixv(const float4 c, const float a, const float b) {
+    return fmaf(c.w, a * b, fmaf(c.y, a, fmaf(c.z, b, c.x)));
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward:  y[j][:] = c0 + ca*x[a_j][:] + cb*x[b_j][:] + cab*x[a_j][:]*x[b_j][:]
+// The CTA first turns the 16 weights of each of its neurons into the four coefficients
+// (softmax / pass-through / arg-max one-hot), then streams the rows.
+// ---------------------------------------------------------------------------------------------
+template <int G, int U, bool VEC4>
+__global__ void __launch_bounds__(kThreads)
+forward_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
+               const float *__restrict__ w, int w_mode, float *__restrict__ y, float4 *__restrict__ coef_out,
+               int64_t n_out, int64_t batch, int64_t ncols, int64_t nslabs) {
+    using V = typename Vec<VEC4>::type;
+    constexpr int R = kThreads / G;  // neurons per pass
+    constexpr int NB = R * U;        // neurons per CTA
+    __shared__ float4 s_coef[NB];
+    __shared__ int64_t s_a[NB];
+    __shared__ int64_t s_b[NB];
+
+    const int tid = threadIdx.x;
+    const int64_t n0 = (int64_t)blockIdx.x * NB;
+    for (int t = tid; t < NB; t += kThreads) {
+        const int64_t j = n0 + t;
+        if (j < n_out) {
+            const float4 c = neuron_coef(w + j * 16, w_mode);
+            s_coef[t] = c;
+            s_a[t] = __ldg(a + j) * batch;
+            s_b[t] = __ldg(b + j) * batch;
+            if (coef_out != nullptr && blockIdx.y == 0) coef_out[j] = c;
+        }
+    }
+    __syncthreads();
+
+    const int lane = tid % G;
+    const int r0 = tid / G;
+    for (int64_t slab = blockIdx.y; slab < nslabs; slab += gridDim.y) {
+        const int64_t col = slab * G + lane;
+        if (col >= ncols) continue;
+        const int64_t off = col * Vec<VEC4>::width;
+        V va[U], vb[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int r = r0 + u * R;
+            if (n0 + r < n_out) {
+                va[u] = ldv(reinterpret_cast<const V *>(x + s_a[r] + off));
+                vb[u] = ldv(reinterpret_cast<const V *>(x + s_b[r] + off));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int r = r0 + u * R;
+            if (n0 + r < n_out)
+                *reinterpret_cast<V *>(y + (n0 + r) * batch + off) = mixv(s_coef[r], va[u], vb[u]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward_w: four batch sums per neuron, reduced over the G lanes of its group by shuffles,
+// expanded to the 16 gate gradients and (DL_W_LOGITS) pushed through the softmax in place.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void acc4(float &s0, float &sa, float &sb, float &sab, float4 va, float4 vb, float4 g) {
+    s0 += (g.x + g.y) + (g.z + g.w);
+    sa += (va.x * g.x + va.y * g.y) + (va.z * g.z + va.w * g.w);
+    sb += (vb.x * g.x + vb.y * g.y) + (vb.z * g.z + vb.w * g.w);
+    sab += (va.x * vb.x * g.x + va.y * vb.y * g.y) + (va.z * vb.z * g.z + va.w * vb.w * g.w);
+}
+__device__ __forceinline__ void acc4(float &s0, float &sa, float &sb, float &sab, float va, float vb, float g) {
+    s0 += g;
+    sa += va * g;
+    sb += vb * g;
+    sab += va * vb * g;
+}
+
+template <int G, bool VEC4>
+__global__ void __launch_bounds__(kThreads)
+backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
+                  const float *__restrict__ gy, const float *__restrict__ w, int w_mode, float *__restrict__ grad_w,
+                  int64_t n_out, int64_t batch, int64_t ncols) {
+    using V = typename Vec<VEC4>::type;
+    constexpr int R = kThreads / G;
+    const int tid = threadIdx.x;
+    const int lane = tid % G;
+    const int64_t j = (int64_t)blockIdx.x * R + tid / G;
+    const bool active = j < n_out;
+
+    float s0 = 0.f, sa = 0.f, sb = 0.f, sab = 0.f;
+    if (active) {
+        const V *xa = reinterpret_cast<const V *>(x + __ldg(a + j) * batch);
+        const V *xb = reinterpret_cast<const V *>(x + __ldg(b + j) * batch);
+        const V *g = reinterpret_cast<const V *>(gy + j * batch);
+#pragma unroll 4
+        for (int64_t col = lane; col < ncols; col += G) acc4(s0, sa, sb, sab, ldv(xa + col), ldv(xb + col), ldv(g + col));
+    }
+#pragma unroll
+    for (int off = G / 2; off > 0; off >>= 1) {
+        s0 += __shfl_xor_sync(0xffffffffu, s0, off);
+        sa += __shfl_xor_sync(0xffffffffu, sa, off);
+        sb += __shfl_xor_sync(0xffffffffu, sb, off);
+        sab += __shfl_xor_sync(0xffffffffu, sab, off);
+    }
+
+    // The 16 gates of the neuron are shared by P lanes, K gates each.
+    constexpr int P = G < 16 ? G : 16;
+    constexpr int K = 16 / P;
+    const int gl = lane & (P - 1);
+    float out[K];
+#pragma unroll
+    for (int q = 0; q < K; ++q) out[q] = gate_grad_from_sums(gl + q * P, s0, sa, sb, sab);
+
+    if (w_mode == DL_W_LOGITS) {
+        float wv[K];
+        float m = -INFINITY;
+#pragma unroll
+        for (int q = 0; q < K; ++q) {
+            wv[q] = active ? __ldg(w + j * 16 + gl + q * P) : 0.f;
+            m = fmaxf(m, wv[q]);
+        }
+#pragma unroll
+        for (int off = P / 2; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+        float s = 0.f;
+#pragma unroll
+        for (int q = 0; q < K; ++q) {
+            wv[q] = expf(wv[q] - m);
+            s += wv[q];
+        }
+#pragma unroll
+        for (int off = P / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        float dot = 0.f;
+#pragma unroll
+        for (int q = 0; q < K; ++q) {
+            wv[q] = wv[q] / s;
+            dot += wv[q] * out[q];
+        }
+#pragma unroll
+        for (int off = P / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+#pragma unroll
+        for (int q = 0; q < K; ++q) out[q] = wv[q] * (out[q] - dot);
+    }
+    if (active && lane < P) {
+#pragma unroll
+        for (int q = 0; q < K; ++q) grad_w[j * 16 + gl + q * P] = out[q];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward_x: each input row gathers from its consumers through the plan (no atomics).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void bx_acc(float4 &acc, float c1, float cab, float4 p, float4 g) {
+    acc.x = fmaf(fmaf(cab, p.x, c1), g.x, acc.x);
+    acc.y = fmaf(fmaf(cab, p.y, c1), g.y, acc.y);
+    acc.z = fmaf(fmaf(cab, p.z, c1), g.z, acc.z);
+    acc.w = fmaf(fmaf(cab, p.w, c1), g.w, acc.w);
+}
+__device__ __forceinline__ void bx_acc(float &acc, float c1, float cab, float p, float g) {
+    acc = fmaf(fmaf(cab, p, c1), g, acc);
+}
+__device__ __forceinline__ float4 scaled(float4 v, float s) { return make_float4(v.x * s, v.y * s, v.z * s, v.w * s); }
+__device__ __forceinline__ float scaled(float v, float s) { return v * s; }
+__device__ __forceinline__ void zero(float4 &v) { v = make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ void zero(float &v) { v = 0.f; }
+
+template <int G, bool VEC4>
+__global__ void __launch_bounds__(kThreads)
+backward_x_kernel(const float *__restrict__ x, const float4 *__restrict__ coef, const float *__restrict__ gy,
+                  const int64_t *__restrict__ start, const int2 *__restrict__ plan, float scale,
+                  float *__restrict__ gx, int64_t n_in, int64_t batch, int64_t ncols, int64_t nslabs) {
+    using V = typename Vec<VEC4>::type;
+    constexpr int R = kThreads / G;
+    const int tid = threadIdx.x;
+    const int lane = tid % G;
+    const int64_t i = (int64_t)blockIdx.x * R + tid / G;
+    if (i >= n_in) return;
+    const int64_t e0 = __ldg(start + i), e1 = __ldg(start + i + 1);
+    for (int64_t slab = blockIdx.y; slab < nslabs; slab += gridDim.y) {
+        const int64_t col = slab * G + lane;
+        if (col >= ncols) continue;
+        const int64_t off = col * Vec<VEC4>::width;
+        V acc;
+        zero(acc);
+#pragma unroll 2
+        for (int64_t e = e0; e < e1; ++e) {
+            const int2 p = __ldg(plan + e);
+            const int64_t j = p.x >> 1;
+            const float4 c = __ldg(coef + j);
+            const V vp = ldv(reinterpret_cast<const V *>(x + (int64_t)p.y * batch + off));
+            const V vg = ldv(reinterpret_cast<const V *>(gy + j * batch + off));
+            bx_acc(acc, (p.x & 1) ? c.z : c.y, c.w, vp, vg);
+        }
+        *reinterpret_cast<V *>(gx + i * batch + off) = scaled(acc, scale);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+build_plan_kernel(const int64_t *__restrict__ a, const int64_t *__restrict__ b, const int64_t *__restrict__ start,
+                  const int64_t *__restrict__ list, int2 *__restrict__ plan, int64_t n_in) {
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n_in) return;
+    const int64_t e0 = start[i], e1 = start[i + 1];
+    for (int64_t e = e0; e < e1; ++e) {
+        const int64_t j = list[e];
+        // A neuron whose inputs are both row i is listed twice in a row: first entry is its
+        // a-slot, second its b-slot.
+        const bool second = e > e0 && list[e - 1] == j;
+        const int slot = second ? 1 : (a[j] == i ? 0 : 1);
+        const int64_t partner = slot ? a[j] : b[j];
+        plan[e] = make_int2((int)(2 * j + slot), (int)partner);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+static inline unsigned slab_grid(int64_t nslabs) { return (unsigned)(nslabs < 65535 ? nslabs : 65535); }
+
+template <bool VEC4>
+static int launch_forward(int G, const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode, float *y,
+                          float *coef, int64_t n_out, int64_t batch, int64_t ncols, cudaStream_t st) {
+    constexpr int U = 4;
+    const int64_t nslabs = ceil_div(ncols, G);
+    const int64_t nb = (kThreads / G) * U;
+    const dim3 grid((unsigned)ceil_div(n_out, nb), slab_grid(nslabs));
+    float4 *c4 = reinterpret_cast<float4 *>(coef);
+#define DL_FWD(GG)                                                                                              \
+    case GG:                                                                                                    \
+        forward_kernel<GG, U, VEC4><<<grid, kThreads, 0, st>>>(x, a, b, w, w_mode, y, c4, n_out, batch, ncols, nslabs); \
+        break;
+    switch (G) {
+        DL_FWD(1) DL_FWD(2) DL_FWD(4) DL_FWD(8) DL_FWD(16) DL_FWD(32)
+    }
+#undef DL_FWD
+    return launch_status("dl_forward_f32");
+}
+
+template <bool VEC4>
+static int launch_backward_w(int G, const float *x, const int64_t *a, const int64_t *b, const float *gy, const float *w,
+                             int w_mode, float *grad_w, int64_t n_out, int64_t batch, int64_t ncols, cudaStream_t st) {
+    const unsigned grid = (unsigned)ceil_div(n_out, kThreads / G);
+#define DL_BW(GG)                                                                                          \
+    case GG:                                                                                               \
+        backward_w_kernel<GG, VEC4><<<grid, kThreads, 0, st>>>(x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols); \
+        break;
+    switch (G) {
+        DL_BW(1) DL_BW(2) DL_BW(4) DL_BW(8) DL_BW(16) DL_BW(32)
+    }
+#undef DL_BW
+    return launch_status("dl_backward_w_f32");
+}
+
+template <bool VEC4>
+static int launch_backward_x(int G, const float *x, const float *coef, const float *gy, const int64_t *start,
+                             const int32_t *plan, float scale, float *gx, int64_t n_in, int64_t batch, int64_t ncols,
+                             cudaStream_t st) {
+    const int64_t nslabs = ceil_div(ncols, G);
+    const dim3 grid((unsigned)ceil_div(n_in, kThreads / G), slab_grid(nslabs));
+    const float4 *c4 = reinterpret_cast<const float4 *>(coef);
+    const int2 *p2 = reinterpret_cast<const int2 *>(plan);
+#define DL_BX(GG)                                                                                               \
+    case GG:                                                                                                    \
+        backward_x_kernel<GG, VEC4><<<grid, kThreads, 0, st>>>(x, c4, gy, start, p2, scale, gx, n_in, batch, ncols, nslabs); \
+        break;
+    switch (G) {
+        DL_BX(1) DL_BX(2) DL_BX(4) DL_BX(8) DL_BX(16) DL_BX(32)
+    }
+#undef DL_BX
+    return launch_status("dl_backward_x_f32");
+}
+
+}  // namespace dl
+
+using namespace dl;
+
+static const int64_t kMaxRows = (int64_t)1 << 30;  // plan entries hold 2*j+slot in an int32
+
+extern "C" DL_API int dl_forward_f32(const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode, float *y,
+                              float *coef, int64_t n_in, int64_t n_out, int64_t batch, void *stream) {
+    DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_forward_f32: negative size");
+    DL_REQUIRE(w_mode >= DL_W_LOGITS && w_mode <= DL_W_ARGMAX, DL_ERR_INVALID_ARG, "dl_forward_f32: unknown w_mode %d", w_mode);
+    if (n_out == 0 || batch == 0) return DL_OK;
+    DL_REQUIRE(x && a && b && w && y, DL_ERR_INVALID_ARG, "dl_forward_f32: null pointer");
+    DL_REQUIRE(n_in > 0, DL_ERR_INVALID_ARG, "dl_forward_f32: n_in is 0 but n_out is %lld", (long long)n_out);
+    DL_REQUIRE(coef == nullptr || aligned_to(coef, 16), DL_ERR_INVALID_ARG, "dl_forward_f32: coef must be 16-byte aligned");
+    const bool vec = batch % 4 == 0 && aligned_to(x, 16) && aligned_to(y, 16);
+    const int64_t ncols = vec ? batch / 4 : batch;
+    const int G = pow2_at_least(ncols, 32);
+    return vec ? launch_forward<true>(G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream))
+               : launch_forward<false>(G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream));
+}
+
+extern "C" DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
+                                 int w_mode, float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, void *stream) {
+    DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_backward_w_f32: negative size");
+    DL_REQUIRE(w_mode == DL_W_LOGITS || w_mode == DL_W_PROBS, DL_ERR_INVALID_ARG,
+               "dl_backward_w_f32: w_mode must be DL_W_LOGITS or DL_W_PROBS, got %d", w_mode);
+    if (n_out == 0) return DL_OK;
+    DL_REQUIRE(a && b && grad_w, DL_ERR_INVALID_ARG, "dl_backward_w_f32: null pointer");
+    DL_REQUIRE(batch == 0 || (x && grad_y), DL_ERR_INVALID_ARG, "dl_backward_w_f32: null pointer");
+    DL_REQUIRE(w_mode != DL_W_LOGITS || w, DL_ERR_INVALID_ARG, "dl_backward_w_f32: DL_W_LOGITS needs the raw weights");
+    const bool vec = batch % 4 == 0 && aligned_to(x, 16) && aligned_to(grad_y, 16);
+    const int64_t ncols = vec ? batch / 4 : batch;
+    const int G = pow2_at_least(ceil_div(ncols, 4), 32);
+    return vec ? launch_backward_w<true>(G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, as_stream(stream))
+               : launch_backward_w<false>(G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, as_stream(stream));
+}
+
+extern "C" DL_API int dl_backward_x_f32(const float *x, const float *coef, const float *grad_y, const int64_t *start,
+                                 const int32_t *plan, float grad_scale, float *grad_x, int64_t n_in, int64_t n_out,
+                                 int64_t batch, void *stream) {
+    DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_backward_x_f32: negative size");
+    DL_REQUIRE(n_out < kMaxRows && n_in < 2 * kMaxRows, DL_ERR_TOO_LARGE, "dl_backward_x_f32: more than 2^30 neurons");
+    if (n_in == 0 || batch == 0) return DL_OK;
+    DL_REQUIRE(x && grad_x && start, DL_ERR_INVALID_ARG, "dl_backward_x_f32: null pointer");
+    DL_REQUIRE(n_out == 0 || (coef && grad_y && plan), DL_ERR_INVALID_ARG, "dl_backward_x_f32: null pointer");
+    DL_REQUIRE(aligned_to(coef, 16) && aligned_to(plan, 8), DL_ERR_INVALID_ARG,
+               "dl_backward_x_f32: coef must be 16-byte and plan 8-byte aligned");
+    const bool vec = batch % 4 == 0 && aligned_to(x, 16) && aligned_to(grad_y, 16) && aligned_to(grad_x, 16);
+    const int64_t ncols = vec ? batch / 4 : batch;
+    const int G = pow2_at_least(ncols, 32);
+    return vec ? launch_backward_x<true>(G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, as_stream(stream))
+               : launch_backward_x<false>(G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, as_stream(stream));
+}
+
+extern "C" DL_API int dl_build_backward_plan(const int64_t *a, const int64_t *b, const int64_t *start, const int64_t *list,
+                                      int32_t *plan, int64_t n_in, int64_t n_out, void *stream) {
+    DL_REQUIRE(n_in >= 0 && n_out >= 0, DL_ERR_INVALID_ARG, "dl_build_backward_plan: negative size");
+    DL_REQUIRE(n_out < kMaxRows && n_in < 2 * kMaxRows, DL_ERR_TOO_LARGE, "dl_build_backward_plan: more than 2^30 neurons");
+    if (n_in == 0 || n_out == 0) return DL_OK;
+    DL_REQUIRE(a && b && start && list && plan, DL_ERR_INVALID_ARG, "dl_build_backward_plan: null pointer");
+    DL_REQUIRE(aligned_to(plan, 8), DL_ERR_INVALID_ARG, "dl_build_backward_plan: plan must be 8-byte aligned");
+    build_plan_kernel<<<(unsigned)ceil_div(n_in, kThreads), kThreads, 0, as_stream(stream)>>>(
+        a, b, start, list, reinterpret_cast<int2 *>(plan), n_in);
+    return launch_status("dl_build_backward_plan");
+}

@@ -1,0 +1,271 @@
+"""Tensor-level operators over the C ABI (include/difflogic_b200.h).
+
+Each function checks its tensors, lets torch allocate the output on the inputs' device and
+launches the kernel on torch's current stream.  Nothing here computes on the CPU; a missing
+library raises (see _native.lib()).
+
+Layouts: float activations are feature-major `[features, batch]` contiguous; packed
+activations are `[features, words]`; indices are int64, as LogicLayer stores them.
+"""
+import torch
+
+from . import _native as N
+from ._native import W_ARGMAX, W_LOGITS, W_PROBS  # noqa: F401  (re-exported)
+
+_BITS_TO_DTYPE = {8: torch.int8, 16: torch.int16, 32: torch.int32, 64: torch.int64}
+_DTYPE_TO_BITS = {v: k for k, v in _BITS_TO_DTYPE.items()}
+_DTYPE_TO_BITS[torch.uint8] = 8
+
+
+def _need(cond, msg):
+    if not cond:
+        raise RuntimeError("difflogic_b200: " + msg)
+
+
+def _f32_matrix(t, name):
+    N.require_cuda(t)
+    _need(t.dtype == torch.float32, "%s must be float32, got %s (the CUDA path computes in fp32)" % (name, t.dtype))
+    _need(t.dim() == 2 and t.is_contiguous(), "%s must be a contiguous 2-D tensor" % name)
+
+
+def _index(t, name, n=None):
+    N.require_cuda(t)
+    _need(t.dtype == torch.int64 and t.dim() == 1 and t.is_contiguous(), "%s must be a contiguous int64 vector" % name)
+    if n is not None:
+        _need(t.numel() == n, "%s has %d entries, expected %d" % (name, t.numel(), n))
+
+
+# ------------------------------------------------------------------------------------------------
+# training
+# ------------------------------------------------------------------------------------------------
+
+def logic_forward(x, a, b, w, w_mode=W_LOGITS, want_coef=False):
+    """y[j,:] = sum_i p[j,i] gate_i(x[a_j,:], x[b_j,:]);  returns (y [n_out,batch], coef or None)."""
+    _f32_matrix(x, "x")
+    _f32_matrix(w, "w")
+    n_in, batch = x.shape
+    n_out = w.shape[0]
+    _need(w.shape[1] == 16, "w must be [n_out, 16]")
+    _index(a, "a", n_out)
+    _index(b, "b", n_out)
+    y = torch.empty((n_out, batch), dtype=torch.float32, device=x.device)
+    coef = torch.empty((n_out, 4), dtype=torch.float32, device=x.device) if want_coef else None
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_forward_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), w.data_ptr(), w_mode, y.data_ptr(),
+                                       N.ptr(coef), n_in, n_out, batch, N.stream_of(x)))
+    return y, coef
+
+
+def logic_coefs(w, w_mode=W_LOGITS):
+    _f32_matrix(w, "w")
+    _need(w.shape[1] == 16, "w must be [n_out, 16]")
+    coef = torch.empty((w.shape[0], 4), dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        N.check(N.lib().dl_coefs_f32(w.data_ptr(), w_mode, coef.data_ptr(), w.shape[0], N.stream_of(w)))
+    return coef
+
+
+def logic_backward_w(x, a, b, grad_y, w=None, w_mode=W_PROBS, out=None):
+    """[n_out,16] gradient: w_mode=W_PROBS w.r.t. the mixing weights, W_LOGITS w.r.t. the raw
+    parameters `w` (softmax backward applied in the kernel)."""
+    _f32_matrix(x, "x")
+    _f32_matrix(grad_y, "grad_y")
+    n_in, batch = x.shape
+    n_out = grad_y.shape[0]
+    _need(grad_y.shape[1] == batch, "grad_y and x disagree on the batch size")
+    _index(a, "a", n_out)
+    _index(b, "b", n_out)
+    if w_mode == W_LOGITS:
+        _need(w is not None, "W_LOGITS needs the raw weights")
+        _f32_matrix(w, "w")
+        _need(tuple(w.shape) == (n_out, 16), "w must be [n_out, 16]")
+    if out is None:
+        out = torch.empty((n_out, 16), dtype=torch.float32, device=x.device)
+    else:
+        _f32_matrix(out, "out")
+        _need(tuple(out.shape) == (n_out, 16), "out must be [n_out, 16]")
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_backward_w_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), grad_y.data_ptr(), N.ptr(w), w_mode,
+                                          out.data_ptr(), n_in, n_out, batch, N.stream_of(x)))
+    return out
+
+
+def inverse_index(a, b, n_in):
+    """The reference's inverse connection index (difflogic/difflogic.py:56-69) built with device
+    ops: for every input row the consumer neurons in increasing order, a neuron whose two inputs
+    are the same row listed twice.  Returns (start [n_in+1] int64, list [2*n_out] int64)."""
+    keys = torch.stack([a, b], dim=1).reshape(-1)           # position 2*j + slot
+    order = torch.argsort(keys, stable=True)
+    counts = torch.bincount(keys, minlength=n_in)
+    start = torch.zeros(n_in + 1, dtype=torch.int64, device=a.device)
+    start[1:] = torch.cumsum(counts, 0)
+    return start, (order // 2).contiguous()
+
+
+def build_backward_plan(a, b, start, lst):
+    n_out = a.numel()
+    n_in = start.numel() - 1
+    _index(a, "a")
+    _index(b, "b", n_out)
+    _index(start, "start")
+    _index(lst, "list", 2 * n_out)
+    plan = torch.empty((2 * n_out, 2), dtype=torch.int32, device=a.device)
+    with torch.cuda.device(a.device):
+        N.check(N.lib().dl_build_backward_plan(a.data_ptr(), b.data_ptr(), start.data_ptr(), lst.data_ptr(),
+                                               plan.data_ptr(), n_in, n_out, N.stream_of(a)))
+    return plan
+
+
+def logic_backward_x(x, coef, grad_y, start, plan, grad_scale=1.0):
+    _f32_matrix(x, "x")
+    _f32_matrix(grad_y, "grad_y")
+    _f32_matrix(coef, "coef")
+    n_in, batch = x.shape
+    n_out = grad_y.shape[0]
+    _need(grad_y.shape[1] == batch, "grad_y and x disagree on the batch size")
+    _need(tuple(coef.shape) == (n_out, 4), "coef must be [n_out, 4]")
+    _index(start, "start", n_in + 1)
+    N.require_cuda(plan)
+    _need(plan.dtype == torch.int32 and plan.is_contiguous() and tuple(plan.shape) == (2 * n_out, 2),
+          "plan must be a contiguous int32 [2*n_out, 2] tensor")
+    gx = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_backward_x_f32(x.data_ptr(), coef.data_ptr(), grad_y.data_ptr(), start.data_ptr(),
+                                          plan.data_ptr(), float(grad_scale), gx.data_ptr(), n_in, n_out, batch,
+                                          N.stream_of(x)))
+    return gx
+
+
+# ------------------------------------------------------------------------------------------------
+# packed-bit inference
+# ------------------------------------------------------------------------------------------------
+
+def bits_of(t):
+    _need(t.dtype in _DTYPE_TO_BITS, "packed tensor must be int8/int16/int32/int64, got %s" % t.dtype)
+    return _DTYPE_TO_BITS[t.dtype]
+
+
+def argmax_gates(w):
+    _f32_matrix(w, "w")
+    _need(w.shape[1] == 16, "w must be [n_out, 16]")
+    g = torch.empty((w.shape[0],), dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        N.check(N.lib().dl_argmax_gate_u8(w.data_ptr(), g.data_ptr(), w.shape[0], N.stream_of(w)))
+    return g
+
+
+def eval_packed(x, a, b, gate, out=None):
+    N.require_cuda(x, gate)
+    _need(x.dim() == 2 and x.is_contiguous(), "x must be a contiguous 2-D tensor")
+    bits = bits_of(x)
+    n_in, words = x.shape
+    n_out = gate.numel()
+    _need(gate.dtype == torch.uint8 and gate.is_contiguous(), "gate must be a contiguous uint8 vector")
+    _index(a, "a", n_out)
+    _index(b, "b", n_out)
+    if out is None:
+        out = torch.empty((n_out, words), dtype=x.dtype, device=x.device)
+    else:
+        _need(out.dtype == x.dtype and tuple(out.shape) == (n_out, words) and out.is_contiguous() and out.is_cuda,
+              "out must be a contiguous [n_out, words] tensor of x's dtype")
+        _need(out.data_ptr() != x.data_ptr(), "eval_packed cannot run in place")
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_eval_packed(x.data_ptr(), a.data_ptr(), b.data_ptr(), gate.data_ptr(), out.data_ptr(),
+                                       n_in, n_out, words, bits, N.stream_of(x)))
+    return out
+
+
+def _as_bool_bytes(t):
+    N.require_cuda(t)
+    _need(t.dim() == 2 and t.is_contiguous(), "t must be a contiguous 2-D tensor")
+    _need(t.dtype in (torch.bool, torch.uint8), "t must be a bool tensor, got %s" % t.dtype)
+    return t
+
+
+def _check_bit_count(bit_count):
+    if bit_count not in _BITS_TO_DTYPE:
+        raise ValueError("`bit_count` has to be in { 8, 16, 32, 64 }")
+
+
+def packbits(t, bit_count):
+    """bool [n, batch] (feature-major) -> (words [n, ceil(batch/bit_count)], pad_len)."""
+    _check_bit_count(bit_count)
+    t = _as_bool_bytes(t)
+    n, batch = t.shape
+    words = -(-batch // bit_count)
+    out = torch.empty((n, words), dtype=_BITS_TO_DTYPE[bit_count], device=t.device)
+    with torch.cuda.device(t.device):
+        N.check(N.lib().dl_packbits(t.data_ptr(), out.data_ptr(), n, batch, bit_count, N.stream_of(t)))
+    return out, (bit_count - batch % bit_count) % bit_count
+
+
+def packbits_batch_major(t, bit_count):
+    """bool [batch, n] (as the user holds it) -> (words [n, ceil(batch/bit_count)], pad_len)."""
+    _check_bit_count(bit_count)
+    t = _as_bool_bytes(t)
+    batch, n = t.shape
+    words = -(-batch // bit_count)
+    out = torch.empty((n, words), dtype=_BITS_TO_DTYPE[bit_count], device=t.device)
+    with torch.cuda.device(t.device):
+        N.check(N.lib().dl_packbits_batch_major(t.data_ptr(), out.data_ptr(), n, batch, bit_count, N.stream_of(t)))
+    return out, (bit_count - batch % bit_count) % bit_count
+
+
+def groupbitsum(x, pad_len, k):
+    """words [n, W] -> int32 [W*bits - pad_len, k] class counts."""
+    N.require_cuda(x)
+    _need(x.dim() == 2 and x.is_contiguous(), "x must be a contiguous 2-D tensor")
+    bits = bits_of(x)
+    n, words = x.shape
+    k = int(k)
+    if k <= 0 or n % k != 0:
+        raise ValueError("in_dim (%d) has to be divisible by k (%d) but it is not" % (n, k))
+    batch = words * bits - int(pad_len)
+    _need(batch >= 0, "pad_len exceeds the packed batch")
+    out = torch.empty((batch, k), dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_groupbitsum(x.data_ptr(), out.data_ptr(), n, words, int(pad_len), k, bits, N.stream_of(x)))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# float GroupSum
+# ------------------------------------------------------------------------------------------------
+
+_workspaces = {}
+
+
+def _groupsum_workspace(device, stream, nbytes):
+    """Zero-initialised scratch for dl_groupsum_f32, one per (device, stream), grown on demand.
+    The kernel leaves the counters at zero, so the buffer is cleared only when it is created."""
+    key = (device, stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def groupsum(x, k, tau):
+    """feature-major x [n, batch] -> [batch, k] = per-class row sums / tau."""
+    _f32_matrix(x, "x")
+    n, batch = x.shape
+    k = int(k)
+    _need(k > 0 and n % k == 0, "n (%d) must be divisible by k (%d)" % (n, k))
+    out = torch.empty((batch, k), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        stream = N.stream_of(x)
+        ws = _groupsum_workspace(x.device, stream, N.lib().dl_groupsum_workspace_bytes(n, batch, k))
+        N.check(N.lib().dl_groupsum_f32(x.data_ptr(), out.data_ptr(), ws.data_ptr(), n, batch, k, 1.0 / float(tau), stream))
+    return out
+
+
+def groupsum_backward(grad_out, n, tau):
+    """[batch, k] -> feature-major [n, batch] with grad_x[i,:] = grad_out[:, i // (n/k)] / tau."""
+    _f32_matrix(grad_out, "grad_out")
+    batch, k = grad_out.shape
+    gx = torch.empty((n, batch), dtype=torch.float32, device=grad_out.device)
+    with torch.cuda.device(grad_out.device):
+        N.check(N.lib().dl_groupsum_backward_f32(grad_out.data_ptr(), gx.data_ptr(), n, batch, k, 1.0 / float(tau),
+                                                 N.stream_of(grad_out)))
+    return gx

@@ -1,0 +1,171 @@
+/*
+ * difflogic_b200 -- C ABI of the logic-layer hot path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers and sizes, launches asynchronously on the
+ * stream it is given (a cudaStream_t passed as void*; NULL is the legacy default stream),
+ * never allocates or frees device memory, never synchronises the device and never exits the
+ * process.  The return value is a status code (DL_OK == 0).  After a non-zero status,
+ * dl_last_error_string() gives a message for the calling thread.
+ *
+ * Layouts.  Float activations are feature-major: x[n_in][batch], y[n_out][batch], batch is
+ * the fastest dimension.  Packed activations are feature-major rows of words along the batch:
+ * t[n][words], word = bit_count bits (8, 16, 32 or 64), sample s is bit (s % bit_count) of
+ * word (s / bit_count), least-significant bit first.  Connection indices a[], b[] are int64,
+ * as the Python API stores them.
+ *
+ * Each declaration names the interface of the reference implementation
+ * (Felix-Petersen/difflogic) that it replaces, as file:line within that project.
+ */
+#ifndef DIFFLOGIC_B200_H
+#define DIFFLOGIC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define DL_API __attribute__((visibility("default")))
+#else
+#define DL_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+enum {
+    DL_OK = 0,
+    DL_ERR_INVALID_ARG = 1,   /* null pointer, negative size, unknown mode  -> RuntimeError   */
+    DL_ERR_BAD_BIT_COUNT = 2, /* bit_count not in {8,16,32,64}              -> ValueError     */
+    DL_ERR_NOT_DIVISIBLE = 3, /* rows not divisible by the number of groups -> ValueError     */
+    DL_ERR_CUDA = 4,          /* a CUDA runtime call or launch failed       -> RuntimeError   */
+    DL_ERR_TOO_LARGE = 5      /* size beyond a documented limit             -> RuntimeError   */
+};
+
+/* How the [n_out][16] weight matrix handed to a training kernel is to be read. */
+enum {
+    DL_W_LOGITS = 0, /* raw parameters; the kernel applies softmax over the 16 gates          */
+    DL_W_PROBS = 1,  /* mixing weights used as they are (already soft-maxed by the caller)    */
+    DL_W_ARGMAX = 2  /* raw parameters; only the arg-max gate is used (first max on ties)     */
+};
+
+DL_API int dl_version(void);
+DL_API const char *dl_last_error_string(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Training forward.
+ * Replaces logic_layer_cuda_forward, difflogic/cuda/difflogic_kernel.cu:259-297 (kernel
+ * :90-135), bound as difflogic_cuda.forward at difflogic/cuda/difflogic.cpp:46-51, together
+ * with the softmax / one_hot(argmax) that LogicLayer.forward_cuda applies before it
+ * (difflogic/difflogic.py:123,128).
+ *
+ *   y[j][s] = sum_i  p[j][i] * gate_i(x[a[j]][s], x[b[j]][s])
+ *
+ * coef (optional, may be NULL) receives per neuron the four numbers {c0, ca, cb, cab} with
+ * y = c0 + ca*A + cb*B + cab*A*B; dl_backward_x_f32 consumes it.
+ * ---------------------------------------------------------------------------------------- */
+DL_API int dl_forward_f32(const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode,
+                   float *y, float *coef, int64_t n_in, int64_t n_out, int64_t batch, void *stream);
+
+/* The coefficient table alone (w [n_out][16] -> coef [n_out][4]); used when a caller hands
+ * dl_backward_x_f32 weights that did not pass through dl_forward_f32.  No counterpart in the
+ * reference, which re-reads 12 of the 16 weights per consumer (difflogic_kernel.cu:215-251). */
+DL_API int dl_coefs_f32(const float *w, int w_mode, float *coef, int64_t n_out, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * backward_w.
+ * Replaces logic_layer_cuda_backward_w, difflogic_kernel.cu:300-364 (kernel :138-178 and the
+ * ATen epilogue :337-360), bound as difflogic_cuda.backward_w at difflogic.cpp:52-56.
+ *
+ * w_mode == DL_W_PROBS : grad_w[j][i] = dL/dp[j][i] (the reference's result; w may be NULL).
+ * w_mode == DL_W_LOGITS: w holds the raw parameters and grad_w receives dL/dw, i.e. the
+ *                        softmax backward of difflogic.py:123 is applied in the same kernel.
+ * grad_w is [n_out][16], fully written (column 0 of the DL_W_PROBS result is exactly zero).
+ * ---------------------------------------------------------------------------------------- */
+DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y,
+                      const float *w, int w_mode, float *grad_w,
+                      int64_t n_in, int64_t n_out, int64_t batch, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * backward_x.
+ * Replaces logic_layer_cuda_backward_x, difflogic_kernel.cu:367-410 (kernel :181-256), bound
+ * as difflogic_cuda.backward_x at difflogic.cpp:57-62, and folds in GradFactor's scaling
+ * (difflogic/functional.py:130-138) through grad_scale.
+ *
+ *   grad_x[i][s] = grad_scale * sum over consumers j of input i of
+ *                    (d y_j / d input)(partner value) * grad_y[j][s]
+ *
+ * plan is the inverse connection index in the form produced by dl_build_backward_plan:
+ * 2*n_out entries of two int32 {2*j + slot, partner row}, grouped by input row; start
+ * [n_in+1] (int64) are the group offsets (LogicLayer.given_x_indices_of_y_start,
+ * difflogic/difflogic.py:66-67).  A neuron whose two inputs are the same row contributes
+ * d/da + d/db (the reference kernel adds 2*d/da there; its python path gives d/da + d/db).
+ * ---------------------------------------------------------------------------------------- */
+DL_API int dl_backward_x_f32(const float *x, const float *coef, const float *grad_y, const int64_t *start,
+                      const int32_t *plan, float grad_scale, float *grad_x,
+                      int64_t n_in, int64_t n_out, int64_t batch, void *stream);
+
+/* Builds `plan` [2*n_out][2] int32 from the reference's inverse index: start [n_in+1] and
+ * list [2*n_out] (LogicLayer.given_x_indices_of_y_start / given_x_indices_of_y,
+ * difflogic/difflogic.py:56-69).  One-time set-up per layer. */
+DL_API int dl_build_backward_plan(const int64_t *a, const int64_t *b, const int64_t *start, const int64_t *list,
+                           int32_t *plan, int64_t n_in, int64_t n_out, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Packed-bit eval.
+ * Replaces logic_layer_cuda_eval, difflogic_kernel.cu:503-541 (kernel :474-501, gates
+ * :437-472), bound as difflogic_cuda.eval at difflogic.cpp:63-68.
+ *   y[j][c] = gate_{gate[j]}(x[a[j]][c], x[b[j]][c])   bitwise, c over the words of a row.
+ * Every word of y is written (no memset needed).  gate is uint8 [n_out].
+ * ---------------------------------------------------------------------------------------- */
+DL_API int dl_eval_packed(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y,
+                   int64_t n_in, int64_t n_out, int64_t words, int bit_count, void *stream);
+
+/* argmax over the 16 gate weights -> uint8 gate id, first maximum on ties
+ * (weights.argmax(-1).to(uint8), difflogic/difflogic.py:146). */
+DL_API int dl_argmax_gate_u8(const float *w, uint8_t *gate, int64_t n_out, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Bit packing.
+ * Replaces tensor_packbits_cuda, difflogic_kernel.cu:583-625 (kernel :547-581), bound at
+ * difflogic.cpp:69-74.  t is bool (one byte, non-zero = true) feature-major [n][batch];
+ * out is [n][ceil(batch/bit_count)] words, every word fully written, pad bits zero.
+ * pad_len = (bit_count - batch % bit_count) % bit_count is the caller's to compute.
+ * ---------------------------------------------------------------------------------------- */
+DL_API int dl_packbits(const uint8_t *t, void *out, int64_t n, int64_t batch, int bit_count, void *stream);
+
+/* Same result from the batch-major matrix t[batch][n] the user holds: the transpose that
+ * PackBitsTensor.__init__ does first (difflogic/packbitstensor.py:15) is folded in. */
+DL_API int dl_packbits_batch_major(const uint8_t *t, void *out, int64_t n, int64_t batch, int bit_count,
+                            void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Group bit-sum.
+ * Replaces groupbitsum, difflogic_kernel.cu:666-700 (kernel :631-664), bound at
+ * difflogic.cpp:75-83 (whose n % k check is DL_ERR_NOT_DIVISIBLE here).
+ * x [n][words] -> out [batch][k] int32, batch = words*bit_count - pad_len, contiguous.
+ * ---------------------------------------------------------------------------------------- */
+DL_API int dl_groupbitsum(const void *x, int32_t *out, int64_t n, int64_t words, int64_t pad_len, int64_t k,
+                   int bit_count, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Float GroupSum, forward and backward, on the feature-major activation of the last layer.
+ * Replaces the torch expression of GroupSum.forward, difflogic/difflogic.py:195-196
+ * (reshape -> sum -> / tau) and its autograd.
+ *   out[s][c]    = inv_tau * sum_{r < n/k} x[c*n/k + r][s]
+ *   grad_x[i][s] = inv_tau * grad_out[s][i / (n/k)]
+ * The forward needs scratch memory: dl_groupsum_workspace_bytes(n, batch, k) bytes, 256-byte
+ * aligned, owned by the caller.  Its first 4096 bytes hold counters that must be zero before
+ * the first use; the kernel leaves them zero again.  Calls that share a workspace must not
+ * overlap on the GPU.
+ * ---------------------------------------------------------------------------------------- */
+DL_API size_t dl_groupsum_workspace_bytes(int64_t n, int64_t batch, int64_t k);
+DL_API int dl_groupsum_f32(const float *x, float *out, void *workspace, int64_t n, int64_t batch, int64_t k,
+                    float inv_tau, void *stream);
+DL_API int dl_groupsum_backward_f32(const float *grad_out, float *grad_x, int64_t n, int64_t batch, int64_t k,
+                             float inv_tau, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIFFLOGIC_B200_H */

@@ -293,3 +293,44 @@ def csr_of_connections(idx_a, idx_b, n_in: int):
     start = np.array([0] + [len(l) for l in lists]).cumsum().astype(np.int64)
     flat = np.array([v for l in lists for v in l], dtype=np.int64)
     return start, flat
+
+
+# ---------------------------------------------------------------------------------------------
+# C restatement of the whole packed net (oracle/bitnet_oracle.c), used for larger batches and as
+# the timed CPU baseline.
+# ---------------------------------------------------------------------------------------------
+
+_c_lib = None
+
+
+def c_oracle():
+    """Loads oracle/_ref/libbitnet_oracle.so, building it with gcc when it is missing."""
+    global _c_lib
+    if _c_lib is None:
+        import ctypes
+        from oracle import build_oracle
+        lib = ctypes.CDLL(build_oracle.build())
+        p, i64 = ctypes.c_void_p, ctypes.c_int64
+        lib.oracle_apply_net.restype = None
+        lib.oracle_apply_net.argtypes = [p, p, i64, i64, ctypes.c_int, p, p, p, p, i64, ctypes.c_int]
+        lib.oracle_eval_layer.restype = None
+        lib.oracle_eval_layer.argtypes = [p, p, p, p, p, i64, i64]
+        _c_lib = lib
+    return _c_lib
+
+
+def c_packed_net_counts(x_bool_bm: np.ndarray, idx_a, idx_b, gate_ids, k: int, threads: int = 1) -> np.ndarray:
+    """bool [B, n_in] -> int32 [B, k], 64 samples per block like CompiledLogicNet(num_bits=64)
+    (compiled_model.py:342-370 for the padding, :159-239 for the per-block work)."""
+    B, n_in = x_bool_bm.shape
+    blocks = -(-B // 64)
+    padded = np.zeros((blocks * 64, n_in), dtype=np.uint8)
+    padded[:B] = x_bool_bm != 0
+    widths = np.array([len(a) for a in idx_a], dtype=np.int64)
+    a = np.ascontiguousarray(np.concatenate([np.asarray(v, dtype=np.int64) for v in idx_a]))
+    b = np.ascontiguousarray(np.concatenate([np.asarray(v, dtype=np.int64) for v in idx_b]))
+    op = np.ascontiguousarray(np.concatenate([np.asarray(v, dtype=np.uint8) for v in gate_ids]))
+    out = np.zeros((blocks * 64, k), dtype=np.int32)
+    c_oracle().oracle_apply_net(padded.ctypes.data, out.ctypes.data, blocks, n_in, len(widths), widths.ctypes.data,
+                                a.ctypes.data, b.ctypes.data, op.ctypes.data, k, threads)
+    return out[:B]

@@ -1,0 +1,250 @@
+"""End-to-end parity of the Python API on the CUDA path: golden fixtures made by the reference,
+the CPU oracle, the reference-named native shim, and the packed-bit pipeline.  Needs a B200."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import difflogic_b200 as D
+from oracle import logic_oracle as O
+from tests.helpers import assert_forward_close, assert_grad_close, build_model, logic_layers
+
+pytestmark = pytest.mark.gpu
+
+
+def _fixture_net(golden_dir, name):
+    g = np.load(os.path.join(golden_dir, name))
+    dims = [int(v) for v in g["dims"]]
+    L = len(dims) - 1
+    ws = [torch.tensor(g["w0_%d" % i]) for i in range(L)]
+    aa = [torch.tensor(g["a_%d" % i]) for i in range(L)]
+    bb = [torch.tensor(g["b_%d" % i]) for i in range(L)]
+    return g, dims, ws, aa, bb
+
+
+@pytest.mark.parametrize("name", ["small_net.npz", "small_net_gf2.npz"])
+def test_small_net_against_reference_fixture(golden_dir, name):
+    g, dims, ws, aa, bb = _fixture_net(golden_dir, name)
+    k, tau, gf = int(g["k"]), float(g["tau"]), float(g["grad_factor"])
+    model = build_model(dims, k, tau, ws, aa, bb, grad_factor=gf)
+    x = torch.tensor(g["x"]).cuda()
+    y = torch.tensor(g["y"]).cuda()
+    L = len(dims) - 1
+
+    model.eval()
+    with torch.no_grad():
+        ev = model(x)
+    assert torch.equal(ev.cpu(), torch.tensor(g["eval_logits"]))  # binary inputs, one gate each: exact
+
+    # packed path == CompiledLogicNet counts of the reference, for every word width
+    for bits in (8, 16, 32, 64):
+        with torch.no_grad():
+            counts = model(D.PackBitsTensor(x.bool(), bit_count=bits))
+        assert counts.dtype == torch.int32
+        assert np.array_equal(counts.cpu().numpy(), g["compiled_counts_%d" % bits]), bits
+
+    model.train()
+    xr = x.clone().requires_grad_(True)
+    torch.nn.functional.cross_entropy(model(xr), y).backward()
+    assert_grad_close(xr.grad, torch.tensor(g["grad_x"]), "grad wrt input")
+    for l in logic_layers(model):
+        l.weights.grad = None
+
+    opt = torch.optim.Adam(model.parameters(), lr=0.01)
+    logits = model(x)
+    loss = torch.nn.functional.cross_entropy(logits, y)
+    opt.zero_grad()
+    loss.backward()
+    assert_forward_close(logits, torch.tensor(g["train_logits"]), "train logits")
+    assert abs(loss.item() - float(g["loss"])) <= 1e-5 * abs(float(g["loss"]))
+    for i, l in enumerate(logic_layers(model)):
+        assert_grad_close(l.weights.grad, torch.tensor(g["grad_%d" % i]), "grad layer %d" % i)
+    opt.step()
+    for i, l in enumerate(logic_layers(model)):
+        # Adam's first step moves every weight by ~lr*sign(grad); compare the update, not the weight
+        ref_step = torch.tensor(g["w1_%d" % i]) - torch.tensor(g["w0_%d" % i])
+        got_step = l.weights.detach().cpu() - torch.tensor(g["w0_%d" % i])
+        big = torch.tensor(g["grad_%d" % i]).abs() > 1e-3 * torch.tensor(g["grad_%d" % i]).abs().max()
+        assert torch.allclose(got_step[big], ref_step[big], rtol=1e-3, atol=1e-6)
+
+
+def test_config1_against_reference_fixture(golden_dir):
+    """784 -> 4 x 8000 -> GroupSum(10, tau 10), batch 100, seed 0: the reference's CPU-runnable case."""
+    g = np.load(os.path.join(golden_dir, "config1.npz"))
+    torch.manual_seed(0)
+    dims = [784, 8000, 8000, 8000, 8000]
+    net = O.OracleNet.build(dims, 10, 10.0)
+    x = (torch.rand(100, 784) < 0.19).float()
+    y = torch.randint(0, 10, (100,))
+    assert np.array_equal(y.numpy(), g["y"])
+    model = build_model(dims, 10, 10.0, net.weights, net.idx_a, net.idx_b)
+    xd, yd = x.cuda(), y.cuda()
+
+    model.eval()
+    with torch.no_grad():
+        assert torch.equal(model(xd).cpu(), torch.tensor(g["eval_logits"]))
+        counts = model(D.PackBitsTensor(xd.bool(), bit_count=64))
+    assert np.array_equal(counts.cpu().numpy(), g["compiled_counts_64"])
+    assert np.array_equal(counts.cpu().numpy(), np.rint(g["eval_logits"] * 10.0).astype(np.int32))
+
+    model.train()
+    opt = torch.optim.Adam(model.parameters(), lr=0.01)
+    logits = model(xd)
+    loss = torch.nn.functional.cross_entropy(logits, yd)
+    opt.zero_grad()
+    loss.backward()
+    assert_forward_close(logits, torch.tensor(g["train_logits"]), "config1 logits")
+    assert abs(loss.item() - float(g["loss"])) <= 1e-5 * abs(float(g["loss"]))
+    # full gradients against the oracle (which the CPU suite pins to the same fixture)
+    _, _, ref_grads = net.train_step(x, y)
+    for i, l in enumerate(logic_layers(model)):
+        assert_grad_close(l.weights.grad, ref_grads[i], "config1 grad layer %d" % i)
+        pos = torch.tensor(g["pos_%d" % i])
+        got = l.weights.grad.detach().cpu().reshape(-1)[pos]
+        scale = float(g["grad_absmax_%d" % i])
+        assert (got - torch.tensor(g["grad_sample_%d" % i])).abs().max().item() <= 1e-4 * scale
+    opt.step()
+    model.eval()
+    with torch.no_grad():
+        after = model(xd)
+    # discrete outputs after the step: at most a few gates may flip on an arg-max tie-break
+    ref_after = torch.tensor(g["eval_logits_after_step"])
+    assert (after.cpu() - ref_after).abs().max().item() <= 0.5
+
+
+def test_deep_net_gradients_not_worse_than_reference_fp32():
+    """12 layers with grad_factor 2: the reference's own fp32 gradients of the early layers are
+    rounding noise, so the kernels are held to the fp32 reference's own distance from fp64."""
+    torch.manual_seed(3)
+    dims = [64] + [512] * 8
+    net = O.OracleNet.build(dims, 2, 20.0, 2.0)
+    x = (torch.rand(96, 64) < 0.5).float()
+    y = torch.randint(0, 2, (96,))
+    net64 = net.double()
+    l64 = torch.nn.functional.cross_entropy(net64.forward(x.double(), True), y)
+    l64.backward()
+    l32 = torch.nn.functional.cross_entropy(net.forward(x, True), y)
+    l32.backward()
+    model = build_model(dims, 2, 20.0, net.weights, net.idx_a, net.idx_b, grad_factor=2.0)
+    model.train()
+    torch.nn.functional.cross_entropy(model(x.cuda()), y.cuda()).backward()
+    for i, l in enumerate(logic_layers(model)):
+        truth = net64.weights[i].grad
+        ref_err = (net.weights[i].grad.double() - truth).abs().max().item()
+        got_err = (l.weights.grad.detach().cpu().double() - truth).abs().max().item()
+        scale = truth.abs().max().item()
+        assert got_err <= max(2.0 * ref_err, 1e-4 * scale), (i, got_err, ref_err, scale)
+
+
+def test_shim_has_the_reference_native_interface():
+    import difflogic_b200.difflogic_cuda as dc
+    n_in, n_out, batch = 40, 64, 50
+    g = torch.Generator().manual_seed(9)
+    a = torch.randint(0, n_in, (n_out,), generator=g)
+    b = torch.randint(0, n_in, (n_out,), generator=g)
+    b[3] = a[3]
+    w = torch.softmax(torch.randn(n_out, 16, generator=g), -1)
+    x = torch.rand(batch, n_in, generator=g)
+    gy = torch.randn(batch, n_out, generator=g)
+
+    xr = x.clone().requires_grad_(True)
+    wr = w.clone().requires_grad_(True)
+    ref = O.mix_gates(xr[:, a], xr[:, b], wr)
+    ref.backward(gy)
+    xd, ad, bd, wd, gyd = x.T.contiguous().cuda(), a.cuda(), b.cuda(), w.cuda(), gy.T.contiguous().cuda()
+    assert_forward_close(dc.forward(xd, ad, bd, wd).T, ref, "shim forward")
+    assert_grad_close(dc.backward_w(xd, ad, bd, gyd), wr.grad, "shim backward_w")
+    start, lst = O.csr_of_connections(a.numpy(), b.numpy(), n_in)
+    gx = dc.backward_x(xd, ad, bd, wd, gyd, torch.tensor(start).cuda(), torch.tensor(lst).cuda())
+    assert_grad_close(gx.T, xr.grad, "shim backward_x")
+
+    t = torch.rand(n_in, 70, generator=g) < 0.5
+    words, pad = dc.tensor_packbits_cuda(t.cuda(), 32)
+    ref_words, ref_pad = O.pack_bits(t.numpy(), 32)
+    assert pad == ref_pad and np.array_equal(words.cpu().numpy(), ref_words)
+    gate = torch.randint(0, 16, (n_out,), generator=g).to(torch.uint8)
+    out = dc.eval(words, ad, bd, gate.cuda())
+    ref_out = O.eval_packed(ref_words, a.numpy(), b.numpy(), gate.numpy())
+    assert np.array_equal(out.cpu().numpy(), ref_out)
+    assert np.array_equal(dc.groupbitsum(out, pad, 4).cpu().numpy(), O.group_bit_sum(ref_out, ref_pad, 4))
+    with pytest.raises(ValueError):
+        dc.groupbitsum(out, pad, 5)
+    with pytest.raises(ValueError):
+        dc.tensor_packbits_cuda(t.cuda(), 7)
+
+    # the reference-named autograd node on top of it
+    from difflogic_b200.difflogic import LogicLayerCudaFunction
+    xg = xd.clone().requires_grad_(True)
+    wg = wd.clone().requires_grad_(True)
+    yy = LogicLayerCudaFunction.apply(xg, ad, bd, wg, torch.tensor(start).cuda(), torch.tensor(lst).cuda())
+    yy.backward(gyd)
+    assert_grad_close(xg.grad.T, xr.grad, "node grad_x")
+    assert_grad_close(wg.grad, wr.grad, "node grad_w")
+
+
+def test_api_surface_and_layouts():
+    torch.manual_seed(0)
+    layer = D.LogicLayer(20, 48, grad_factor=1.5)
+    assert layer.device == 'cuda' and layer.implementation == 'cuda' and layer.connections == 'random'
+    assert layer.weights.shape == (48, 16) and layer.weights.is_cuda
+    assert layer.indices[0].dtype == torch.int64 and layer.indices[0].is_cuda
+    assert layer.given_x_indices_of_y_start.shape == (21,) and layer.given_x_indices_of_y.shape == (96,)
+    assert layer.num_neurons == 48 and layer.num_weights == 48
+    assert list(layer.state_dict().keys()) == ['weights']
+    assert 'train' in repr(layer)
+    x = torch.rand(6, 20, device='cuda')
+    y = layer(x)
+    assert y.shape == (6, 48) and y.stride() == (1, 6)  # transposed view of the feature-major buffer
+    gs = D.GroupSum(4, tau=3.0)
+    out = gs(y)
+    assert out.shape == (6, 4)
+    assert torch.allclose(out, y.reshape(6, 4, 12).sum(-1) / 3.0, rtol=1e-5)
+    # generic (batch-major, 3-D) inputs still work
+    z = torch.rand(2, 3, 8, device='cuda')
+    assert torch.allclose(gs(z), z.reshape(2, 3, 4, 2).sum(-1) / 3.0)
+
+    layer.eval()
+    p = D.PackBitsTensor(torch.rand(70, 20, device='cuda') < 0.5)
+    assert p.bit_count == 32 and p.t.dtype == torch.int32 and p.t.shape == (20, 3) and p.pad_len == 26
+    assert p.flatten() is p
+    q = layer(p)
+    assert q is p and p.t.shape == (48, 3)  # in place on the caller's object
+    assert gs(p).shape == (70, 4) and gs(p).dtype == torch.int32
+    layer.train()
+    with pytest.raises(AssertionError):
+        layer(p)
+    with pytest.raises(NotImplementedError):
+        D.PackBitsTensor(torch.zeros(4, 4, dtype=torch.bool), device='cpu')
+    assert len(repr(D.PackBitsTensor(torch.rand(40, 3, device='cuda') < 0.5, bit_count=8)).split('\n')) == 3
+
+
+def test_unique_connections_layer_trains():
+    torch.manual_seed(1)
+    layer = D.LogicLayer(16, 40, connections='unique')
+    ref = D.LogicLayer(16, 40, device='cpu', connections='unique')
+    ref.set_connections(layer.indices[0].cpu(), layer.indices[1].cpu())
+    with torch.no_grad():
+        ref.weights.copy_(layer.weights.cpu())
+    x = torch.rand(9, 16)
+    xa = x.clone().cuda().requires_grad_(True)
+    xb = x.clone().requires_grad_(True)
+    layer(xa).sum().backward()
+    ref(xb).sum().backward()
+    assert_grad_close(xa.grad, xb.grad, "unique grad_x")
+    assert_grad_close(layer.weights.grad, ref.weights.grad, "unique grad_w")
+
+
+def test_packed_eval_larger_batch_against_oracle_and_float_path():
+    torch.manual_seed(4)
+    dims = [100, 640, 640, 320]
+    net = O.OracleNet.build(dims, 10, 1.0)
+    model = build_model(dims, 10, 1.0, net.weights, net.idx_a, net.idx_b)
+    model.eval()
+    x = torch.rand(5000, 100) < 0.3
+    ref = O.packed_net_counts(x.numpy(), net.idx_a, net.idx_b, net.gate_ids(), 10, 64)
+    with torch.no_grad():
+        counts = model(D.PackBitsTensor(x.cuda(), bit_count=64))
+        fl = model(x.cuda().float())
+    assert np.array_equal(counts.cpu().numpy(), ref)
+    assert np.array_equal(np.rint(fl.cpu().numpy()).astype(np.int32), ref)

@@ -127,3 +127,20 @@ def test_csr_of_connections_lists_each_neuron_twice():
     start, flat = O.csr_of_connections(a, b, 3)
     assert list(start) == [0, 2, 5, 8]
     assert list(flat) == [0, 2, 0, 3, 3, 1, 1, 2]
+
+
+@pytest.mark.parametrize("name", ["small_net.npz", "small_net_gf2.npz"])
+def test_c_oracle_matches_compiled_logic_net(golden_dir, name):
+    g = _load(golden_dir, name)
+    net, L = _net_from_fixture(g)
+    for threads in (1, 3):
+        counts = O.c_packed_net_counts(g["x"].astype(bool), net.idx_a, net.idx_b, net.gate_ids(), int(g["k"]), threads)
+        assert np.array_equal(counts, g["compiled_counts_64"])
+
+
+def test_c_oracle_matches_numpy_oracle_on_ragged_batch():
+    torch.manual_seed(8)
+    net = O.OracleNet.build([30, 64, 50], 5, 1.0)
+    x = torch.rand(200, 30) < 0.5
+    ref = O.packed_net_counts(x.numpy(), net.idx_a, net.idx_b, net.gate_ids(), 5, 64)
+    assert np.array_equal(O.c_packed_net_counts(x.numpy(), net.idx_a, net.idx_b, net.gate_ids(), 5, 2), ref)
