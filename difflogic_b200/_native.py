@@ -23,6 +23,7 @@ W_LOGITS, W_PROBS, W_ARGMAX = 0, 1, 2
 SIGNATURES = {
     "dl_version": (_int, []),
     "dl_last_error_string": (ctypes.c_char_p, []),
+    "dl_async_error": (_int, []),
     "dl_forward_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _ptr]),
     "dl_coefs_f32": (_int, [_ptr, _int, _ptr, _i64, _ptr]),
     "dl_backward_w_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _int, _ptr, _i64, _i64, _i64, _ptr]),
@@ -39,6 +40,12 @@ SIGNATURES = {
 }
 
 _lib = None
+_launches = 0
+
+
+def launch_count():
+    """Number of kernel launches issued through check() so far (every checked entry point launches one kernel)."""
+    return _launches
 
 
 class NativeLibraryMissing(RuntimeError):
@@ -74,7 +81,9 @@ def last_error():
 def check(status):
     """Maps a status code to the exception type the reference raises for the same mistake:
     ValueError for a bad bit_count or a non-divisible group count, RuntimeError otherwise."""
+    global _launches
     if status == DL_OK:
+        _launches += 1
         return
     msg = last_error()
     if status in (DL_ERR_BAD_BIT_COUNT, DL_ERR_NOT_DIVISIBLE):

@@ -1,7 +1,7 @@
 // Float GroupSum on the feature-major activation of the last layer, forward and backward.
 //
-//   out[s][c]    = inv_tau * sum_{r < m} x[c*m + r][s]          m = n / k
-//   grad_x[i][s] = inv_tau * grad_out[s][i / m]
+//   out[s][c]    = (sum_{r < m} x[c*m + r][s]) / tau          m = n / k
+//   grad_x[i][s] = grad_out[s][i / m] / tau
 //
 // Forward.  The rows of a class are split into `chunks` pieces; a CTA sums one piece for a
 // block of 128 batch columns (32 lanes x float4, 8 warps striding the rows, shared-memory
@@ -28,7 +28,7 @@ static int64_t groupsum_chunks(int64_t n, int64_t batch, int64_t k) {
 
 __global__ void __launch_bounds__(kThreads)
 groupsum_kernel(const float *__restrict__ x, float *__restrict__ out, unsigned int *__restrict__ counters,
-                float *__restrict__ partial, int64_t batch, int k, int m, int chunks, float inv_tau) {
+                float *__restrict__ partial, int64_t batch, int k, int m, int chunks, float tau) {
     __shared__ float s_part[8][kGsCols];
     __shared__ bool s_last;
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -67,7 +67,7 @@ groupsum_kernel(const float *__restrict__ x, float *__restrict__ out, unsigned i
         for (int wv = 0; wv < 8; ++wv) sum += s_part[wv][tid];
     }
     if (chunks == 1) {
-        if (tid < kGsCols && gcol < batch) out[gcol * k + c] = sum * inv_tau;
+        if (tid < kGsCols && gcol < batch) out[gcol * k + c] = sum / tau;
         return;
     }
     // partial[(c * chunks + q)][batch]
@@ -85,14 +85,14 @@ groupsum_kernel(const float *__restrict__ x, float *__restrict__ out, unsigned i
     if (tid < kGsCols && gcol < batch) {
         float total = 0.f;
         for (int qq = 0; qq < chunks; ++qq) total += __ldcg(partial + ((int64_t)c * chunks + qq) * batch + gcol);
-        out[gcol * k + c] = total * inv_tau;
+        out[gcol * k + c] = total / tau;
     }
     if (tid == 0) *counter = 0u;  // ready for the next call
 }
 
 __global__ void __launch_bounds__(kThreads)
 groupsum_backward_kernel(const float *__restrict__ grad_out, float *__restrict__ grad_x, int64_t n, int64_t batch, int k,
-                         int m, float inv_tau) {
+                         int m, float tau) {
     // a warp per row, lanes along the batch
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const bool vec = (batch % 4 == 0);
@@ -102,14 +102,14 @@ groupsum_backward_kernel(const float *__restrict__ grad_out, float *__restrict__
         if (vec) {
             for (int64_t col = lane * 4; col < batch; col += 128) {
                 float4 v;
-                v.x = __ldg(grad_out + (col + 0) * k + c) * inv_tau;
-                v.y = __ldg(grad_out + (col + 1) * k + c) * inv_tau;
-                v.z = __ldg(grad_out + (col + 2) * k + c) * inv_tau;
-                v.w = __ldg(grad_out + (col + 3) * k + c) * inv_tau;
+                v.x = __ldg(grad_out + (col + 0) * k + c) / tau;
+                v.y = __ldg(grad_out + (col + 1) * k + c) / tau;
+                v.z = __ldg(grad_out + (col + 2) * k + c) / tau;
+                v.w = __ldg(grad_out + (col + 3) * k + c) / tau;
                 *reinterpret_cast<float4 *>(dst + col) = v;
             }
         } else {
-            for (int64_t col = lane; col < batch; col += 32) dst[col] = __ldg(grad_out + col * k + c) * inv_tau;
+            for (int64_t col = lane; col < batch; col += 32) dst[col] = __ldg(grad_out + col * k + c) / tau;
         }
     }
 }
@@ -132,7 +132,7 @@ extern "C" DL_API size_t dl_groupsum_workspace_bytes(int64_t n, int64_t batch, i
     return (size_t)kGsCounterBytes + (size_t)(k * chunks * batch) * sizeof(float);
 }
 
-extern "C" DL_API int dl_groupsum_f32(const float *x, float *out, void *workspace, int64_t n, int64_t batch, int64_t k, float inv_tau,
+extern "C" DL_API int dl_groupsum_f32(const float *x, float *out, void *workspace, int64_t n, int64_t batch, int64_t k, float tau,
                                void *stream) {
     if (int s = groupsum_check("dl_groupsum_f32", n, batch, k)) return s;
     if (batch == 0) return DL_OK;
@@ -148,12 +148,12 @@ extern "C" DL_API int dl_groupsum_f32(const float *x, float *out, void *workspac
     float *partial = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + kGsCounterBytes);
     const dim3 grid((unsigned)colblocks, (unsigned)k, (unsigned)chunks);
     groupsum_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(x, out, counters, partial, batch, (int)k, (int)(n / k),
-                                                              (int)chunks, inv_tau);
+                                                              (int)chunks, tau);
     return launch_status("dl_groupsum_f32");
 }
 
 extern "C" DL_API int dl_groupsum_backward_f32(const float *grad_out, float *grad_x, int64_t n, int64_t batch, int64_t k,
-                                        float inv_tau, void *stream) {
+                                        float tau, void *stream) {
     if (int s = groupsum_check("dl_groupsum_backward_f32", n, batch, k)) return s;
     if (batch == 0 || n == 0) return DL_OK;
     DL_REQUIRE(grad_out && grad_x, DL_ERR_INVALID_ARG, "dl_groupsum_backward_f32: null pointer");
@@ -162,6 +162,6 @@ extern "C" DL_API int dl_groupsum_backward_f32(const float *grad_out, float *gra
     int64_t blocks = ceil_div(n, 8);
     if (blocks > 148 * 16) blocks = 148 * 16;
     groupsum_backward_kernel<<<(unsigned)blocks, kThreads, 0, as_stream(stream)>>>(grad_out, grad_x, n, batch, (int)k,
-                                                                                  (int)(n / k), inv_tau);
+                                                                                  (int)(n / k), tau);
     return launch_status("dl_groupsum_backward_f32");
 }

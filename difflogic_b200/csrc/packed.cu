@@ -6,10 +6,21 @@
 // words*bit_count/8 bytes and move it in the widest unit that divides it (16 bytes when they
 // can).  The work is bitwise integer logic bounded by HBM traffic; there is nothing for
 // tensor cores to do.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "gates.cuh"
+#include "bitcount.cuh"
 
 namespace dl {
+
+// packed_tma.cu: the same eval with the gathered rows staged in shared memory by bulk copies
+bool eval_tma_applicable(const void *x, const void *y, int64_t row_bytes, int64_t n_out);
+int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_out,
+                    int64_t row_bytes, cudaStream_t st);
+// groupbitsum_tma.cu: the group bit-sum with rows staged the same way
+bool groupbitsum_tma_applicable(const void *x, int64_t n, int64_t row_bytes, int64_t k);
+int launch_groupbitsum_tma(const void *x, int32_t *out, int64_t n, int64_t row_bytes, int64_t batch, int64_t k, cudaStream_t st);
 
 // ---------------------------------------------------------------------------------------------
 // eval:  y[j][c] = gate_j(x[a_j][c], x[b_j][c])
@@ -182,59 +193,6 @@ packbits_bm_kernel(const uint8_t *__restrict__ t, uint8_t *__restrict__ out, int
 // add per bit.  The planes are then spread to per-sample integers four samples at a time
 // (16-bit fields) and added into a shared-memory tile that leaves as contiguous int32 runs.
 // ---------------------------------------------------------------------------------------------
-#define DL_CSA(h, l, a, b, c)               \
-    {                                       \
-        const unsigned long long u_ = (a) ^ (b); \
-        const unsigned long long c_ = (c);  \
-        h = ((a) & (b)) | (u_ & c_);        \
-        l = u_ ^ c_;                        \
-    }
-
-constexpr int kHiPlanes = 9;                      // weights 8 .. 2048
-constexpr int kPlanes = 3 + kHiPlanes;            // ones, twos, fours + high planes
-constexpr int kMaxChunkRows = 8 * (1 << kHiPlanes) - 1;  // 4095
-
-struct BitCounter {
-    unsigned long long ones, twos, fours, hi[kHiPlanes];
-    __device__ __forceinline__ void clear() {
-        ones = twos = fours = 0ull;
-#pragma unroll
-        for (int q = 0; q < kHiPlanes; ++q) hi[q] = 0ull;
-    }
-    __device__ __forceinline__ void add8(const unsigned long long (&v)[8]) {
-        unsigned long long t2a, t2b, t4a, t4b, e8;
-        DL_CSA(t2a, ones, ones, v[0], v[1]);
-        DL_CSA(t2b, ones, ones, v[2], v[3]);
-        DL_CSA(t4a, twos, twos, t2a, t2b);
-        DL_CSA(t2a, ones, ones, v[4], v[5]);
-        DL_CSA(t2b, ones, ones, v[6], v[7]);
-        DL_CSA(t4b, twos, twos, t2a, t2b);
-        DL_CSA(e8, fours, fours, t4a, t4b);
-        unsigned long long carry = e8;
-#pragma unroll
-        for (int q = 0; q < kHiPlanes; ++q) {
-            const unsigned long long t = hi[q] & carry;
-            hi[q] ^= carry;
-            carry = t;
-        }
-    }
-    __device__ __forceinline__ void add1(unsigned long long v) {
-        unsigned long long carry = v, t;
-        t = ones & carry; ones ^= carry; carry = t;
-        t = twos & carry; twos ^= carry; carry = t;
-        t = fours & carry; fours ^= carry; carry = t;
-#pragma unroll
-        for (int q = 0; q < kHiPlanes; ++q) {
-            t = hi[q] & carry;
-            hi[q] ^= carry;
-            carry = t;
-        }
-    }
-    __device__ __forceinline__ unsigned long long plane(int p) const {
-        return p == 0 ? ones : p == 1 ? twos : p == 2 ? fours : hi[p - 3];
-    }
-};
-
 // planes -> integers for the 64 samples of one word: field f of `acc` holds sample s + 16 f.
 template <int LANES>
 __device__ __forceinline__ void spread_counts(const BitCounter &cn, int *dst, int nplanes) {
@@ -375,6 +333,10 @@ extern "C" DL_API int dl_eval_packed(const void *x, const int64_t *a, const int6
     const int64_t row_bytes = words * (bit_count / 8);
     cudaStream_t st = as_stream(stream);
     auto fits = [&](int64_t sz) { return row_bytes % sz == 0 && aligned_to(x, sz) && aligned_to(y, sz); };
+    // DL_EVAL_KERNEL=plain forces the register-staged kernel (for A/B measurements)
+    const char *force = getenv("DL_EVAL_KERNEL");
+    const bool plain_only = force != nullptr && force[0] == 'p';
+    if (!plain_only && eval_tma_applicable(x, y, row_bytes, n_out)) return launch_eval_tma(x, a, b, gate, y, n_out, row_bytes, st);
     if (fits(16)) return launch_eval<uint4>(x, a, b, gate, y, n_out, row_bytes, st);
     if (fits(8)) return launch_eval<unsigned long long>(x, a, b, gate, y, n_out, row_bytes, st);
     if (fits(4)) return launch_eval<uint32_t>(x, a, b, gate, y, n_out, row_bytes, st);
@@ -428,6 +390,11 @@ extern "C" DL_API int dl_groupbitsum(const void *x, int32_t *out, int64_t n, int
     DL_REQUIRE(out && (x || n == 0), DL_ERR_INVALID_ARG, "dl_groupbitsum: null pointer");
     const int64_t row_bytes = words * (bit_count / 8);
     cudaStream_t st = as_stream(stream);
+    // DL_GROUPBITSUM_KERNEL=plain forces the register-staged kernel (for A/B measurements)
+    const char *force = getenv("DL_GROUPBITSUM_KERNEL");
+    const bool plain_only = force != nullptr && force[0] == 'p';
+    if (!plain_only && groupbitsum_tma_applicable(x, n, row_bytes, k))
+        return launch_groupbitsum_tma(x, out, n, row_bytes, batch, k, st);
     if (n > 0 && row_bytes % 16 == 0 && aligned_to(x, 16)) {
         const int64_t ncols16 = row_bytes / 16;
         // narrower column blocks when the batch alone cannot fill the machine

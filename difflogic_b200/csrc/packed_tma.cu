@@ -1,0 +1,203 @@
+// Packed-bit eval for long rows: gathered input rows staged in shared memory by bulk asynchronous
+// copies (TMA), warp-specialised.
+//
+// Why: the plain eval kernel keeps its loads in registers, and at 16 bytes per lane the register
+// file caps the bytes in flight per SM well below what HBM3e needs (ncu: 91 registers, 2 CTAs per SM,
+// 42 % of DRAM peak).  Here one producer warp issues a 1-D bulk copy per gathered row segment --
+// no registers, up to ~160 KB in flight per SM -- and eight consumer warps turn finished stages into
+// output rows with 16-byte shared loads, LOP3s and 16-byte global stores.
+//
+// Tiling: a tile is kTileRows neurons x `chunk` bytes of their rows.  Tiles are numbered column
+// chunk major, so the CTAs of the persistent grid (one per SM) work on the same column chunk of x at
+// the same time and the second reader of an input row finds it in L2; DRAM reads stay at one pass
+// over x.
+#include "common.cuh"
+#include "gates.cuh"
+#include "tma.cuh"
+
+namespace dl {
+
+constexpr int kTileRows = 8;        // neurons per tile: 16 row segments, one bulk copy each
+constexpr int kStages = 6;
+constexpr int kConsumerWarps = 8;
+constexpr int kTmaThreads = 32 * (1 + kConsumerWarps);
+constexpr int kMaxChunk = 2048;     // bytes of a row per tile; stage = 2*8*2048 = 32 KB, six stages in flight
+
+__device__ int g_async_error = 0;   // set when a bounded wait ran out; read by dl_async_error()
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(kTmaThreads, 1)
+eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
+                const uint8_t *__restrict__ gate, uint8_t *__restrict__ y, int64_t n_out, int64_t row_bytes, int chunk,
+                int64_t row_blocks, int64_t ntiles) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const size_t stage_bytes = (size_t)2 * kTileRows * chunk;
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kStages * stage_bytes);
+    uint64_t *empty = full + kStages;
+    uint8_t *meta = reinterpret_cast<uint8_t *>(empty + kStages);  // [kStages][kTileRows] gate ids
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, kConsumerWarps);
+        }
+        s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    volatile int *abort_flag = &s_abort;
+
+    if (warp == 0) {
+        // ---------------- producer: one bulk copy per (neuron, input) of the tile ----------------
+        // Lanes 0 .. 2*kTileRows-1 own one row segment each.  The connection indices of the NEXT tile are
+        // fetched while this tile's stage is still being waited for, so their latency is off the refill path.
+        const int r = lane % kTileRows, which = lane / kTileRows;
+        const bool copier = lane < 2 * kTileRows;
+        int64_t it = 0;
+        bool ok = true;
+        int64_t idx = 0;
+        uint32_t op = 0;
+        {
+            const int64_t j = (blockIdx.x % row_blocks) * kTileRows + r;
+            if (copier && blockIdx.x < ntiles && j < n_out) {
+                idx = __ldg((which ? b : a) + j);
+                op = __ldg(gate + j);
+            }
+        }
+        for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+            const int s = (int)(it % kStages);
+            const uint32_t use = (uint32_t)(it / kStages);
+            // prefetch for the tile after this one
+            int64_t idx_next = 0;
+            uint32_t op_next = 0;
+            const int64_t tn = t + gridDim.x;
+            if (copier && tn < ntiles) {
+                const int64_t jn = (tn % row_blocks) * kTileRows + r;
+                if (jn < n_out) {
+                    idx_next = __ldg((which ? b : a) + jn);
+                    op_next = __ldg(gate + jn);
+                }
+            }
+            if (!wait_or_abort(empty + s, (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+            const int64_t cb = t / row_blocks, nb = t % row_blocks;
+            const int64_t col0 = cb * chunk;
+            const uint32_t bytes = (uint32_t)min((int64_t)chunk, row_bytes - col0);
+            const bool valid = copier && nb * kTileRows + r < n_out;
+            const int nvalid = (int)min((int64_t)kTileRows, n_out - nb * kTileRows);
+            if (valid && which == 0) meta[s * kTileRows + r] = (uint8_t)op;
+            __syncwarp();
+            if (lane == 0) mbar_arrive_expect_tx(full + s, 2u * (uint32_t)nvalid * bytes);
+            __syncwarp();
+            if (valid)
+                bulk_load(smem + s * stage_bytes + (size_t)(which * kTileRows + r) * chunk, x + idx * row_bytes + col0, bytes,
+                          full + s);
+            idx = idx_next;
+            op = op_next;
+        }
+        if (!ok || *abort_flag) {
+            // something went wrong: flag it, stop the consumers, and give copies already issued time to land
+            if (lane == 0) {
+                g_async_error = 1;
+                s_abort = 1;
+            }
+            __syncwarp();
+            for (int s = 0; s < kStages; ++s) {
+                const int64_t fills = (it + kStages - 1 - s) / kStages;  // copies issued into stage s so far
+                if (fills > 0) mbar_wait(full + s, (uint32_t)(fills - 1) & 1u);
+            }
+        }
+    } else {
+        // ---------------- consumers: finished stages -> output rows ------------------------------
+        const int cw = warp - 1;
+        int64_t it = 0;
+        for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+            const int s = (int)(it % kStages);
+            const uint32_t use = (uint32_t)(it / kStages);
+            if (!wait_or_abort(full + s, use & 1u, abort_flag)) {
+                if (lane == 0) {
+                    g_async_error = 1;
+                    s_abort = 1;
+                }
+                break;
+            }
+            const int64_t cb = t / row_blocks, nb = t % row_blocks;
+            const int64_t col0 = cb * chunk;
+            const int vecs = (int)(min((int64_t)chunk, row_bytes - col0) / 16);
+            const int nvalid = (int)min((int64_t)kTileRows, n_out - nb * kTileRows);
+            const uint4 *sa = reinterpret_cast<const uint4 *>(smem + s * stage_bytes);
+            const uint4 *sb = reinterpret_cast<const uint4 *>(smem + s * stage_bytes + (size_t)kTileRows * chunk);
+            const int pitch = chunk / 16;
+            for (int r = cw; r < nvalid; r += kConsumerWarps) {
+                const GateMasks gm = gate_masks(meta[s * kTileRows + r]);
+                uint4 *dst = reinterpret_cast<uint4 *>(y + (nb * kTileRows + r) * row_bytes + col0);
+#pragma unroll 4
+                for (int c = lane; c < vecs; c += 32) {
+                    const uint4 va = sa[r * pitch + c], vb = sb[r * pitch + c];
+                    dst[c] = make_uint4(gate32(va.x, vb.x, gm), gate32(va.y, vb.y, gm), gate32(va.z, vb.z, gm),
+                                        gate32(va.w, vb.w, gm));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + s);
+        }
+    }
+}
+
+int groupbitsum_async_error();  // groupbitsum_tma.cu
+
+static int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// True when the staged kernel applies: 16-byte aligned rows of at least 512 bytes.
+bool eval_tma_applicable(const void *x, const void *y, int64_t row_bytes, int64_t n_out) {
+    return row_bytes % 16 == 0 && row_bytes >= 512 && n_out >= kTileRows && aligned_to(x, 16) && aligned_to(y, 16);
+}
+
+int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_out,
+                    int64_t row_bytes, cudaStream_t st) {
+    const int chunk = (int)(row_bytes < kMaxChunk ? row_bytes : kMaxChunk);
+    const int64_t col_chunks = ceil_div(row_bytes, chunk);
+    const int64_t row_blocks = ceil_div(n_out, kTileRows);
+    const int64_t ntiles = col_chunks * row_blocks;
+    const size_t smem = (size_t)kStages * 2 * kTileRows * chunk + 2 * kStages * sizeof(uint64_t) + kStages * kTileRows;
+    if (cudaFuncSetAttribute(eval_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return launch_status("dl_eval_packed (shared memory opt-in)");
+    const int64_t sms = sm_count();
+    const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
+    eval_tma_kernel<<<grid, kTmaThreads, smem, st>>>(reinterpret_cast<const uint8_t *>(x), a, b, gate,
+                                                    reinterpret_cast<uint8_t *>(y), n_out, row_bytes, chunk, row_blocks, ntiles);
+    return launch_status("dl_eval_packed");
+}
+
+}  // namespace dl
+
+// 1 if a bounded wait inside a kernel of this library ever ran out on the current device (the affected
+// launch produced incomplete output), else 0; negative on a CUDA error.  Synchronises the device.
+extern "C" DL_API int dl_async_error(void) {
+    int flag = 0;
+    if (cudaMemcpyFromSymbol(&flag, dl::g_async_error, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    const int other = dl::groupbitsum_async_error();
+    if (other < 0) return other;
+    return flag | other;
+}

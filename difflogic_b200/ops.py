@@ -256,7 +256,7 @@ def groupsum(x, k, tau):
     with torch.cuda.device(x.device):
         stream = N.stream_of(x)
         ws = _groupsum_workspace(x.device, stream, N.lib().dl_groupsum_workspace_bytes(n, batch, k))
-        N.check(N.lib().dl_groupsum_f32(x.data_ptr(), out.data_ptr(), ws.data_ptr(), n, batch, k, 1.0 / float(tau), stream))
+        N.check(N.lib().dl_groupsum_f32(x.data_ptr(), out.data_ptr(), ws.data_ptr(), n, batch, k, float(tau), stream))
     return out
 
 
@@ -266,6 +266,6 @@ def groupsum_backward(grad_out, n, tau):
     batch, k = grad_out.shape
     gx = torch.empty((n, batch), dtype=torch.float32, device=grad_out.device)
     with torch.cuda.device(grad_out.device):
-        N.check(N.lib().dl_groupsum_backward_f32(grad_out.data_ptr(), gx.data_ptr(), n, batch, k, 1.0 / float(tau),
+        N.check(N.lib().dl_groupsum_backward_f32(grad_out.data_ptr(), gx.data_ptr(), n, batch, k, float(tau),
                                                  N.stream_of(grad_out)))
     return gx

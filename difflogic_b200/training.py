@@ -1,0 +1,103 @@
+"""Training step of a logic gate network: eager or captured in a CUDA graph, on one GPU or
+batch-sharded over several (one process per GPU).
+
+The reference has no multi-GPU code; its step is `loss_fn(model(x), y) -> zero_grad -> backward ->
+optimizer.step` (experiments/main.py:174-181).  `TrainStep` runs exactly that.  When a process
+group is given, every rank holds a full replica of the weights and connection indices, works on
+its own shard of the batch, and the `[out_dim, 16]` weight gradients are averaged with one NCCL
+all-reduce per layer, launched on a side stream as soon as that layer's backward_w has finished so
+that it overlaps the rest of the backward pass.  Nothing else crosses GPUs.
+
+`capture()` records the whole step (H2D staging excluded) in one CUDA graph: the model's kernels
+launch on torch's current stream, allocate nothing themselves and never synchronise, so a step of
+~25 small kernels replays without per-launch host overhead.
+"""
+import torch
+import torch.distributed as dist
+
+
+class TrainStep:
+    def __init__(self, model, optimizer, loss_fn=None, process_group=None, world_size=None):
+        """
+        :param model:         module on the current CUDA device (replicated on every rank)
+        :param optimizer:     its optimizer; for `capture()` it must be graph-capturable
+                              (e.g. torch.optim.Adam(..., capturable=True))
+        :param loss_fn:       defaults to CrossEntropyLoss (mean over the local batch)
+        :param process_group: torch.distributed group to average gradients over, or None
+        """
+        self.model = model
+        self.optimizer = optimizer
+        self.loss_fn = loss_fn if loss_fn is not None else torch.nn.CrossEntropyLoss()
+        self.group = process_group
+        self.world_size = world_size if world_size is not None else (
+            dist.get_world_size(process_group) if process_group is not None else 1)
+        self.params = [p for p in model.parameters() if p.requires_grad]
+        self._graph = None
+        self._static_x = self._static_y = self._static_loss = None
+        self._comm_stream = None
+        self._hooks = []
+        if self.group is not None and self.world_size > 1:
+            self._comm_stream = torch.cuda.Stream()
+            for p in self.params:
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._reduce_when_ready))
+
+    # -- gradient exchange -----------------------------------------------------------------------
+
+    def _reduce_when_ready(self, param):
+        """Runs right after `param.grad` has been written by the layer's backward_w."""
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        self._comm_stream.wait_event(ready)
+        with torch.cuda.stream(self._comm_stream):
+            dist.all_reduce(param.grad, op=dist.ReduceOp.AVG, group=self.group)
+
+    def _join_comm(self):
+        if self._comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._comm_stream)
+
+    # -- the step --------------------------------------------------------------------------------
+
+    def _step(self, x, y):
+        loss = self.loss_fn(self.model(x), y)
+        self.optimizer.zero_grad(set_to_none=True)
+        loss.backward()
+        self._join_comm()
+        self.optimizer.step()
+        return loss.detach()
+
+    def __call__(self, x, y):
+        """One step on device tensors; returns the (local) loss as a device scalar."""
+        if self._graph is None:
+            return self._step(x, y)
+        self._static_x.copy_(x, non_blocking=True)
+        self._static_y.copy_(y, non_blocking=True)
+        self._graph.replay()
+        return self._static_loss
+
+    def capture(self, x, y, warmup=3):
+        """Captures the step in a CUDA graph.  `x`, `y` give the shapes; their contents are used for
+        `warmup` eager steps (they DO update the weights) that run before the capture."""
+        self._static_x = x.clone()
+        self._static_y = y.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self._step(self._static_x, self._static_y)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._static_loss = self._step(self._static_x, self._static_y)
+        self._graph = graph
+        return self
+
+    @property
+    def static_inputs(self):
+        return self._static_x, self._static_y
+
+    def replay(self):
+        """Replays the captured step on whatever the static input buffers hold."""
+        self._graph.replay()
+        return self._static_loss

@@ -52,6 +52,13 @@ enum {
 DL_API int dl_version(void);
 DL_API const char *dl_last_error_string(void);
 
+/* Kernels that stage data with asynchronous copies poll their barriers a bounded number of times
+ * instead of waiting forever.  Returns 1 if such a wait ever ran out on the current device (the
+ * launch it happened in wrote incomplete output), 0 if not, negative on a CUDA error.  This call
+ * synchronises the device; it is a diagnostic, not part of the hot path.  The reference has no
+ * counterpart: its kernels never wait on anything (difflogic_kernel.cu). */
+DL_API int dl_async_error(void);
+
 /* ------------------------------------------------------------------------------------------
  * Training forward.
  * Replaces logic_layer_cuda_forward, difflogic/cuda/difflogic_kernel.cu:259-297 (kernel
@@ -152,8 +159,8 @@ DL_API int dl_groupbitsum(const void *x, int32_t *out, int64_t n, int64_t words,
  * Float GroupSum, forward and backward, on the feature-major activation of the last layer.
  * Replaces the torch expression of GroupSum.forward, difflogic/difflogic.py:195-196
  * (reshape -> sum -> / tau) and its autograd.
- *   out[s][c]    = inv_tau * sum_{r < n/k} x[c*n/k + r][s]
- *   grad_x[i][s] = inv_tau * grad_out[s][i / (n/k)]
+ *   out[s][c]    = (sum_{r < n/k} x[c*n/k + r][s]) / tau
+ *   grad_x[i][s] = grad_out[s][i / (n/k)] / tau      (a true division, as the reference does)
  * The forward needs scratch memory: dl_groupsum_workspace_bytes(n, batch, k) bytes, 256-byte
  * aligned, owned by the caller.  Its first 4096 bytes hold counters that must be zero before
  * the first use; the kernel leaves them zero again.  Calls that share a workspace must not
@@ -161,9 +168,9 @@ DL_API int dl_groupbitsum(const void *x, int32_t *out, int64_t n, int64_t words,
  * ---------------------------------------------------------------------------------------- */
 DL_API size_t dl_groupsum_workspace_bytes(int64_t n, int64_t batch, int64_t k);
 DL_API int dl_groupsum_f32(const float *x, float *out, void *workspace, int64_t n, int64_t batch, int64_t k,
-                    float inv_tau, void *stream);
+                    float tau, void *stream);
 DL_API int dl_groupsum_backward_f32(const float *grad_out, float *grad_x, int64_t n, int64_t batch, int64_t k,
-                             float inv_tau, void *stream);
+                             float tau, void *stream);
 
 #ifdef __cplusplus
 }

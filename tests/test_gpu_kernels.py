@@ -10,6 +10,7 @@ from tests.helpers import assert_forward_close, assert_grad_close, random_layer
 pytestmark = pytest.mark.gpu
 
 ops = pytest.importorskip("difflogic_b200.ops")
+from difflogic_b200 import _native as N  # noqa: E402
 
 # (n_in, n_out, batch): ragged sizes (batch not a multiple of 4 / 32 / 128, n_out not of 32), one
 # column, one float4, several slabs
@@ -152,7 +153,8 @@ def test_packbits_treats_any_nonzero_byte_as_true():
 
 
 @pytest.mark.parametrize("bits", [8, 16, 32, 64])
-@pytest.mark.parametrize("shape", [(20, 32, 1), (33, 50, 3), (64, 100, 16), (100, 333, 70), (8, 5, 257)])
+@pytest.mark.parametrize("shape", [(20, 32, 1), (33, 50, 3), (64, 100, 16), (100, 333, 70), (8, 5, 257), (50, 37, 300),
+                                   (300, 1000, 1024), (40, 16, 2048 + 64)])
 def test_eval_packed_matches_oracle(bits, shape):
     n_in, n_out, words = shape
     g = torch.Generator().manual_seed(sum(shape) + bits)
@@ -164,6 +166,23 @@ def test_eval_packed_matches_oracle(bits, shape):
     ref = O.eval_packed(x.numpy(), a.numpy(), b.numpy(), gate.numpy())
     got = ops.eval_packed(_dev(x), _dev(a), _dev(b), _dev(gate))
     assert got.dtype == x.dtype and np.array_equal(got.cpu().numpy(), ref)
+    assert N.lib().dl_async_error() == 0  # no bounded wait of the staged kernel ran out
+
+
+def test_eval_packed_staged_and_plain_kernels_agree(monkeypatch):
+    """Rows of 8 KB: the bulk-copy staged kernel is chosen; DL_EVAL_KERNEL=plain forces the register kernel."""
+    n_in, n_out, words = 500, 777, 1024 + 6
+    g = torch.Generator().manual_seed(1)
+    x = torch.randint(-2**62, 2**62, (n_in, words), dtype=torch.int64, generator=g)
+    a = torch.randint(0, n_in, (n_out,), generator=g)
+    b = torch.randint(0, n_in, (n_out,), generator=g)
+    gate = torch.randint(0, 16, (n_out,), generator=g).to(torch.uint8)
+    ref = O.eval_packed(x.numpy(), a.numpy(), b.numpy(), gate.numpy())
+    staged = ops.eval_packed(_dev(x), _dev(a), _dev(b), _dev(gate))
+    monkeypatch.setenv("DL_EVAL_KERNEL", "plain")
+    plain = ops.eval_packed(_dev(x), _dev(a), _dev(b), _dev(gate))
+    assert np.array_equal(staged.cpu().numpy(), ref) and np.array_equal(plain.cpu().numpy(), ref)
+    assert N.lib().dl_async_error() == 0
 
 
 def test_argmax_gates_first_maximum_on_ties():
@@ -177,7 +196,7 @@ def test_argmax_gates_first_maximum_on_ties():
 
 @pytest.mark.parametrize("bits", [8, 16, 32, 64])
 @pytest.mark.parametrize("case", [(30, 3, 37), (40, 10, 64), (8000, 10, 200), (64, 2, 4096), (12, 1, 130), (6000, 2, 1000),
-                                  (50, 50, 77), (130, 10, 128 * 70)])
+                                  (50, 50, 77), (130, 10, 128 * 70), (2000, 2, 4160), (4100, 1, 2048)])
 def test_groupbitsum_matches_oracle(bits, case):
     n, k, batch = case
     t = torch.rand(n, batch, generator=torch.Generator().manual_seed(n + k + batch)) < 0.5
@@ -191,6 +210,20 @@ def test_groupbitsum_matches_oracle(bits, case):
     got = ops.groupbitsum(_dev(torch.from_numpy(words)), pad, k)
     assert got.dtype == torch.int32 and got.shape == (batch, k) and got.is_contiguous()
     assert np.array_equal(got.cpu().numpy(), ref)
+
+
+def test_groupbitsum_staged_and_plain_kernels_agree(monkeypatch):
+    """Rows of 2 KB: the bulk-copy staged kernel is chosen; DL_GROUPBITSUM_KERNEL=plain forces the register kernel."""
+    n, k, batch = 3000, 10, 16384 - 5
+    t = torch.rand(n, batch, generator=torch.Generator().manual_seed(12)) < 0.5
+    words, pad = O.pack_bits(t.numpy(), 64)
+    ref = O.group_bit_sum(words, pad, k)
+    xd = _dev(torch.from_numpy(words))
+    staged = ops.groupbitsum(xd, pad, k)
+    monkeypatch.setenv("DL_GROUPBITSUM_KERNEL", "plain")
+    plain = ops.groupbitsum(xd, pad, k)
+    assert np.array_equal(staged.cpu().numpy(), ref) and np.array_equal(plain.cpu().numpy(), ref)
+    assert N.lib().dl_async_error() == 0
 
 
 def test_groupbitsum_rejects_indivisible_rows():
