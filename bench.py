@@ -293,12 +293,12 @@ def bench_train(args, rank, world):
         L, st = _native.lib(), torch.cuda.current_stream().cuda_stream
         kernels = {
             "forward": (5, lambda: L.dl_forward_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), w.data_ptr(), 0, y.data_ptr(),
-                                                    coef.data_ptr(), n, n, TRAIN_BATCH, st)),
+                                                    coef.data_ptr(), n, n, TRAIN_BATCH, 1, st)),
             "backward_w": (5, lambda: L.dl_backward_w_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), gy.data_ptr(), w.data_ptr(), 0,
-                                                          gw.data_ptr(), n, n, TRAIN_BATCH, st)),
+                                                          gw.data_ptr(), n, n, TRAIN_BATCH, 1, st)),
             "backward_x": (4, lambda: L.dl_backward_x_f32(x.data_ptr(), coef.data_ptr(), gy.data_ptr(),
                                                           layer.given_x_indices_of_y_start.data_ptr(), layer._plan.data_ptr(),
-                                                          1.0, gx.data_ptr(), n, n, TRAIN_BATCH, st)),
+                                                          1.0, gx.data_ptr(), n, n, TRAIN_BATCH, 1, st)),
         }
         rows = {}
         for name, (count, fn) in kernels.items():

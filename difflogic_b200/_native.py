@@ -18,16 +18,17 @@ _f32 = ctypes.c_float
 
 DL_OK, DL_ERR_INVALID_ARG, DL_ERR_BAD_BIT_COUNT, DL_ERR_NOT_DIVISIBLE, DL_ERR_CUDA, DL_ERR_TOO_LARGE = range(6)
 W_LOGITS, W_PROBS, W_ARGMAX = 0, 1, 2
+LAUNCH_PLAIN, LAUNCH_OVERLAP_SETUP = 0, 1
 
 # name -> (restype, argtypes); mirrors include/difflogic_b200.h one to one
 SIGNATURES = {
     "dl_version": (_int, []),
     "dl_last_error_string": (ctypes.c_char_p, []),
     "dl_async_error": (_int, []),
-    "dl_forward_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _ptr]),
+    "dl_forward_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr]),
     "dl_coefs_f32": (_int, [_ptr, _int, _ptr, _i64, _ptr]),
-    "dl_backward_w_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _int, _ptr, _i64, _i64, _i64, _ptr]),
-    "dl_backward_x_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, _i64, _i64, _i64, _ptr]),
+    "dl_backward_w_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _int, _ptr, _i64, _i64, _i64, _int, _ptr]),
+    "dl_backward_x_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, _i64, _i64, _i64, _int, _ptr]),
     "dl_build_backward_plan": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr]),
     "dl_eval_packed": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr]),
     "dl_argmax_gate_u8": (_int, [_ptr, _ptr, _i64, _ptr]),

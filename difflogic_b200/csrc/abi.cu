@@ -1,6 +1,7 @@
 // Version, error reporting and the two per-neuron helper kernels (coefficients, arg-max gate).
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "gates.cuh"
@@ -15,6 +16,15 @@ int fail(int code, const char *fmt, ...) {
     vsnprintf(g_error, sizeof(g_error), fmt, ap);
     va_end(ap);
     return code;
+}
+
+bool pdl_enabled() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char *v = getenv("DL_PDL");
+        cached = (v != nullptr && v[0] == '0') ? 0 : 1;
+    }
+    return cached == 1;
 }
 
 int launch_status(const char *what) {

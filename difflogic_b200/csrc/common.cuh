@@ -30,3 +30,38 @@ static inline int pow2_at_least(int64_t v, int cap) {
     do {                                                  \
         if (!(cond)) return dl::fail((code), __VA_ARGS__); \
     } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  With DL_LAUNCH_OVERLAP_SETUP the small training kernels are
+// launched so that a kernel's set-up (reading the connection indices / the gather plan) may run
+// while the previous kernel in the stream is still draining; everything else is touched only
+// after grid_dependency_wait().  Without the launch attribute the two device calls are no-ops,
+// so the same kernels are correct under an ordinary launch.  DL_PDL=0 in the environment turns
+// the attribute off everywhere.
+// ---------------------------------------------------------------------------------------------
+namespace dl {
+
+bool pdl_enabled();
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_dependent(bool overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                           Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = (overlap && pdl_enabled()) ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
+}  // namespace dl

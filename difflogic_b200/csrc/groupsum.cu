@@ -19,8 +19,8 @@ constexpr int kGsMaxCounters = kGsCounterBytes / 4;
 static int64_t groupsum_chunks(int64_t n, int64_t batch, int64_t k) {
     const int64_t m = n / k;
     const int64_t colblocks = ceil_div(batch, kGsCols);
-    // aim at ~4 CTAs per SM over 148 SMs, at least 16 rows per piece
-    int64_t chunks = ceil_div(592, k * colblocks);
+    // aim at ~2 CTAs per SM over 148 SMs, at least 16 rows per piece
+    int64_t chunks = ceil_div(296, k * colblocks);
     if (chunks > ceil_div(m, 16)) chunks = ceil_div(m, 16);
     if (chunks < 1) chunks = 1;
     return chunks;

@@ -44,9 +44,64 @@ __device__ __forceinline__ float mixv(const float4 c, const float a, const float
 }
 
 // ---------------------------------------------------------------------------------------------
+// Coefficients of one neuron computed by four adjacent lanes (a "quad"), lane q holding gates
+// 4q .. 4q+3: softmax / pass-through / arg-max one-hot over the 16 weights, then the sum over
+// the gates of p_i times the gate's multilinear coefficients.  All 32 lanes of the warp call it.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v;
+}
+
+__device__ __forceinline__ float4 quad_coef(const float *__restrict__ wq, bool live, int q, int w_mode) {
+    float p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = live ? __ldg(wq + i) : 0.f;
+    if (w_mode == DL_W_LOGITS) {
+        float m = fmaxf(fmaxf(p[0], p[1]), fmaxf(p[2], p[3]));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { p[i] = expf(p[i] - m); s += p[i]; }
+        s = quad_sum(s);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = p[i] / s;
+    } else if (w_mode == DL_W_ARGMAX) {
+        int best = 0;
+        float m = p[0];
+#pragma unroll
+        for (int i = 1; i < 4; ++i) if (p[i] > m) { m = p[i]; best = i; }
+        int gbest = 4 * q + best;
+#pragma unroll
+        for (int off = 1; off <= 2; off <<= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, m, off);
+            const int og = __shfl_xor_sync(0xffffffffu, gbest, off);
+            if (om > m || (om == m && og < gbest)) { m = om; gbest = og; }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = (4 * q + i == gbest) ? 1.f : 0.f;
+    }
+    // gate 4q+i has truth table t00 = q>>1, t01 = q&1, t10 = i>>1, t11 = i&1
+    const int t00 = q >> 1, t01 = q & 1;
+    float c0 = 0.f, ca = 0.f, cb = 0.f, cab = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t10 = i >> 1, t11 = i & 1;
+        c0 += p[i] * (float)t00;
+        ca += p[i] * (float)(t10 - t00);
+        cb += p[i] * (float)(t01 - t00);
+        cab += p[i] * (float)(t00 - t01 - t10 + t11);
+    }
+    return make_float4(quad_sum(c0), quad_sum(ca), quad_sum(cb), quad_sum(cab));
+}
+
+// ---------------------------------------------------------------------------------------------
 // forward:  y[j][:] = c0 + ca*x[a_j][:] + cb*x[b_j][:] + cab*x[a_j][:]*x[b_j][:]
-// The CTA first turns the 16 weights of each of its neurons into the four coefficients
-// (softmax / pass-through / arg-max one-hot), then streams the rows.
+// Set-up (before the grid dependency is waited for): connection indices into registers.  Then the
+// row loads are issued and, while they are in flight, the four coefficients of each of the CTA's
+// neurons are computed into shared memory.
 // ---------------------------------------------------------------------------------------------
 template <int G, int U, bool VEC4>
 __global__ void __launch_bounds__(kThreads)
@@ -57,42 +112,57 @@ forward_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const
     constexpr int R = kThreads / G;  // neurons per pass
     constexpr int NB = R * U;        // neurons per CTA
     __shared__ float4 s_coef[NB];
-    __shared__ int64_t s_a[NB];
-    __shared__ int64_t s_b[NB];
 
     const int tid = threadIdx.x;
-    const int64_t n0 = (int64_t)blockIdx.x * NB;
-    for (int t = tid; t < NB; t += kThreads) {
-        const int64_t j = n0 + t;
-        if (j < n_out) {
-            const float4 c = neuron_coef(w + j * 16, w_mode);
-            s_coef[t] = c;
-            s_a[t] = __ldg(a + j) * batch;
-            s_b[t] = __ldg(b + j) * batch;
-            if (coef_out != nullptr && blockIdx.y == 0) coef_out[j] = c;
-        }
-    }
-    __syncthreads();
-
     const int lane = tid % G;
     const int r0 = tid / G;
+    const int64_t n0 = (int64_t)blockIdx.x * NB;
+
+    int64_t offa[U], offb[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t j = n0 + r0 + u * R;
+        if (j < n_out) {
+            offa[u] = __ldg(a + j) * batch;
+            offb[u] = __ldg(b + j) * batch;
+        }
+    }
+    // Only the connection indices (fixed at construction) are read before this point: the weights may have
+    // been written by the kernel just before this one (an optimizer step), the input certainly was.
+    grid_dependency_wait();
+    grid_dependents_launch();
+
+    bool first = true;
     for (int64_t slab = blockIdx.y; slab < nslabs; slab += gridDim.y) {
         const int64_t col = slab * G + lane;
-        if (col >= ncols) continue;
+        const bool incol = col < ncols;
         const int64_t off = col * Vec<VEC4>::width;
         V va[U], vb[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int r = r0 + u * R;
-            if (n0 + r < n_out) {
-                va[u] = ldv(reinterpret_cast<const V *>(x + s_a[r] + off));
-                vb[u] = ldv(reinterpret_cast<const V *>(x + s_b[r] + off));
+            if (incol && n0 + r0 + u * R < n_out) {
+                va[u] = ldv(reinterpret_cast<const V *>(x + offa[u] + off));
+                vb[u] = ldv(reinterpret_cast<const V *>(x + offb[u] + off));
             }
+        }
+        if (first) {
+            // coefficients of the CTA's neurons, computed while the row loads are in flight
+            for (int t = tid; t < NB * 4; t += kThreads) {  // NB*4 is a multiple of 32: whole warps iterate together
+                const int nl = t >> 2, q = t & 3;
+                const int64_t j = n0 + nl;
+                const float4 c = quad_coef(w + j * 16 + q * 4, j < n_out, q, w_mode);
+                if (q == 0 && j < n_out) {
+                    s_coef[nl] = c;
+                    if (coef_out != nullptr && blockIdx.y == 0) coef_out[j] = c;
+                }
+            }
+            __syncthreads();
+            first = false;
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int r = r0 + u * R;
-            if (n0 + r < n_out)
+            if (incol && n0 + r < n_out)
                 *reinterpret_cast<V *>(y + (n0 + r) * batch + off) = mixv(s_coef[r], va[u], vb[u]);
         }
     }
@@ -122,15 +192,34 @@ backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, co
                   int64_t n_out, int64_t batch, int64_t ncols) {
     using V = typename Vec<VEC4>::type;
     constexpr int R = kThreads / G;
+    // The 16 gates of the neuron are shared by P lanes of its group, K gates each.
+    constexpr int P = G < 16 ? G : 16;
+    constexpr int K = 16 / P;
     const int tid = threadIdx.x;
     const int lane = tid % G;
+    const int gl = lane & (P - 1);
     const int64_t j = (int64_t)blockIdx.x * R + tid / G;
     const bool active = j < n_out;
 
+    // ---- set-up: the connection indices are fixed at construction
+    int64_t ia = 0, ib = 0;
+    if (active) {
+        ia = __ldg(a + j) * batch;
+        ib = __ldg(b + j) * batch;
+    }
+    grid_dependency_wait();      // weights, x and grad_y may have been written by the kernels just before
+    grid_dependents_launch();
+
+    float prob[K];
+    if (w_mode == DL_W_LOGITS) {
+#pragma unroll
+        for (int q = 0; q < K; ++q) prob[q] = active ? __ldg(w + j * 16 + gl + q * P) : 0.f;
+    }
+
     float s0 = 0.f, sa = 0.f, sb = 0.f, sab = 0.f;
     if (active) {
-        const V *xa = reinterpret_cast<const V *>(x + __ldg(a + j) * batch);
-        const V *xb = reinterpret_cast<const V *>(x + __ldg(b + j) * batch);
+        const V *xa = reinterpret_cast<const V *>(x + ia);
+        const V *xb = reinterpret_cast<const V *>(x + ib);
         const V *g = reinterpret_cast<const V *>(gy + j * batch);
 #pragma unroll 4
         for (int64_t col = lane; col < ncols; col += G) acc4(s0, sa, sb, sab, ldv(xa + col), ldv(xb + col), ldv(g + col));
@@ -143,42 +232,32 @@ backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, co
         sab += __shfl_xor_sync(0xffffffffu, sab, off);
     }
 
-    // The 16 gates of the neuron are shared by P lanes, K gates each.
-    constexpr int P = G < 16 ? G : 16;
-    constexpr int K = 16 / P;
-    const int gl = lane & (P - 1);
     float out[K];
 #pragma unroll
     for (int q = 0; q < K; ++q) out[q] = gate_grad_from_sums(gl + q * P, s0, sa, sb, sab);
-
     if (w_mode == DL_W_LOGITS) {
-        float wv[K];
         float m = -INFINITY;
 #pragma unroll
-        for (int q = 0; q < K; ++q) {
-            wv[q] = active ? __ldg(w + j * 16 + gl + q * P) : 0.f;
-            m = fmaxf(m, wv[q]);
-        }
+        for (int q = 0; q < K; ++q) m = fmaxf(m, prob[q]);
 #pragma unroll
         for (int off = P / 2; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
         float s = 0.f;
 #pragma unroll
         for (int q = 0; q < K; ++q) {
-            wv[q] = expf(wv[q] - m);
-            s += wv[q];
+            prob[q] = expf(prob[q] - m);
+            s += prob[q];
         }
 #pragma unroll
         for (int off = P / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+#pragma unroll
+        for (int q = 0; q < K; ++q) prob[q] = prob[q] / s;
         float dot = 0.f;
 #pragma unroll
-        for (int q = 0; q < K; ++q) {
-            wv[q] = wv[q] / s;
-            dot += wv[q] * out[q];
-        }
+        for (int q = 0; q < K; ++q) dot += prob[q] * out[q];
 #pragma unroll
         for (int off = P / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
 #pragma unroll
-        for (int q = 0; q < K; ++q) out[q] = wv[q] * (out[q] - dot);
+        for (int q = 0; q < K; ++q) out[q] = prob[q] * (out[q] - dot);
     }
     if (active && lane < P) {
 #pragma unroll
@@ -187,7 +266,9 @@ backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, co
 }
 
 // ---------------------------------------------------------------------------------------------
-// backward_x: each input row gathers from its consumers through the plan (no atomics).
+// backward_x: each input row gathers from its consumers through the plan (no atomics).  The
+// row's first two plan entries and their coefficients are fetched during set-up; with the usual
+// fan-out of two nothing but the row loads is left once the previous kernel has finished.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void bx_acc(float4 &acc, float c1, float cab, float4 p, float4 g) {
     acc.x = fmaf(fmaf(cab, p.x, c1), g.x, acc.x);
@@ -213,16 +294,44 @@ backward_x_kernel(const float *__restrict__ x, const float4 *__restrict__ coef, 
     const int tid = threadIdx.x;
     const int lane = tid % G;
     const int64_t i = (int64_t)blockIdx.x * R + tid / G;
-    if (i >= n_in) return;
-    const int64_t e0 = __ldg(start + i), e1 = __ldg(start + i + 1);
+    const bool active = i < n_in;
+
+    // ---- set-up
+    int64_t e0 = 0, e1 = 0;
+    int2 p0 = make_int2(0, 0), p1 = make_int2(0, 0);
+    if (active) {
+        e0 = __ldg(start + i);
+        e1 = __ldg(start + i + 1);
+        if (e0 < e1) p0 = __ldg(plan + e0);
+        if (e0 + 1 < e1) p1 = __ldg(plan + e0 + 1);
+    }
+    grid_dependency_wait();      // coef (forward of this layer) and grad_y (previous kernel) are final from here on
+    grid_dependents_launch();
+    if (!active) return;
+    float4 c0 = make_float4(0.f, 0.f, 0.f, 0.f), c1 = c0;
+    if (e0 < e1) c0 = __ldg(coef + (p0.x >> 1));
+    if (e0 + 1 < e1) c1 = __ldg(coef + (p1.x >> 1));
+
     for (int64_t slab = blockIdx.y; slab < nslabs; slab += gridDim.y) {
         const int64_t col = slab * G + lane;
         if (col >= ncols) continue;
         const int64_t off = col * Vec<VEC4>::width;
         V acc;
         zero(acc);
+        if (e0 < e1) {
+            const V vp = ldv(reinterpret_cast<const V *>(x + (int64_t)p0.y * batch + off));
+            const V vg = ldv(reinterpret_cast<const V *>(gy + (int64_t)(p0.x >> 1) * batch + off));
+            if (e0 + 1 < e1) {
+                const V vp1 = ldv(reinterpret_cast<const V *>(x + (int64_t)p1.y * batch + off));
+                const V vg1 = ldv(reinterpret_cast<const V *>(gy + (int64_t)(p1.x >> 1) * batch + off));
+                bx_acc(acc, (p0.x & 1) ? c0.z : c0.y, c0.w, vp, vg);
+                bx_acc(acc, (p1.x & 1) ? c1.z : c1.y, c1.w, vp1, vg1);
+            } else {
+                bx_acc(acc, (p0.x & 1) ? c0.z : c0.y, c0.w, vp, vg);
+            }
+        }
 #pragma unroll 2
-        for (int64_t e = e0; e < e1; ++e) {
+        for (int64_t e = e0 + 2; e < e1; ++e) {
             const int2 p = __ldg(plan + e);
             const int64_t j = p.x >> 1;
             const float4 c = __ldg(coef + j);
@@ -257,7 +366,7 @@ build_plan_kernel(const int64_t *__restrict__ a, const int64_t *__restrict__ b, 
 static inline unsigned slab_grid(int64_t nslabs) { return (unsigned)(nslabs < 65535 ? nslabs : 65535); }
 
 template <bool VEC4>
-static int launch_forward(int G, const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode, float *y,
+static int launch_forward(bool overlap, int G, const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode, float *y,
                           float *coef, int64_t n_out, int64_t batch, int64_t ncols, cudaStream_t st) {
     constexpr int U = 4;
     const int64_t nslabs = ceil_div(ncols, G);
@@ -266,7 +375,7 @@ static int launch_forward(int G, const float *x, const int64_t *a, const int64_t
     float4 *c4 = reinterpret_cast<float4 *>(coef);
 #define DL_FWD(GG)                                                                                              \
     case GG:                                                                                                    \
-        forward_kernel<GG, U, VEC4><<<grid, kThreads, 0, st>>>(x, a, b, w, w_mode, y, c4, n_out, batch, ncols, nslabs); \
+        launch_dependent(overlap, forward_kernel<GG, U, VEC4>, grid, dim3(kThreads), 0, st, x, a, b, w, w_mode, y, c4, n_out, batch, ncols, nslabs); \
         break;
     switch (G) {
         DL_FWD(1) DL_FWD(2) DL_FWD(4) DL_FWD(8) DL_FWD(16) DL_FWD(32)
@@ -276,12 +385,12 @@ static int launch_forward(int G, const float *x, const int64_t *a, const int64_t
 }
 
 template <bool VEC4>
-static int launch_backward_w(int G, const float *x, const int64_t *a, const int64_t *b, const float *gy, const float *w,
+static int launch_backward_w(bool overlap, int G, const float *x, const int64_t *a, const int64_t *b, const float *gy, const float *w,
                              int w_mode, float *grad_w, int64_t n_out, int64_t batch, int64_t ncols, cudaStream_t st) {
     const unsigned grid = (unsigned)ceil_div(n_out, kThreads / G);
 #define DL_BW(GG)                                                                                          \
     case GG:                                                                                               \
-        backward_w_kernel<GG, VEC4><<<grid, kThreads, 0, st>>>(x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols); \
+        launch_dependent(overlap, backward_w_kernel<GG, VEC4>, dim3(grid), dim3(kThreads), 0, st, x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols); \
         break;
     switch (G) {
         DL_BW(1) DL_BW(2) DL_BW(4) DL_BW(8) DL_BW(16) DL_BW(32)
@@ -291,7 +400,7 @@ static int launch_backward_w(int G, const float *x, const int64_t *a, const int6
 }
 
 template <bool VEC4>
-static int launch_backward_x(int G, const float *x, const float *coef, const float *gy, const int64_t *start,
+static int launch_backward_x(bool overlap, int G, const float *x, const float *coef, const float *gy, const int64_t *start,
                              const int32_t *plan, float scale, float *gx, int64_t n_in, int64_t batch, int64_t ncols,
                              cudaStream_t st) {
     const int64_t nslabs = ceil_div(ncols, G);
@@ -300,7 +409,7 @@ static int launch_backward_x(int G, const float *x, const float *coef, const flo
     const int2 *p2 = reinterpret_cast<const int2 *>(plan);
 #define DL_BX(GG)                                                                                               \
     case GG:                                                                                                    \
-        backward_x_kernel<GG, VEC4><<<grid, kThreads, 0, st>>>(x, c4, gy, start, p2, scale, gx, n_in, batch, ncols, nslabs); \
+        launch_dependent(overlap, backward_x_kernel<GG, VEC4>, grid, dim3(kThreads), 0, st, x, c4, gy, start, p2, scale, gx, n_in, batch, ncols, nslabs); \
         break;
     switch (G) {
         DL_BX(1) DL_BX(2) DL_BX(4) DL_BX(8) DL_BX(16) DL_BX(32)
@@ -316,7 +425,7 @@ using namespace dl;
 static const int64_t kMaxRows = (int64_t)1 << 30;  // plan entries hold 2*j+slot in an int32
 
 extern "C" DL_API int dl_forward_f32(const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode, float *y,
-                              float *coef, int64_t n_in, int64_t n_out, int64_t batch, void *stream) {
+                              float *coef, int64_t n_in, int64_t n_out, int64_t batch, int flags, void *stream) {
     DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_forward_f32: negative size");
     DL_REQUIRE(w_mode >= DL_W_LOGITS && w_mode <= DL_W_ARGMAX, DL_ERR_INVALID_ARG, "dl_forward_f32: unknown w_mode %d", w_mode);
     if (n_out == 0 || batch == 0) return DL_OK;
@@ -326,12 +435,13 @@ extern "C" DL_API int dl_forward_f32(const float *x, const int64_t *a, const int
     const bool vec = batch % 4 == 0 && aligned_to(x, 16) && aligned_to(y, 16);
     const int64_t ncols = vec ? batch / 4 : batch;
     const int G = pow2_at_least(ncols, 32);
-    return vec ? launch_forward<true>(G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream))
-               : launch_forward<false>(G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream));
+    const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
+    return vec ? launch_forward<true>(overlap, G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream))
+               : launch_forward<false>(overlap, G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream));
 }
 
 extern "C" DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
-                                 int w_mode, float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, void *stream) {
+                                 int w_mode, float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int flags, void *stream) {
     DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_backward_w_f32: negative size");
     DL_REQUIRE(w_mode == DL_W_LOGITS || w_mode == DL_W_PROBS, DL_ERR_INVALID_ARG,
                "dl_backward_w_f32: w_mode must be DL_W_LOGITS or DL_W_PROBS, got %d", w_mode);
@@ -342,13 +452,14 @@ extern "C" DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const 
     const bool vec = batch % 4 == 0 && aligned_to(x, 16) && aligned_to(grad_y, 16);
     const int64_t ncols = vec ? batch / 4 : batch;
     const int G = pow2_at_least(ceil_div(ncols, 4), 32);
-    return vec ? launch_backward_w<true>(G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, as_stream(stream))
-               : launch_backward_w<false>(G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, as_stream(stream));
+    const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
+    return vec ? launch_backward_w<true>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, as_stream(stream))
+               : launch_backward_w<false>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, as_stream(stream));
 }
 
 extern "C" DL_API int dl_backward_x_f32(const float *x, const float *coef, const float *grad_y, const int64_t *start,
                                  const int32_t *plan, float grad_scale, float *grad_x, int64_t n_in, int64_t n_out,
-                                 int64_t batch, void *stream) {
+                                 int64_t batch, int flags, void *stream) {
     DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_backward_x_f32: negative size");
     DL_REQUIRE(n_out < kMaxRows && n_in < 2 * kMaxRows, DL_ERR_TOO_LARGE, "dl_backward_x_f32: more than 2^30 neurons");
     if (n_in == 0 || batch == 0) return DL_OK;
@@ -359,8 +470,9 @@ extern "C" DL_API int dl_backward_x_f32(const float *x, const float *coef, const
     const bool vec = batch % 4 == 0 && aligned_to(x, 16) && aligned_to(grad_y, 16) && aligned_to(grad_x, 16);
     const int64_t ncols = vec ? batch / 4 : batch;
     const int G = pow2_at_least(ncols, 32);
-    return vec ? launch_backward_x<true>(G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, as_stream(stream))
-               : launch_backward_x<false>(G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, as_stream(stream));
+    const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
+    return vec ? launch_backward_x<true>(overlap, G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, as_stream(stream))
+               : launch_backward_x<false>(overlap, G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, as_stream(stream));
 }
 
 extern "C" DL_API int dl_build_backward_plan(const int64_t *a, const int64_t *b, const int64_t *start, const int64_t *list,

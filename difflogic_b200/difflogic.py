@@ -97,6 +97,9 @@ class LogicLayer(torch.nn.Module):
         self.given_x_indices_of_y_start, self.given_x_indices_of_y = ops.inverse_index(a, b, self.in_dim)
         if a.is_cuda:
             self._plan = ops.build_backward_plan(a, b, self.given_x_indices_of_y_start, self.given_x_indices_of_y)
+            # the layer's kernels may read these index tensors ahead of the kernel that precedes them in the
+            # stream (DL_LAUNCH_OVERLAP_SETUP), so they must be final before any such launch is queued
+            torch.cuda.current_stream(a.device).synchronize()
         else:
             self._plan = None
 
@@ -164,7 +167,7 @@ class LogicLayer(torch.nn.Module):
                                          float(self.grad_factor))
         else:
             with torch.no_grad():
-                y, _ = ops.logic_forward(x, a, b, self.weights, ops.W_ARGMAX)
+                y, _ = ops.logic_forward(x, a, b, self.weights, ops.W_ARGMAX, overlap=True)
         return y.transpose(0, 1)
 
     def forward_cuda_eval(self, x: PackBitsTensor):
@@ -235,7 +238,7 @@ class LogicLayerFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weights, a, b, start, plan, grad_factor):
-        y, coef = ops.logic_forward(x, a, b, weights, ops.W_LOGITS, want_coef=True)
+        y, coef = ops.logic_forward(x, a, b, weights, ops.W_LOGITS, want_coef=True, overlap=True)
         ctx.save_for_backward(x, weights, a, b, start, plan, coef)
         ctx.grad_factor = grad_factor
         return y
@@ -246,9 +249,9 @@ class LogicLayerFunction(torch.autograd.Function):
         grad_y = grad_y.contiguous()
         grad_x = grad_w = None
         if ctx.needs_input_grad[0]:
-            grad_x = ops.logic_backward_x(x, coef, grad_y, start, plan, ctx.grad_factor)
+            grad_x = ops.logic_backward_x(x, coef, grad_y, start, plan, ctx.grad_factor, overlap=True)
         if ctx.needs_input_grad[1]:
-            grad_w = ops.logic_backward_w(x, a, b, grad_y, weights, ops.W_LOGITS)
+            grad_w = ops.logic_backward_w(x, a, b, grad_y, weights, ops.W_LOGITS, overlap=True)
         return grad_x, grad_w, None, None, None, None, None
 
 

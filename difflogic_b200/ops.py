@@ -39,8 +39,11 @@ def _index(t, name, n=None):
 # training
 # ------------------------------------------------------------------------------------------------
 
-def logic_forward(x, a, b, w, w_mode=W_LOGITS, want_coef=False):
-    """y[j,:] = sum_i p[j,i] gate_i(x[a_j,:], x[b_j,:]);  returns (y [n_out,batch], coef or None)."""
+def logic_forward(x, a, b, w, w_mode=W_LOGITS, want_coef=False, overlap=False):
+    """y[j,:] = sum_i p[j,i] gate_i(x[a_j,:], x[b_j,:]);  returns (y [n_out,batch], coef or None).
+
+    overlap=True lets the kernel read `a`, `b` while the previous kernel in the stream is still running; pass
+    it only when those index tensors were complete before that kernel was launched (see DL_LAUNCH_OVERLAP_SETUP)."""
     _f32_matrix(x, "x")
     _f32_matrix(w, "w")
     n_in, batch = x.shape
@@ -52,7 +55,7 @@ def logic_forward(x, a, b, w, w_mode=W_LOGITS, want_coef=False):
     coef = torch.empty((n_out, 4), dtype=torch.float32, device=x.device) if want_coef else None
     with torch.cuda.device(x.device):
         N.check(N.lib().dl_forward_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), w.data_ptr(), w_mode, y.data_ptr(),
-                                       N.ptr(coef), n_in, n_out, batch, N.stream_of(x)))
+                                       N.ptr(coef), n_in, n_out, batch, int(overlap), N.stream_of(x)))
     return y, coef
 
 
@@ -65,7 +68,7 @@ def logic_coefs(w, w_mode=W_LOGITS):
     return coef
 
 
-def logic_backward_w(x, a, b, grad_y, w=None, w_mode=W_PROBS, out=None):
+def logic_backward_w(x, a, b, grad_y, w=None, w_mode=W_PROBS, out=None, overlap=False):
     """[n_out,16] gradient: w_mode=W_PROBS w.r.t. the mixing weights, W_LOGITS w.r.t. the raw
     parameters `w` (softmax backward applied in the kernel)."""
     _f32_matrix(x, "x")
@@ -86,7 +89,7 @@ def logic_backward_w(x, a, b, grad_y, w=None, w_mode=W_PROBS, out=None):
         _need(tuple(out.shape) == (n_out, 16), "out must be [n_out, 16]")
     with torch.cuda.device(x.device):
         N.check(N.lib().dl_backward_w_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), grad_y.data_ptr(), N.ptr(w), w_mode,
-                                          out.data_ptr(), n_in, n_out, batch, N.stream_of(x)))
+                                          out.data_ptr(), n_in, n_out, batch, int(overlap), N.stream_of(x)))
     return out
 
 
@@ -116,7 +119,7 @@ def build_backward_plan(a, b, start, lst):
     return plan
 
 
-def logic_backward_x(x, coef, grad_y, start, plan, grad_scale=1.0):
+def logic_backward_x(x, coef, grad_y, start, plan, grad_scale=1.0, overlap=False):
     _f32_matrix(x, "x")
     _f32_matrix(grad_y, "grad_y")
     _f32_matrix(coef, "coef")
@@ -132,7 +135,7 @@ def logic_backward_x(x, coef, grad_y, start, plan, grad_scale=1.0):
     with torch.cuda.device(x.device):
         N.check(N.lib().dl_backward_x_f32(x.data_ptr(), coef.data_ptr(), grad_y.data_ptr(), start.data_ptr(),
                                           plan.data_ptr(), float(grad_scale), gx.data_ptr(), n_in, n_out, batch,
-                                          N.stream_of(x)))
+                                          int(overlap), N.stream_of(x)))
     return gx
 
 

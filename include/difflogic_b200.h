@@ -49,6 +49,14 @@ enum {
     DL_W_ARGMAX = 2  /* raw parameters; only the arg-max gate is used (first max on ties)     */
 };
 
+/* Launch flags of the training entry points.
+ * DL_LAUNCH_OVERLAP_SETUP: launch with programmatic stream serialisation, so that the kernel may
+ * read its connection indices (a, b, start, plan) while the previous kernel in the stream is still
+ * running.  The caller promises that those index arrays were final before the previous kernel in
+ * the stream was launched (they are fixed when a layer is built).  All other operands -- x, grad_y,
+ * w, coef -- are read only after the previous kernel has completed, as under a plain launch. */
+enum { DL_LAUNCH_PLAIN = 0, DL_LAUNCH_OVERLAP_SETUP = 1 };
+
 DL_API int dl_version(void);
 DL_API const char *dl_last_error_string(void);
 
@@ -72,7 +80,7 @@ DL_API int dl_async_error(void);
  * y = c0 + ca*A + cb*B + cab*A*B; dl_backward_x_f32 consumes it.
  * ---------------------------------------------------------------------------------------- */
 DL_API int dl_forward_f32(const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode,
-                   float *y, float *coef, int64_t n_in, int64_t n_out, int64_t batch, void *stream);
+                   float *y, float *coef, int64_t n_in, int64_t n_out, int64_t batch, int flags, void *stream);
 
 /* The coefficient table alone (w [n_out][16] -> coef [n_out][4]); used when a caller hands
  * dl_backward_x_f32 weights that did not pass through dl_forward_f32.  No counterpart in the
@@ -91,7 +99,7 @@ DL_API int dl_coefs_f32(const float *w, int w_mode, float *coef, int64_t n_out, 
  * ---------------------------------------------------------------------------------------- */
 DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y,
                       const float *w, int w_mode, float *grad_w,
-                      int64_t n_in, int64_t n_out, int64_t batch, void *stream);
+                      int64_t n_in, int64_t n_out, int64_t batch, int flags, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * backward_x.
@@ -110,7 +118,7 @@ DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const int64_t *b,
  * ---------------------------------------------------------------------------------------- */
 DL_API int dl_backward_x_f32(const float *x, const float *coef, const float *grad_y, const int64_t *start,
                       const int32_t *plan, float grad_scale, float *grad_x,
-                      int64_t n_in, int64_t n_out, int64_t batch, void *stream);
+                      int64_t n_in, int64_t n_out, int64_t batch, int flags, void *stream);
 
 /* Builds `plan` [2*n_out][2] int32 from the reference's inverse index: start [n_in+1] and
  * list [2*n_out] (LogicLayer.given_x_indices_of_y_start / given_x_indices_of_y,

@@ -42,15 +42,15 @@ def test_argument_errors_are_reported_before_any_launch(lib):
     assert lib.dl_groupbitsum(null, null, 10, 4, 0, 3, 64, null) == _native.DL_ERR_NOT_DIVISIBLE
     with pytest.raises(ValueError, match="divisible"):
         _native.check(lib.dl_groupbitsum(null, null, 10, 4, 0, 3, 64, null))
-    assert lib.dl_forward_f32(null, null, null, null, 0, null, null, 4, 4, 4, null) == _native.DL_ERR_INVALID_ARG
-    assert lib.dl_forward_f32(null, null, null, null, 9, null, null, 4, 4, 4, null) == _native.DL_ERR_INVALID_ARG
-    assert lib.dl_forward_f32(null, null, null, null, 0, null, null, -1, 4, 4, null) == _native.DL_ERR_INVALID_ARG
+    assert lib.dl_forward_f32(null, null, null, null, 0, null, null, 4, 4, 4, 0, null) == _native.DL_ERR_INVALID_ARG
+    assert lib.dl_forward_f32(null, null, null, null, 9, null, null, 4, 4, 4, 0, null) == _native.DL_ERR_INVALID_ARG
+    assert lib.dl_forward_f32(null, null, null, null, 0, null, null, -1, 4, 4, 0, null) == _native.DL_ERR_INVALID_ARG
     with pytest.raises(RuntimeError):
-        _native.check(lib.dl_backward_x_f32(null, null, null, null, null, 1.0, null, 4, 4, 4, null))
-    assert lib.dl_backward_x_f32(null, null, null, null, null, 1.0, null, 4, 1 << 31, 4, null) == _native.DL_ERR_TOO_LARGE
+        _native.check(lib.dl_backward_x_f32(null, null, null, null, null, 1.0, null, 4, 4, 4, 0, null))
+    assert lib.dl_backward_x_f32(null, null, null, null, null, 1.0, null, 4, 1 << 31, 4, 0, null) == _native.DL_ERR_TOO_LARGE
     assert lib.dl_groupsum_f32(null, null, null, 10, 4, 3, 1.0, null) == _native.DL_ERR_NOT_DIVISIBLE
     # empty problems are fine and launch nothing
-    assert lib.dl_forward_f32(null, null, null, null, 0, null, null, 4, 0, 4, null) == _native.DL_OK
+    assert lib.dl_forward_f32(null, null, null, null, 0, null, null, 4, 0, 4, 0, null) == _native.DL_OK
     assert lib.dl_eval_packed(null, null, null, null, null, 4, 4, 0, 64, null) == _native.DL_OK
     assert lib.dl_groupsum_workspace_bytes(16000, 128, 10) > 4096
 
