@@ -208,7 +208,11 @@ def bench_train(args, rank, world):
     dev = torch.device("cuda")
     model = build_gpu_model(TRAIN_DIMS, TRAIN_K, TRAIN_TAU, seed=0)   # same seed: identical replicas
     model.train()
-    opt = torch.optim.Adam(model.parameters(), lr=TRAIN_LR, capturable=True, fused=True)
+    if args.optimizer == "torch":
+        opt = torch.optim.Adam(model.parameters(), lr=TRAIN_LR, capturable=True, fused=True)
+    else:
+        from difflogic_b200.optim import FlatAdam
+        opt = FlatAdam(model.parameters(), lr=TRAIN_LR)
     group = dist.group.WORLD if world > 1 else None
     step = TrainStep(model, opt, torch.nn.CrossEntropyLoss(), process_group=group, world_size=world)
 
@@ -506,6 +510,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-packed", action="store_true")
+    ap.add_argument("--optimizer", default="flat", choices=["flat", "torch"],
+                    help="flat: difflogic_b200.optim.FlatAdam (one kernel); torch: torch.optim.Adam(capturable, fused)")
     ap.add_argument("--skip-cpu", action="store_true")
     args = ap.parse_args()
 

@@ -38,8 +38,12 @@ int launch_status(const char *what) {
 
 __global__ void __launch_bounds__(kThreads) coefs_kernel(const float *__restrict__ w, int w_mode,
                                                          float4 *__restrict__ coef, int64_t n_out) {
-    const int64_t j = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    if (j < n_out) coef[j] = neuron_coef(w + j * 16, w_mode);
+    // four lanes per neuron, the same arithmetic (and rounding) as inside the forward kernel
+    const int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    const int64_t j = t >> 2;
+    const int q = (int)(t & 3);
+    const float4 c = quad_coef(w + j * 16 + q * 4, j < n_out, q, w_mode);
+    if (q == 0 && j < n_out) coef[j] = c;
 }
 
 __global__ void __launch_bounds__(kThreads) argmax_kernel(const float *__restrict__ w, uint8_t *__restrict__ gate,
@@ -60,7 +64,7 @@ extern "C" DL_API int dl_coefs_f32(const float *w, int w_mode, float *coef, int6
     DL_REQUIRE(w_mode >= DL_W_LOGITS && w_mode <= DL_W_ARGMAX, DL_ERR_INVALID_ARG, "dl_coefs_f32: unknown w_mode %d", w_mode);
     DL_REQUIRE(dl::aligned_to(coef, 16), DL_ERR_INVALID_ARG, "dl_coefs_f32: coef must be 16-byte aligned");
     if (n_out == 0) return DL_OK;
-    dl::coefs_kernel<<<(unsigned)dl::ceil_div(n_out, dl::kThreads), dl::kThreads, 0, dl::as_stream(stream)>>>(
+    dl::coefs_kernel<<<(unsigned)dl::ceil_div(4 * n_out, dl::kThreads), dl::kThreads, 0, dl::as_stream(stream)>>>(
         w, w_mode, reinterpret_cast<float4 *>(coef), n_out);
     return dl::launch_status("dl_coefs_f32");
 }

@@ -11,20 +11,6 @@
 
 namespace dl {
 
-// {c0, ca, cb, cab} of  sum_i p[i] * gate_i(A,B) = c0 + ca A + cb B + cab A B.
-__device__ __forceinline__ float4 coef_from_mix(const float (&p)[16]) {
-    float c0 = 0.f, ca = 0.f, cb = 0.f, cab = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const int t00 = (i >> 3) & 1, t01 = (i >> 2) & 1, t10 = (i >> 1) & 1, t11 = i & 1;
-        c0 += p[i] * (float)t00;
-        ca += p[i] * (float)(t10 - t00);
-        cb += p[i] * (float)(t01 - t00);
-        cab += p[i] * (float)(t00 - t01 - t10 + t11);
-    }
-    return make_float4(c0, ca, cb, cab);
-}
-
 __device__ __forceinline__ int first_argmax16(const float *__restrict__ w) {
     int best = 0;
     float m = __ldg(w);
@@ -36,29 +22,58 @@ __device__ __forceinline__ int first_argmax16(const float *__restrict__ w) {
     return best;
 }
 
-// Coefficients of one neuron from its 16 weights, read as `w_mode` says.
-__device__ __forceinline__ float4 neuron_coef(const float *__restrict__ w, int w_mode) {
-    float p[16];
+// ---------------------------------------------------------------------------------------------
+// Coefficients of one neuron computed by four adjacent lanes (a "quad"), lane q holding gates
+// 4q .. 4q+3: softmax / pass-through / arg-max one-hot over the 16 weights, then the sum over
+// the gates of p_i times the gate's multilinear coefficients.  All 32 lanes of the warp call it.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v;
+}
+
+__device__ __forceinline__ float4 quad_coef(const float *__restrict__ wq, bool live, int q, int w_mode) {
+    float p[4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) p[i] = __ldg(w + i);
+    for (int i = 0; i < 4; ++i) p[i] = live ? __ldg(wq + i) : 0.f;
     if (w_mode == DL_W_LOGITS) {
-        float m = p[0];
-#pragma unroll
-        for (int i = 1; i < 16; ++i) m = fmaxf(m, p[i]);
+        float m = fmaxf(fmaxf(p[0], p[1]), fmaxf(p[2], p[3]));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
         float s = 0.f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { p[i] = expf(p[i] - m); s += p[i]; }
+        for (int i = 0; i < 4; ++i) { p[i] = expf(p[i] - m); s += p[i]; }
+        s = quad_sum(s);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) p[i] = p[i] / s;
+        for (int i = 0; i < 4; ++i) p[i] = p[i] / s;
     } else if (w_mode == DL_W_ARGMAX) {
         int best = 0;
         float m = p[0];
 #pragma unroll
-        for (int i = 1; i < 16; ++i) if (p[i] > m) { m = p[i]; best = i; }
+        for (int i = 1; i < 4; ++i) if (p[i] > m) { m = p[i]; best = i; }
+        int gbest = 4 * q + best;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) p[i] = (i == best) ? 1.f : 0.f;
+        for (int off = 1; off <= 2; off <<= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, m, off);
+            const int og = __shfl_xor_sync(0xffffffffu, gbest, off);
+            if (om > m || (om == m && og < gbest)) { m = om; gbest = og; }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = (4 * q + i == gbest) ? 1.f : 0.f;
     }
-    return coef_from_mix(p);
+    // gate 4q+i has truth table t00 = q>>1, t01 = q&1, t10 = i>>1, t11 = i&1
+    const int t00 = q >> 1, t01 = q & 1;
+    float c0 = 0.f, ca = 0.f, cb = 0.f, cab = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t10 = i >> 1, t11 = i & 1;
+        c0 += p[i] * (float)t00;
+        ca += p[i] * (float)(t10 - t00);
+        cb += p[i] * (float)(t01 - t00);
+        cab += p[i] * (float)(t00 - t01 - t10 + t11);
+    }
+    return make_float4(quad_sum(c0), quad_sum(ca), quad_sum(cb), quad_sum(cab));
 }
 
 // dL/dp_i from the four batch sums S = {sum g, sum A g, sum B g, sum A B g}.

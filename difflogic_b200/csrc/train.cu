@@ -44,67 +44,13 @@ __device__ __forceinline__ float mixv(const float4 c, const float a, const float
 }
 
 // ---------------------------------------------------------------------------------------------
-// Coefficients of one neuron computed by four adjacent lanes (a "quad"), lane q holding gates
-// 4q .. 4q+3: softmax / pass-through / arg-max one-hot over the 16 weights, then the sum over
-// the gates of p_i times the gate's multilinear coefficients.  All 32 lanes of the warp call it.
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ float quad_sum(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    return v;
-}
-
-__device__ __forceinline__ float4 quad_coef(const float *__restrict__ wq, bool live, int q, int w_mode) {
-    float p[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) p[i] = live ? __ldg(wq + i) : 0.f;
-    if (w_mode == DL_W_LOGITS) {
-        float m = fmaxf(fmaxf(p[0], p[1]), fmaxf(p[2], p[3]));
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-        float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { p[i] = expf(p[i] - m); s += p[i]; }
-        s = quad_sum(s);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) p[i] = p[i] / s;
-    } else if (w_mode == DL_W_ARGMAX) {
-        int best = 0;
-        float m = p[0];
-#pragma unroll
-        for (int i = 1; i < 4; ++i) if (p[i] > m) { m = p[i]; best = i; }
-        int gbest = 4 * q + best;
-#pragma unroll
-        for (int off = 1; off <= 2; off <<= 1) {
-            const float om = __shfl_xor_sync(0xffffffffu, m, off);
-            const int og = __shfl_xor_sync(0xffffffffu, gbest, off);
-            if (om > m || (om == m && og < gbest)) { m = om; gbest = og; }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) p[i] = (4 * q + i == gbest) ? 1.f : 0.f;
-    }
-    // gate 4q+i has truth table t00 = q>>1, t01 = q&1, t10 = i>>1, t11 = i&1
-    const int t00 = q >> 1, t01 = q & 1;
-    float c0 = 0.f, ca = 0.f, cb = 0.f, cab = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int t10 = i >> 1, t11 = i & 1;
-        c0 += p[i] * (float)t00;
-        ca += p[i] * (float)(t10 - t00);
-        cb += p[i] * (float)(t01 - t00);
-        cab += p[i] * (float)(t00 - t01 - t10 + t11);
-    }
-    return make_float4(quad_sum(c0), quad_sum(ca), quad_sum(cb), quad_sum(cab));
-}
-
-// ---------------------------------------------------------------------------------------------
 // forward:  y[j][:] = c0 + ca*x[a_j][:] + cb*x[b_j][:] + cab*x[a_j][:]*x[b_j][:]
 // Set-up (before the grid dependency is waited for): connection indices into registers.  Then the
 // row loads are issued and, while they are in flight, the four coefficients of each of the CTA's
 // neurons are computed into shared memory.
 // ---------------------------------------------------------------------------------------------
 template <int G, int U, bool VEC4>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 forward_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
                const float *__restrict__ w, int w_mode, float *__restrict__ y, float4 *__restrict__ coef_out,
                int64_t n_out, int64_t batch, int64_t ncols, int64_t nslabs) {
@@ -291,12 +237,13 @@ backward_x_kernel(const float *__restrict__ x, const float4 *__restrict__ coef, 
                   float *__restrict__ gx, int64_t n_in, int64_t batch, int64_t ncols, int64_t nslabs) {
     using V = typename Vec<VEC4>::type;
     constexpr int R = kThreads / G;
+    constexpr int C = 4;  // columns per lane within a slab: lane, lane+G, lane+2G, lane+3G
     const int tid = threadIdx.x;
     const int lane = tid % G;
     const int64_t i = (int64_t)blockIdx.x * R + tid / G;
     const bool active = i < n_in;
 
-    // ---- set-up
+    // ---- set-up: the gather plan is fixed at construction
     int64_t e0 = 0, e1 = 0;
     int2 p0 = make_int2(0, 0), p1 = make_int2(0, 0);
     if (active) {
@@ -311,35 +258,39 @@ backward_x_kernel(const float *__restrict__ x, const float4 *__restrict__ coef, 
     float4 c0 = make_float4(0.f, 0.f, 0.f, 0.f), c1 = c0;
     if (e0 < e1) c0 = __ldg(coef + (p0.x >> 1));
     if (e0 + 1 < e1) c1 = __ldg(coef + (p1.x >> 1));
+    const float k0 = (p0.x & 1) ? c0.z : c0.y, k1 = (p1.x & 1) ? c1.z : c1.y;
+    const float *xp0 = x + (int64_t)p0.y * batch, *gp0 = gy + (int64_t)(p0.x >> 1) * batch;
+    const float *xp1 = x + (int64_t)p1.y * batch, *gp1 = gy + (int64_t)(p1.x >> 1) * batch;
+    const bool has0 = e0 < e1, has1 = e0 + 1 < e1;
 
     for (int64_t slab = blockIdx.y; slab < nslabs; slab += gridDim.y) {
-        const int64_t col = slab * G + lane;
-        if (col >= ncols) continue;
-        const int64_t off = col * Vec<VEC4>::width;
-        V acc;
-        zero(acc);
-        if (e0 < e1) {
-            const V vp = ldv(reinterpret_cast<const V *>(x + (int64_t)p0.y * batch + off));
-            const V vg = ldv(reinterpret_cast<const V *>(gy + (int64_t)(p0.x >> 1) * batch + off));
-            if (e0 + 1 < e1) {
-                const V vp1 = ldv(reinterpret_cast<const V *>(x + (int64_t)p1.y * batch + off));
-                const V vg1 = ldv(reinterpret_cast<const V *>(gy + (int64_t)(p1.x >> 1) * batch + off));
-                bx_acc(acc, (p0.x & 1) ? c0.z : c0.y, c0.w, vp, vg);
-                bx_acc(acc, (p1.x & 1) ? c1.z : c1.y, c1.w, vp1, vg1);
-            } else {
-                bx_acc(acc, (p0.x & 1) ? c0.z : c0.y, c0.w, vp, vg);
-            }
-        }
 #pragma unroll 2
-        for (int64_t e = e0 + 2; e < e1; ++e) {
-            const int2 p = __ldg(plan + e);
-            const int64_t j = p.x >> 1;
-            const float4 c = __ldg(coef + j);
-            const V vp = ldv(reinterpret_cast<const V *>(x + (int64_t)p.y * batch + off));
-            const V vg = ldv(reinterpret_cast<const V *>(gy + j * batch + off));
-            bx_acc(acc, (p.x & 1) ? c.z : c.y, c.w, vp, vg);
+        for (int cc = 0; cc < C; ++cc) {
+            const int64_t col = slab * (G * C) + cc * G + lane;
+            if (col >= ncols) break;
+            const int64_t off = col * Vec<VEC4>::width;
+            V acc;
+            zero(acc);
+            if (has1) {
+                const V vp = ldv(reinterpret_cast<const V *>(xp0 + off));
+                const V vg = ldv(reinterpret_cast<const V *>(gp0 + off));
+                const V vp1 = ldv(reinterpret_cast<const V *>(xp1 + off));
+                const V vg1 = ldv(reinterpret_cast<const V *>(gp1 + off));
+                bx_acc(acc, k0, c0.w, vp, vg);
+                bx_acc(acc, k1, c1.w, vp1, vg1);
+            } else if (has0) {
+                bx_acc(acc, k0, c0.w, ldv(reinterpret_cast<const V *>(xp0 + off)), ldv(reinterpret_cast<const V *>(gp0 + off)));
+            }
+            for (int64_t e = e0 + 2; e < e1; ++e) {
+                const int2 p = __ldg(plan + e);
+                const int64_t j = p.x >> 1;
+                const float4 c = __ldg(coef + j);
+                const V vp = ldv(reinterpret_cast<const V *>(x + (int64_t)p.y * batch + off));
+                const V vg = ldv(reinterpret_cast<const V *>(gy + j * batch + off));
+                bx_acc(acc, (p.x & 1) ? c.z : c.y, c.w, vp, vg);
+            }
+            *reinterpret_cast<V *>(gx + i * batch + off) = scaled(acc, scale);
         }
-        *reinterpret_cast<V *>(gx + i * batch + off) = scaled(acc, scale);
     }
 }
 
@@ -403,7 +354,7 @@ template <bool VEC4>
 static int launch_backward_x(bool overlap, int G, const float *x, const float *coef, const float *gy, const int64_t *start,
                              const int32_t *plan, float scale, float *gx, int64_t n_in, int64_t batch, int64_t ncols,
                              cudaStream_t st) {
-    const int64_t nslabs = ceil_div(ncols, G);
+    const int64_t nslabs = ceil_div(ncols, G * 4);
     const dim3 grid((unsigned)ceil_div(n_in, kThreads / G), slab_grid(nslabs));
     const float4 *c4 = reinterpret_cast<const float4 *>(coef);
     const int2 *p2 = reinterpret_cast<const int2 *>(plan);
@@ -469,7 +420,7 @@ extern "C" DL_API int dl_backward_x_f32(const float *x, const float *coef, const
                "dl_backward_x_f32: coef must be 16-byte and plan 8-byte aligned");
     const bool vec = batch % 4 == 0 && aligned_to(x, 16) && aligned_to(grad_y, 16) && aligned_to(grad_x, 16);
     const int64_t ncols = vec ? batch / 4 : batch;
-    const int G = pow2_at_least(ncols, 32);
+    const int G = pow2_at_least(ceil_div(ncols, 4), 32);
     const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
     return vec ? launch_backward_x<true>(overlap, G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, as_stream(stream))
                : launch_backward_x<false>(overlap, G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, as_stream(stream));

@@ -164,7 +164,7 @@ class LogicLayer(torch.nn.Module):
         a, b = self.indices
         if self.training:
             y = LogicLayerFunction.apply(x, self.weights, a, b, self.given_x_indices_of_y_start, self._plan,
-                                         float(self.grad_factor))
+                                         float(self.grad_factor), getattr(self.weights, '_dl_grad_out', None))
         else:
             with torch.no_grad():
                 y, _ = ops.logic_forward(x, a, b, self.weights, ops.W_ARGMAX, overlap=True)
@@ -237,10 +237,11 @@ class LogicLayerFunction(torch.autograd.Function):
     in front of it and the GradFactor node before the layer."""
 
     @staticmethod
-    def forward(ctx, x, weights, a, b, start, plan, grad_factor):
+    def forward(ctx, x, weights, a, b, start, plan, grad_factor, grad_out=None):
         y, coef = ops.logic_forward(x, a, b, weights, ops.W_LOGITS, want_coef=True, overlap=True)
         ctx.save_for_backward(x, weights, a, b, start, plan, coef)
         ctx.grad_factor = grad_factor
+        ctx.grad_out = grad_out  # optional [out_dim, 16] buffer (a slice of a flat gradient bucket) for backward_w
         return y
 
     @staticmethod
@@ -251,8 +252,8 @@ class LogicLayerFunction(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             grad_x = ops.logic_backward_x(x, coef, grad_y, start, plan, ctx.grad_factor, overlap=True)
         if ctx.needs_input_grad[1]:
-            grad_w = ops.logic_backward_w(x, a, b, grad_y, weights, ops.W_LOGITS, overlap=True)
-        return grad_x, grad_w, None, None, None, None, None
+            grad_w = ops.logic_backward_w(x, a, b, grad_y, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True)
+        return grad_x, grad_w, None, None, None, None, None, None
 
 
 class LogicLayerCudaFunction(torch.autograd.Function):

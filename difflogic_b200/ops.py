@@ -239,12 +239,22 @@ _workspaces = {}
 
 
 def _groupsum_workspace(device, stream, nbytes):
-    """Zero-initialised scratch for dl_groupsum_f32, one per (device, stream), grown on demand.
-    The kernel leaves the counters at zero, so the buffer is cleared only when it is created."""
-    key = (device, stream)
+    """Zero-initialised scratch for dl_groupsum_f32, grown on demand.  The kernel leaves the counters at
+    zero, so a buffer is cleared only when it is created.  Eager calls use one buffer per (device, stream).
+    Calls made while a CUDA graph is being captured share one buffer per device that is created by the first
+    eager call on that device (warm-up steps), so that a captured step contains no allocation and no memset;
+    graphs replayed concurrently on different streams must therefore not both contain a GroupSum."""
+    want = max(nbytes, 1 << 20)
+    graph_key = (device, "graph")
+    capturing = torch.cuda.is_current_stream_capturing()
+    if not capturing:
+        gws = _workspaces.get(graph_key)
+        if gws is None or gws.numel() < want:
+            _workspaces[graph_key] = torch.zeros(want, dtype=torch.uint8, device=device)
+    key = graph_key if capturing else (device, stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = torch.zeros(want, dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
 

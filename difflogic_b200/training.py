@@ -49,8 +49,11 @@ class TrainStep:
         ready = torch.cuda.Event()
         ready.record(main)
         self._comm_stream.wait_event(ready)
+        # with FlatAdam the gradient lives in the optimizer's flat bucket (backward_w wrote it there)
+        view = getattr(self.optimizer, "grad_view", None)
+        grad = view(param) if view is not None else param.grad
         with torch.cuda.stream(self._comm_stream):
-            dist.all_reduce(param.grad, op=dist.ReduceOp.AVG, group=self.group)
+            dist.all_reduce(grad, op=dist.ReduceOp.AVG, group=self.group)
 
     def _join_comm(self):
         if self._comm_stream is not None:

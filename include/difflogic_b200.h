@@ -180,6 +180,18 @@ DL_API int dl_groupsum_f32(const float *x, float *out, void *workspace, int64_t 
 DL_API int dl_groupsum_backward_f32(const float *grad_out, float *grad_x, int64_t n, int64_t batch, int64_t k,
                              float tau, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Adam step over a flat fp32 parameter vector (all layers' gate weights in one buffer).
+ * Replaces torch.optim.Adam(model.parameters(), lr).step() of the reference's training loop
+ * (experiments/main.py:169,179), same update rule (no weight decay, no amsgrad):
+ *   m = m + (g - m)(1 - beta1);  v = v beta2 + g g (1 - beta2);
+ *   p = p - lr / (1 - beta1^t) * m / (sqrt(v) / sqrt(1 - beta2^t) + eps),     g = grad * grad_scale
+ * state is two int32 on the device: {t (steps done so far), 0}; the kernel advances t, so the
+ * launch can be replayed from a CUDA graph.  All buffers 16-byte aligned.
+ * ---------------------------------------------------------------------------------------- */
+DL_API int dl_adam_step_f32(float *param, const float *grad, float *exp_avg, float *exp_avg_sq, int64_t n, float lr,
+                            float beta1, float beta2, float eps, float grad_scale, int32_t *state, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -248,3 +248,53 @@ def test_packed_eval_larger_batch_against_oracle_and_float_path():
         fl = model(x.cuda().float())
     assert np.array_equal(counts.cpu().numpy(), ref)
     assert np.array_equal(np.rint(fl.cpu().numpy()).astype(np.int32), ref)
+
+
+def test_flat_adam_matches_torch_adam():
+    """FlatAdam (one kernel over a flat parameter buffer) against torch.optim.Adam over several steps."""
+    from difflogic_b200.optim import FlatAdam
+    torch.manual_seed(2)
+    dims = [40, 96, 96, 60]
+    net = O.OracleNet.build(dims, 6, 4.0)
+    x = (torch.rand(48, 40) < 0.4).float().cuda()
+    y = torch.randint(0, 6, (48,)).cuda()
+    m1 = build_model(dims, 6, 4.0, net.weights, net.idx_a, net.idx_b)
+    m2 = build_model(dims, 6, 4.0, net.weights, net.idx_a, net.idx_b)
+    o1 = torch.optim.Adam(m1.parameters(), lr=0.01)
+    o2 = FlatAdam(m2.parameters(), lr=0.01)
+    for l in logic_layers(m2):
+        assert l.weights.data_ptr() >= o2.flat_param.data_ptr()  # parameters became views of the flat buffer
+    for step in range(5):
+        for m, o in ((m1, o1), (m2, o2)):
+            m.train()
+            loss = torch.nn.functional.cross_entropy(m(x), y)
+            o.zero_grad()
+            loss.backward()
+            o.step()
+        for l1, l2 in zip(logic_layers(m1), logic_layers(m2)):
+            assert l2.weights.grad.data_ptr() == o2.grad_view(l2.weights).data_ptr()  # written in place, not copied
+            assert torch.allclose(l1.weights, l2.weights, rtol=1e-5, atol=2e-6), step
+    assert int(o2.state_t[0].item()) == 5 and int(o2.state_t[1].item()) == 0
+
+
+def test_captured_train_step_matches_eager():
+    """TrainStep.capture(): the CUDA-graph replay of a step gives the same weights as eager steps."""
+    from difflogic_b200.optim import FlatAdam
+    from difflogic_b200.training import TrainStep
+    torch.manual_seed(6)
+    dims = [30, 64, 64]
+    net = O.OracleNet.build(dims, 4, 2.0)
+    xs = [(torch.rand(32, 30) < 0.5).float().cuda() for _ in range(4)]
+    ys = [torch.randint(0, 4, (32,)).cuda() for _ in range(4)]
+    models = [build_model(dims, 4, 2.0, net.weights, net.idx_a, net.idx_b) for _ in range(2)]
+    steps = [TrainStep(m, FlatAdam(m.parameters(), lr=0.01)) for m in models]
+    for m in models:
+        m.train()
+    steps[1].capture(xs[0], ys[0], warmup=0)
+    losses = [[], []]
+    for i in range(4):
+        for s in (0, 1):
+            losses[s].append(float(steps[s](xs[i], ys[i]).item()))
+    assert np.allclose(losses[0], losses[1], rtol=1e-5)
+    for l0, l1 in zip(logic_layers(models[0]), logic_layers(models[1])):
+        assert torch.allclose(l0.weights, l1.weights, rtol=1e-5, atol=1e-6)
