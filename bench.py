@@ -283,7 +283,7 @@ def bench_train(args, rank, world):
     }
 
     # ---- roofline of the three layer kernels at the hidden-layer shape (rank 0 only)
-    if rank == 0:
+    if rank == 0 and not args.skip_kernel_timing:
         layer = [m for m in model if hasattr(m, "indices")][2]
         a, b = layer.indices
         n = TRAIN_DIMS[1]
@@ -513,6 +513,7 @@ def main():
     ap.add_argument("--optimizer", default="flat", choices=["flat", "torch"],
                     help="flat: difflogic_b200.optim.FlatAdam (one kernel); torch: torch.optim.Adam(capturable, fused)")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-kernel-timing", action="store_true", help="leave out the per-kernel roofline timing")
     args = ap.parse_args()
 
     if args.impl == "reference":

@@ -3,9 +3,10 @@
 //
 // Why: the plain eval kernel keeps its loads in registers, and at 16 bytes per lane the register
 // file caps the bytes in flight per SM well below what HBM3e needs (ncu: 91 registers, 2 CTAs per SM,
-// 42 % of DRAM peak).  Here one producer warp issues a 1-D bulk copy per gathered row segment --
-// no registers, up to ~160 KB in flight per SM -- and eight consumer warps turn finished stages into
-// output rows with 16-byte shared loads, LOP3s and 16-byte global stores.
+// 42 % of DRAM peak).  Here two producer warps issue one 1-D bulk copy per gathered row segment --
+// no registers held, 64 KB per stage -- and eight consumer warps turn finished stages into output
+// rows with 16-byte shared loads, LOP3s and 16-byte global stores.  One producer warp alone was the
+// bottleneck (about 1 us of issue work per tile); two alternate over the tiles.
 //
 // Tiling: a tile is kTileRows neurons x `chunk` bytes of their rows.  Tiles are numbered column
 // chunk major, so the CTAs of the persistent grid (one per SM) work on the same column chunk of x at
@@ -17,11 +18,12 @@
 
 namespace dl {
 
-constexpr int kTileRows = 8;        // neurons per tile: 16 row segments, one bulk copy each
-constexpr int kStages = 6;
+constexpr int kTileRows = 16;       // neurons per tile: 32 row segments = one copy per producer lane
+constexpr int kStages = 2;          // 2 x 64 KB
+constexpr int kProducers = 2;       // producer warps; tile i is issued by warp i % kProducers
 constexpr int kConsumerWarps = 8;
-constexpr int kTmaThreads = 32 * (1 + kConsumerWarps);
-constexpr int kMaxChunk = 2048;     // bytes of a row per tile; stage = 2*8*2048 = 32 KB, six stages in flight
+constexpr int kTmaThreads = 32 * (kProducers + kConsumerWarps);
+constexpr int kMaxChunk = 2048;     // bytes of a row per tile
 
 __device__ int g_async_error = 0;   // set when a bounded wait ran out; read by dl_async_error()
 
@@ -35,8 +37,8 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
 
 __global__ void __launch_bounds__(kTmaThreads, 1)
 eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
-                const uint8_t *__restrict__ gate, uint8_t *__restrict__ y, int64_t n_out, int64_t row_bytes, int chunk,
-                int64_t row_blocks, int64_t ntiles) {
+                const uint8_t *__restrict__ gate, uint8_t *__restrict__ y, uint32_t n_out, int64_t row_bytes, int chunk,
+                uint32_t row_blocks, uint32_t ntiles) {
     extern __shared__ __align__(128) uint8_t smem[];
     const size_t stage_bytes = (size_t)2 * kTileRows * chunk;
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + kStages * stage_bytes);
@@ -55,73 +57,75 @@ eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, co
     }
     __syncthreads();
     volatile int *abort_flag = &s_abort;
+    const uint32_t G = gridDim.x;
 
-    if (warp == 0) {
-        // ---------------- producer: one bulk copy per (neuron, input) of the tile ----------------
-        // Lanes 0 .. 2*kTileRows-1 own one row segment each.  The connection indices of the NEXT tile are
-        // fetched while this tile's stage is still being waited for, so their latency is off the refill path.
+    if (warp < kProducers) {
+        // ---------------- producers: one bulk copy per (neuron, input) of the tile ----------------
+        // Lane l owns input (l / kTileRows) of neuron (l % kTileRows).  The connection indices of this warp's
+        // NEXT tile are fetched while the current stage is still being waited for.
         const int r = lane % kTileRows, which = lane / kTileRows;
-        const bool copier = lane < 2 * kTileRows;
-        int64_t it = 0;
+        uint32_t it = warp;
+        uint32_t t = blockIdx.x + warp * G;
+        uint32_t issued = 0;
         bool ok = true;
         int64_t idx = 0;
         uint32_t op = 0;
-        {
-            const int64_t j = (blockIdx.x % row_blocks) * kTileRows + r;
-            if (copier && blockIdx.x < ntiles && j < n_out) {
+        if (t < ntiles) {
+            const uint32_t j = (t % row_blocks) * kTileRows + r;
+            if (j < n_out) {
                 idx = __ldg((which ? b : a) + j);
                 op = __ldg(gate + j);
             }
         }
-        for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+        for (; t < ntiles; t += kProducers * G, it += kProducers) {
             const int s = (int)(it % kStages);
-            const uint32_t use = (uint32_t)(it / kStages);
-            // prefetch for the tile after this one
+            const uint32_t use = it / kStages;
             int64_t idx_next = 0;
             uint32_t op_next = 0;
-            const int64_t tn = t + gridDim.x;
-            if (copier && tn < ntiles) {
-                const int64_t jn = (tn % row_blocks) * kTileRows + r;
+            const uint32_t tn = t + kProducers * G;
+            if (tn < ntiles) {
+                const uint32_t jn = (tn % row_blocks) * kTileRows + r;
                 if (jn < n_out) {
                     idx_next = __ldg((which ? b : a) + jn);
                     op_next = __ldg(gate + jn);
                 }
             }
             if (!wait_or_abort(empty + s, (use & 1u) ^ 1u, abort_flag)) { ok = false; break; }
-            const int64_t cb = t / row_blocks, nb = t % row_blocks;
-            const int64_t col0 = cb * chunk;
+            const uint32_t cb = t / row_blocks, nb = t % row_blocks;
+            const int64_t col0 = (int64_t)cb * chunk;
             const uint32_t bytes = (uint32_t)min((int64_t)chunk, row_bytes - col0);
-            const bool valid = copier && nb * kTileRows + r < n_out;
-            const int nvalid = (int)min((int64_t)kTileRows, n_out - nb * kTileRows);
+            const bool valid = nb * kTileRows + r < n_out;
+            const uint32_t nvalid = min((uint32_t)kTileRows, n_out - nb * kTileRows);
             if (valid && which == 0) meta[s * kTileRows + r] = (uint8_t)op;
             __syncwarp();
-            if (lane == 0) mbar_arrive_expect_tx(full + s, 2u * (uint32_t)nvalid * bytes);
+            if (lane == 0) mbar_arrive_expect_tx(full + s, 2u * nvalid * bytes);
             __syncwarp();
             if (valid)
                 bulk_load(smem + s * stage_bytes + (size_t)(which * kTileRows + r) * chunk, x + idx * row_bytes + col0, bytes,
                           full + s);
+            ++issued;
             idx = idx_next;
             op = op_next;
         }
         if (!ok || *abort_flag) {
-            // something went wrong: flag it, stop the consumers, and give copies already issued time to land
+            // something went wrong: flag it, stop everybody, and give this warp's last copies time to land
             if (lane == 0) {
                 g_async_error = 1;
                 s_abort = 1;
             }
             __syncwarp();
-            for (int s = 0; s < kStages; ++s) {
-                const int64_t fills = (it + kStages - 1 - s) / kStages;  // copies issued into stage s so far
-                if (fills > 0) mbar_wait(full + s, (uint32_t)(fills - 1) & 1u);
+            if (issued > 0) {
+                const uint32_t last = it - kProducers;  // iteration of this warp's latest fill
+                mbar_wait(full + (last % kStages), (last / kStages) & 1u);
             }
         }
     } else {
         // ---------------- consumers: finished stages -> output rows ------------------------------
-        const int cw = warp - 1;
-        int64_t it = 0;
-        for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+        const int cw = warp - kProducers;
+        uint32_t it = 0;
+        for (uint32_t t = blockIdx.x; t < ntiles; t += G, ++it) {
             const int s = (int)(it % kStages);
-            const uint32_t use = (uint32_t)(it / kStages);
+            const uint32_t use = it / kStages;
             if (!wait_or_abort(full + s, use & 1u, abort_flag)) {
                 if (lane == 0) {
                     g_async_error = 1;
@@ -129,16 +133,16 @@ eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, co
                 }
                 break;
             }
-            const int64_t cb = t / row_blocks, nb = t % row_blocks;
-            const int64_t col0 = cb * chunk;
+            const uint32_t cb = t / row_blocks, nb = t % row_blocks;
+            const int64_t col0 = (int64_t)cb * chunk;
             const int vecs = (int)(min((int64_t)chunk, row_bytes - col0) / 16);
-            const int nvalid = (int)min((int64_t)kTileRows, n_out - nb * kTileRows);
+            const int nvalid = (int)min((uint32_t)kTileRows, n_out - nb * kTileRows);
             const uint4 *sa = reinterpret_cast<const uint4 *>(smem + s * stage_bytes);
             const uint4 *sb = reinterpret_cast<const uint4 *>(smem + s * stage_bytes + (size_t)kTileRows * chunk);
             const int pitch = chunk / 16;
             for (int r = cw; r < nvalid; r += kConsumerWarps) {
                 const GateMasks gm = gate_masks(meta[s * kTileRows + r]);
-                uint4 *dst = reinterpret_cast<uint4 *>(y + (nb * kTileRows + r) * row_bytes + col0);
+                uint4 *dst = reinterpret_cast<uint4 *>(y + ((int64_t)nb * kTileRows + r) * row_bytes + col0);
 #pragma unroll 4
                 for (int c = lane; c < vecs; c += 32) {
                     const uint4 va = sa[r * pitch + c], vb = sb[r * pitch + c];
@@ -166,9 +170,11 @@ static int sm_count() {
     return cached[dev];
 }
 
-// True when the staged kernel applies: 16-byte aligned rows of at least 512 bytes.
+// True when the staged kernel applies: 16-byte aligned rows of at least 512 bytes, tile count within 32 bits.
 bool eval_tma_applicable(const void *x, const void *y, int64_t row_bytes, int64_t n_out) {
-    return row_bytes % 16 == 0 && row_bytes >= 512 && n_out >= kTileRows && aligned_to(x, 16) && aligned_to(y, 16);
+    if (!(row_bytes % 16 == 0 && row_bytes >= 512 && n_out >= kTileRows && aligned_to(x, 16) && aligned_to(y, 16))) return false;
+    const int64_t chunk = row_bytes < kMaxChunk ? row_bytes : kMaxChunk;
+    return n_out < ((int64_t)1 << 31) && ceil_div(row_bytes, chunk) * ceil_div(n_out, kTileRows) < ((int64_t)1 << 31) - 4096;
 }
 
 int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_out,
@@ -183,7 +189,8 @@ int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uin
     const int64_t sms = sm_count();
     const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
     eval_tma_kernel<<<grid, kTmaThreads, smem, st>>>(reinterpret_cast<const uint8_t *>(x), a, b, gate,
-                                                    reinterpret_cast<uint8_t *>(y), n_out, row_bytes, chunk, row_blocks, ntiles);
+                                                    reinterpret_cast<uint8_t *>(y), (uint32_t)n_out, row_bytes, chunk,
+                                                    (uint32_t)row_blocks, (uint32_t)ntiles);
     return launch_status("dl_eval_packed");
 }
 

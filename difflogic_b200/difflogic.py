@@ -253,6 +253,10 @@ class LogicLayerFunction(torch.autograd.Function):
             grad_x = ops.logic_backward_x(x, coef, grad_y, start, plan, ctx.grad_factor, overlap=True)
         if ctx.needs_input_grad[1]:
             grad_w = ops.logic_backward_w(x, a, b, grad_y, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True)
+            if ctx.grad_out is not None:
+                # a fresh alias that nothing else references: autograd then adopts it as `weights.grad`
+                # instead of copying it, so the gradient stays inside the flat bucket
+                grad_w = grad_w.view(grad_w.shape)
         return grad_x, grad_w, None, None, None, None, None, None
 
 
