@@ -36,8 +36,10 @@ class TrainStep:
         self._static_x = self._static_y = self._static_loss = None
         self._comm_stream = None
         self._hooks = []
+        self._on_gpu = all(p.is_cuda for p in self.params)
         if self.group is not None and self.world_size > 1:
-            self._comm_stream = torch.cuda.Stream()
+            if self._on_gpu:
+                self._comm_stream = torch.cuda.Stream()
             for p in self.params:
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._reduce_when_ready))
 
@@ -45,6 +47,11 @@ class TrainStep:
 
     def _reduce_when_ready(self, param):
         """Runs right after `param.grad` has been written by the layer's backward_w."""
+        if not self._on_gpu:
+            # host tensors (the pure-python implementation, gloo): no streams, and gloo has no AVG
+            dist.all_reduce(param.grad, op=dist.ReduceOp.SUM, group=self.group)
+            param.grad.div_(self.world_size)
+            return
         main = torch.cuda.current_stream()
         ready = torch.cuda.Event()
         ready.record(main)
@@ -104,3 +111,14 @@ class TrainStep:
         """Replays the captured step on whatever the static input buffers hold."""
         self._graph.replay()
         return self._static_loss
+
+
+def shard_range(n_samples, rank, world_size, multiple=1):
+    """[start, stop) of the samples rank `rank` works on when `n_samples` are split over `world_size` ranks in
+    contiguous pieces whose sizes are multiples of `multiple` (64 for packed int64 words: a shard is then a
+    column range of whole words of the packed tensor); the last rank takes the remainder."""
+    units = -(-n_samples // multiple)
+    per = -(-units // world_size)
+    start = min(rank * per * multiple, n_samples)
+    stop = min((rank + 1) * per * multiple, n_samples)
+    return start, stop
