@@ -129,6 +129,7 @@ static int groupsum_check(const char *who, int64_t n, int64_t batch, int64_t k) 
 extern "C" DL_API size_t dl_groupsum_workspace_bytes(int64_t n, int64_t batch, int64_t k) {
     if (n <= 0 || batch <= 0 || k <= 0 || n % k != 0) return kGsCounterBytes;
     const int64_t chunks = groupsum_chunks(n, batch, k);
+    if (chunks == 1) return kGsCounterBytes;  // one piece per class: no partial sums are stored
     return (size_t)kGsCounterBytes + (size_t)(k * chunks * batch) * sizeof(float);
 }
 
@@ -164,4 +165,64 @@ extern "C" DL_API int dl_groupsum_backward_f32(const float *grad_out, float *gra
     groupsum_backward_kernel<<<(unsigned)blocks, kThreads, 0, as_stream(stream)>>>(grad_out, grad_x, n, batch, (int)k,
                                                                                   (int)(n / k), tau);
     return launch_status("dl_groupsum_backward_f32");
+}
+
+// ---------------------------------------------------------------------------------------------
+// dl_groupsum_f32_static: the same forward GroupSum for callers that cannot hand over a workspace.
+//
+// Some callers of this library own no device allocator: a binding from another language that only
+// passes through the input and output buffers its framework gave it, or a serving process whose
+// memory pool was sized at start-up and is full.  dl_groupsum_f32 is closed to them because it needs
+// caller-owned scratch.  This variant keeps that scratch in the library itself, in a fixed device
+// array that exists once per GPU for as long as the library is loaded, so the call allocates nothing.
+// The price is a size limit (kStaticScratchBytes) and that all calls on a GPU share the array.
+// ---------------------------------------------------------------------------------------------
+namespace dl {
+
+constexpr size_t kStaticScratchBytes = 256u << 10;  // 256 KiB per GPU: counters + partial sums
+
+static __device__ __align__(256) unsigned char g_groupsum_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void *g_scratch_ptr[kMaxDevices];  // device address of the array, per device; null until looked up
+
+// Device address of this device's copy of the scratch array.  In host code the array's name is only a
+// handle; the address a kernel can use has to be asked for, with the device current.
+static int static_scratch(void **out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+        return fail(DL_ERR_CUDA, "dl_groupsum_f32_static: cannot tell the current device");
+    void *ptr = __atomic_load_n(&g_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+    if (ptr == nullptr) {
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_groupsum_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return fail(DL_ERR_CUDA, "dl_groupsum_f32_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        }
+        __atomic_store_n(&g_scratch_ptr[dev], ptr, __ATOMIC_RELEASE);  // every thread would store the same value
+    }
+    *out = ptr;
+    return DL_OK;
+}
+
+}  // namespace dl
+
+extern "C" DL_API size_t dl_groupsum_static_limit_bytes(void) { return dl::kStaticScratchBytes; }
+
+extern "C" DL_API int dl_groupsum_f32_static(const float *x, float *out, int64_t n, int64_t batch, int64_t k, float tau,
+                                             void *stream) {
+    if (int s = groupsum_check("dl_groupsum_f32_static", n, batch, k)) return s;
+    if (batch == 0) return DL_OK;
+    const size_t need = dl_groupsum_workspace_bytes(n, batch, k);
+    DL_REQUIRE(need <= kStaticScratchBytes, DL_ERR_TOO_LARGE,
+               "dl_groupsum_f32_static: this shape needs %zu bytes of scratch, the built-in array holds %zu; "
+               "use dl_groupsum_f32 with a workspace of your own",
+               need, (size_t)kStaticScratchBytes);
+    void *scratch = nullptr;
+    if (int s = static_scratch(&scratch)) return s;
+    // The array keeps whatever the previous call left.  The partial sums are overwritten before they are
+    // read; the counters must start at zero, so they are cleared on the caller's stream first.
+    if (cudaMemsetAsync(scratch, 0, kGsCounterBytes, as_stream(stream)) != cudaSuccess)
+        return launch_status("dl_groupsum_f32_static (clearing the counters)");
+    return dl_groupsum_f32(x, out, scratch, n, batch, k, tau, stream);
 }

@@ -181,6 +181,26 @@ DL_API int dl_groupsum_backward_f32(const float *grad_out, float *grad_x, int64_
                              float tau, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * dl_groupsum_f32 without a caller-owned workspace.  No counterpart in the reference (its GroupSum
+ * is a torch expression that allocates through torch).
+ *
+ * For callers that cannot allocate device memory: a foreign-language binding that only forwards the
+ * buffers its own framework handed it, or a process whose device memory pool is fixed and full.  The
+ * scratch lives in a device array inside the library: dl_groupsum_static_limit_bytes() bytes (256 KiB)
+ * per GPU, held from the first use of the library on that GPU until the process exits.  The call
+ * allocates and frees nothing.  Limits and rules:
+ *   - shapes with dl_groupsum_workspace_bytes(n, batch, k) above the limit get DL_ERR_TOO_LARGE;
+ *   - the first call on a device looks up the array's device address (with that device current);
+ *     make that first call outside any stream capture;
+ *   - every call on a GPU uses the same array: calls that may overlap on the GPU (different
+ *     streams) race with each other and must be ordered by the caller.
+ * Results are identical to dl_groupsum_f32.
+ * ---------------------------------------------------------------------------------------- */
+DL_API size_t dl_groupsum_static_limit_bytes(void);
+DL_API int dl_groupsum_f32_static(const float *x, float *out, int64_t n, int64_t batch, int64_t k, float tau,
+                                  void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * Adam step over a flat fp32 parameter vector (all layers' gate weights in one buffer).
  * Replaces torch.optim.Adam(model.parameters(), lr).step() of the reference's training loop
  * (experiments/main.py:169,179), same update rule (no weight decay, no amsgrad):
