@@ -20,6 +20,8 @@ import argparse
 import json
 import os
 import sys
+import faulthandler
+import gc
 import threading
 import time
 
@@ -214,7 +216,7 @@ def bench_train(args, rank, world):
         from difflogic_b200.optim import FlatAdam
         opt = FlatAdam(model.parameters(), lr=TRAIN_LR)
     group = dist.group.WORLD if world > 1 else None
-    step = TrainStep(model, opt, torch.nn.CrossEntropyLoss(), process_group=group, world_size=world)
+    step = TrainStep(model, opt, torch.nn.CrossEntropyLoss(), process_group=group, world_size=world, buckets=args.buckets)
 
     # synthetic batches, per-rank seed; a pool in pinned host memory and a copy of it in HBM
     g = torch.Generator().manual_seed(1000 + rank)
@@ -318,7 +320,9 @@ def bench_train(args, rank, world):
                            "note": "hot = back-to-back launches, operands L2-resident as inside the step (the layer's "
                                    "working set is 26 MB); cold = L2 flushed before every launch"}
         out["roofline_kernels"] = rows
+    step.close()   # the graph holds captured collectives: drop it before the process group goes away
     del step, model, opt
+    gc.collect()
     torch.cuda.empty_cache()
     return out
 
@@ -513,8 +517,11 @@ def main():
     ap.add_argument("--optimizer", default="flat", choices=["flat", "torch"],
                     help="flat: difflogic_b200.optim.FlatAdam (one kernel); torch: torch.optim.Adam(capturable, fused)")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--buckets", type=int, default=2, help="all-reduce pieces of the flat gradient buffer (N > 1)")
     ap.add_argument("--skip-kernel-timing", action="store_true", help="leave out the per-kernel roofline timing")
     args = ap.parse_args()
+    # a run that is stuck (e.g. in a collective) ends itself with a traceback instead of holding the GPUs
+    faulthandler.dump_traceback_later(1200, exit=True)
 
     if args.impl == "reference":
         reference_arm(args)
@@ -569,8 +576,13 @@ def main():
                                                     "CompiledLogicNet's generated C, num_bits=64)"}
         print(json.dumps(line))
     barrier(world)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    faulthandler.cancel_dump_traceback_later()
     if world > 1:
-        dist.destroy_process_group()
+        # every rank is past the last collective; leave without tearing NCCL down (its teardown has hung here
+        # while CUDA graphs with captured collectives were still referenced)
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -4,9 +4,10 @@ batch-sharded over several (one process per GPU).
 The reference has no multi-GPU code; its step is `loss_fn(model(x), y) -> zero_grad -> backward ->
 optimizer.step` (experiments/main.py:174-181).  `TrainStep` runs exactly that.  When a process
 group is given, every rank holds a full replica of the weights and connection indices, works on
-its own shard of the batch, and the `[out_dim, 16]` weight gradients are averaged with one NCCL
-all-reduce per layer, launched on a side stream as soon as that layer's backward_w has finished so
-that it overlaps the rest of the backward pass.  Nothing else crosses GPUs.
+its own shard of the batch, and only the `[out_dim, 16]` weight gradients are averaged over the
+ranks (NCCL all-reduce on a side stream, launched as soon as the gradients of a bucket of layers
+have been written by their backward_w, so that it overlaps the rest of the backward pass).
+Nothing else crosses GPUs.
 
 `capture()` records the whole step (H2D staging excluded) in one CUDA graph: the model's kernels
 launch on torch's current stream, allocate nothing themselves and never synchronise, so a step of
@@ -17,13 +18,16 @@ import torch.distributed as dist
 
 
 class TrainStep:
-    def __init__(self, model, optimizer, loss_fn=None, process_group=None, world_size=None):
+    def __init__(self, model, optimizer, loss_fn=None, process_group=None, world_size=None, buckets=2):
         """
         :param model:         module on the current CUDA device (replicated on every rank)
         :param optimizer:     its optimizer; for `capture()` it must be graph-capturable
-                              (e.g. torch.optim.Adam(..., capturable=True))
+                              (difflogic_b200.optim.FlatAdam, or torch.optim.Adam(..., capturable=True))
         :param loss_fn:       defaults to CrossEntropyLoss (mean over the local batch)
         :param process_group: torch.distributed group to average gradients over, or None
+        :param buckets:       with FlatAdam: number of contiguous pieces of the flat gradient buffer that are
+                              all-reduced separately (the piece holding the last layers first); 1 = one
+                              all-reduce after the whole backward pass.  Other optimizers: one per parameter.
         """
         self.model = model
         self.optimizer = optimizer
@@ -37,13 +41,47 @@ class TrainStep:
         self._comm_stream = None
         self._hooks = []
         self._on_gpu = all(p.is_cuda for p in self.params)
+        self._bucket_of = {}       # param -> bucket index
+        self._bucket_slices = []   # flat gradient slice of each bucket
+        self._bucket_sizes = []    # parameters per bucket
+        self._pending = []
         if self.group is not None and self.world_size > 1:
             if self._on_gpu:
                 self._comm_stream = torch.cuda.Stream()
+                self._plan_buckets(max(1, int(buckets)))
             for p in self.params:
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._reduce_when_ready))
 
     # -- gradient exchange -----------------------------------------------------------------------
+
+    def _plan_buckets(self, n_buckets):
+        """With a flat gradient buffer (FlatAdam), groups consecutive parameters into `n_buckets` slices of it."""
+        slices = getattr(self.optimizer, "_slices", None)
+        flat = getattr(self.optimizer, "flat_grad", None)
+        if slices is None or flat is None or any(p not in slices for p in self.params):
+            return
+        order = sorted(self.params, key=lambda p: slices[p][0])
+        n_buckets = min(n_buckets, len(order))
+        per = -(-len(order) // n_buckets)
+        for bi in range(n_buckets):
+            group = order[bi * per:(bi + 1) * per]
+            if not group:
+                continue
+            lo = slices[group[0]][0]
+            hi = slices[group[-1]][0] + slices[group[-1]][1]
+            for p in group:
+                self._bucket_of[p] = len(self._bucket_slices)
+            self._bucket_slices.append(flat[lo:hi])
+            self._bucket_sizes.append(len(group))
+        self._pending = list(self._bucket_sizes)
+
+    def _launch_all_reduce(self, tensor):
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        self._comm_stream.wait_event(ready)
+        with torch.cuda.stream(self._comm_stream):
+            dist.all_reduce(tensor, op=dist.ReduceOp.AVG, group=self.group)
 
     def _reduce_when_ready(self, param):
         """Runs right after `param.grad` has been written by the layer's backward_w."""
@@ -52,15 +90,13 @@ class TrainStep:
             dist.all_reduce(param.grad, op=dist.ReduceOp.SUM, group=self.group)
             param.grad.div_(self.world_size)
             return
-        main = torch.cuda.current_stream()
-        ready = torch.cuda.Event()
-        ready.record(main)
-        self._comm_stream.wait_event(ready)
-        # with FlatAdam the gradient lives in the optimizer's flat bucket (backward_w wrote it there)
-        view = getattr(self.optimizer, "grad_view", None)
-        grad = view(param) if view is not None else param.grad
-        with torch.cuda.stream(self._comm_stream):
-            dist.all_reduce(grad, op=dist.ReduceOp.AVG, group=self.group)
+        if param in self._bucket_of:
+            bi = self._bucket_of[param]
+            self._pending[bi] -= 1
+            if self._pending[bi] == 0:
+                self._launch_all_reduce(self._bucket_slices[bi])
+            return
+        self._launch_all_reduce(param.grad)
 
     def _join_comm(self):
         if self._comm_stream is not None:
@@ -69,6 +105,7 @@ class TrainStep:
     # -- the step --------------------------------------------------------------------------------
 
     def _step(self, x, y):
+        self._pending = list(self._bucket_sizes)
         loss = self.loss_fn(self.model(x), y)
         self.optimizer.zero_grad(set_to_none=True)
         loss.backward()
@@ -111,6 +148,17 @@ class TrainStep:
         """Replays the captured step on whatever the static input buffers hold."""
         self._graph.replay()
         return self._static_loss
+
+    def close(self):
+        """Drops the captured graph and the gradient hooks.  Call it before tearing down the process group: a
+        graph that holds captured collectives must not outlive the communicator."""
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+        if self._on_gpu and torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self._graph = None
+        self._static_loss = None
 
 
 def shard_range(n_samples, rank, world_size, multiple=1):
