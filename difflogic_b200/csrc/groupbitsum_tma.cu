@@ -15,7 +15,7 @@ namespace dl {
 
 constexpr int kGbRows = 32;         // rows per stage: one copy per producer lane
 constexpr int kGbColBytes = 1024;   // column block: 128 words of 64 bits
-constexpr int kGbStages = 6;        // 6 x 32 KB
+constexpr int kGbStages = 3;        // 3 x 32 KB per CTA; two CTAs share an SM, so two producer warps issue copies per SM
 constexpr int kGbConsumers = 128;
 constexpr int kGbThreads = 32 + kGbConsumers;
 
@@ -51,7 +51,7 @@ __device__ __forceinline__ GbUnit gb_unit(int64_t u, int64_t row_bytes, int k, i
     return g;
 }
 
-__global__ void __launch_bounds__(kGbThreads, 1)
+__global__ void __launch_bounds__(kGbThreads, 2)
 groupbitsum_tma_kernel(const uint8_t *__restrict__ x, int32_t *__restrict__ out, int64_t row_bytes, int64_t batch, int k, int m,
                        int splits, int nplanes, int64_t nunits) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -190,7 +190,7 @@ int launch_groupbitsum_tma(const void *x, int32_t *out, int64_t n, int64_t row_b
     const int64_t colblocks = ceil_div(row_bytes, kGbColBytes);
     const int64_t sms = gb_sm_count();
     // split a class's rows when columns x classes alone cannot occupy every SM a few times over
-    int64_t splits = ceil_div(4 * sms, colblocks * k);
+    int64_t splits = ceil_div(8 * sms, colblocks * k);
     if (splits > m / 64) splits = m / 64;
     if (splits < 1) splits = 1;
     while (ceil_div(m, splits) > kMaxChunkRows) ++splits;
@@ -202,7 +202,7 @@ int launch_groupbitsum_tma(const void *x, int32_t *out, int64_t n, int64_t row_b
     const size_t smem = (size_t)kGbStages * kGbRows * kGbColBytes + 2 * kGbStages * sizeof(uint64_t);
     if (cudaFuncSetAttribute(groupbitsum_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return launch_status("dl_groupbitsum (shared memory opt-in)");
-    const unsigned grid = (unsigned)(nunits < sms ? nunits : sms);
+    const unsigned grid = (unsigned)(nunits < 2 * sms ? nunits : 2 * sms);
     groupbitsum_tma_kernel<<<grid, kGbThreads, smem, st>>>(reinterpret_cast<const uint8_t *>(x), out, row_bytes, batch, (int)k,
                                                           (int)m, (int)splits, nplanes, nunits);
     return launch_status("dl_groupbitsum");
