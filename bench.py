@@ -42,7 +42,14 @@ UNIT = "samples/s"
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures summarised under
 # profiles/; None until a capture of that kernel exists.
-NCU_TRAFFIC = {"backward_x": None, "forward": None, "backward_w": None, "eval_packed": None, "groupbitsum": None}
+NCU_TRAFFIC = {
+    # profiles/train_kernels_16000x16000_batch128.md: cold-cache captures; inside a step the operands are L2-resident
+    "forward": 9.49e6, "backward_w": 17.68e6, "backward_x": 17.04e6,
+    # profiles/eval_tma_kernel_8000x8000_4096words.md and groupbitsum_tma_kernel_...: captured at 4096 words per row and
+    # scaled by 4 to the 16384 words of the bench (traffic is proportional to the row length; the part of the
+    # output still dirty in L2 at the end of the kernel, ~40 MB, is not)
+    "eval_packed": 4 * 262.79e6 + (4 * 262.14e6 - 40.7e6), "groupbitsum": 4 * 272.67e6 + (4 * 10.49e6 - 2.3e6),
+}
 
 
 # ----------------------------------------------------------------------------------------------------------
@@ -216,7 +223,12 @@ def bench_train(args, rank, world):
         from difflogic_b200.optim import FlatAdam
         opt = FlatAdam(model.parameters(), lr=TRAIN_LR)
     group = dist.group.WORLD if world > 1 else None
-    step = TrainStep(model, opt, torch.nn.CrossEntropyLoss(), process_group=group, world_size=world, buckets=args.buckets)
+    if args.loss == "torch":
+        loss_fn = torch.nn.CrossEntropyLoss()
+    else:
+        from difflogic_b200.losses import CrossEntropyLoss
+        loss_fn = CrossEntropyLoss()
+    step = TrainStep(model, opt, loss_fn, process_group=group, world_size=world, buckets=args.buckets)
 
     # synthetic batches, per-rank seed; a pool in pinned host memory and a copy of it in HBM
     g = torch.Generator().manual_seed(1000 + rank)
@@ -513,6 +525,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--loss", default="fused", choices=["fused", "torch"],
+                    help="fused: difflogic_b200.losses.CrossEntropyLoss (one kernel each way); torch: torch.nn.CrossEntropyLoss")
     ap.add_argument("--skip-packed", action="store_true")
     ap.add_argument("--optimizer", default="flat", choices=["flat", "torch"],
                     help="flat: difflogic_b200.optim.FlatAdam (one kernel); torch: torch.optim.Adam(capturable, fused)")
@@ -554,6 +568,10 @@ def main():
                        "batch_per_gpu": TRAIN_BATCH, "global_batch": TRAIN_BATCH * world,
                        "parallelism": "batch-sharded replicas x%d, weight-gradient all-reduce" % world,
                        "execution": "whole step replayed as one CUDA graph",
+                       "loss": "CrossEntropy (%s)" % ("difflogic_b200.losses.CrossEntropyLoss" if args.loss == "fused"
+                                                      else "torch.nn.CrossEntropyLoss"),
+                       "optimizer": "Adam lr=0.01 (%s)" % ("difflogic_b200.optim.FlatAdam" if args.optimizer == "flat"
+                                                           else "torch.optim.Adam capturable fused"),
                        "l2": "flushed between timed steps (256 MiB memset, untimed)"},
             "e2e": train["e2e"], "gpu_launches": train["gpu_launches"], "launches_per_step": train["launches_per_step"],
             "clocks": train["clocks"], "loss": train["loss"],

@@ -40,6 +40,8 @@ SIGNATURES = {
     "dl_groupsum_backward_f32": (_int, [_ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),
     "dl_groupsum_static_limit_bytes": (ctypes.c_size_t, []),
     "dl_groupsum_f32_static": (_int, [_ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),
+    "dl_cross_entropy_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr]),
+    "dl_cross_entropy_backward_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr]),
     "dl_adam_step_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _f32, _f32, _f32, _f32, _f32, _ptr, _ptr]),
 }
 

@@ -8,6 +8,9 @@
 // merge) and stores the partial sum in the caller's workspace.  The CTA that finishes a
 // (class, column block) last adds the pieces in a fixed order and writes the result, so the
 // sum does not depend on scheduling and no float atomics are used.
+#include <cooperative_groups.h>
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace dl {
@@ -90,27 +93,89 @@ groupsum_kernel(const float *__restrict__ x, float *__restrict__ out, unsigned i
     if (tid == 0) *counter = 0u;  // ready for the next call
 }
 
-__global__ void __launch_bounds__(kThreads)
-groupsum_backward_kernel(const float *__restrict__ grad_out, float *__restrict__ grad_x, int64_t n, int64_t batch, int k,
-                         int m, float tau) {
-    // a warp per row, lanes along the batch
-    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const bool vec = (batch % 4 == 0);
-    for (int64_t row = (int64_t)blockIdx.x * 8 + warp; row < n; row += (int64_t)gridDim.x * 8) {
-        const int c = (int)(row / m);
-        float *dst = grad_x + row * batch;
-        if (vec) {
-            for (int64_t col = lane * 4; col < batch; col += 128) {
-                float4 v;
-                v.x = __ldg(grad_out + (col + 0) * k + c) / tau;
-                v.y = __ldg(grad_out + (col + 1) * k + c) / tau;
-                v.z = __ldg(grad_out + (col + 2) * k + c) / tau;
-                v.w = __ldg(grad_out + (col + 3) * k + c) / tau;
-                *reinterpret_cast<float4 *>(dst + col) = v;
-            }
-        } else {
-            for (int64_t col = lane; col < batch; col += 32) dst[col] = __ldg(grad_out + col * k + c) / tau;
+// Forward for classes of moderate size: a thread-block cluster of kGcCluster CTAs shares one (class, column
+// block); each CTA sums its piece of the rows, the pieces meet in the first CTA's view of the others' shared
+// memory (distributed shared memory) and are added there in a fixed order.  No scratch in global memory,
+// no fence, no atomics: one memory round trip plus a cluster barrier.
+constexpr int kGcThreads = 512;
+constexpr int kGcCluster = 8;
+
+__global__ void __launch_bounds__(kGcThreads)
+groupsum_cluster_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t batch, int k, int m, float tau) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float s_part[kGcThreads / 32][kGsCols];
+    __shared__ float s_sum[kGsCols];
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int colblock = blockIdx.x, c = blockIdx.y;
+    const int q = (int)cluster.block_rank(), nq = (int)cluster.num_blocks();
+    const int64_t col0 = (int64_t)colblock * kGsCols + lane * 4;
+    const int64_t rbeg = (int64_t)c * m + ((int64_t)m * q) / nq;
+    const int64_t rend = (int64_t)c * m + ((int64_t)m * (q + 1)) / nq;
+
+    grid_dependency_wait();  // x is the output of the kernel just before
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if ((batch % 4 == 0) && col0 + 3 < batch) {
+#pragma unroll 8
+        for (int64_t r = rbeg + warp; r < rend; r += kGcThreads / 32) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(x + r * batch + col0));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
+    } else {
+        for (int64_t r = rbeg + warp; r < rend; r += kGcThreads / 32) {
+            const float *p = x + r * batch + col0;
+            if (col0 + 0 < batch) acc.x += __ldg(p + 0);
+            if (col0 + 1 < batch) acc.y += __ldg(p + 1);
+            if (col0 + 2 < batch) acc.z += __ldg(p + 2);
+            if (col0 + 3 < batch) acc.w += __ldg(p + 3);
+        }
+    }
+    s_part[warp][lane * 4 + 0] = acc.x;
+    s_part[warp][lane * 4 + 1] = acc.y;
+    s_part[warp][lane * 4 + 2] = acc.z;
+    s_part[warp][lane * 4 + 3] = acc.w;
+    __syncthreads();
+    if (tid < kGsCols) {
+        float sum = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < kGcThreads / 32; ++wv) sum += s_part[wv][tid];
+        s_sum[tid] = sum;
+    }
+    cluster.sync();
+    const int64_t gcol = (int64_t)colblock * kGsCols + tid;
+    if (q == 0 && tid < kGsCols && gcol < batch) {
+        float total = 0.f;
+        for (int r = 0; r < nq; ++r) total += *cluster.map_shared_rank(&s_sum[tid], r);
+        out[gcol * k + c] = total / tau;
+    }
+    cluster.sync();  // the other CTAs' shared memory must stay alive until the first one has read it
+}
+
+// Backward: grad_x[i][:] = grad_out[:, class(i)] / tau.  A CTA takes a run of rows of one class and a block of
+// 128 batch columns: the class's 128 gradient values are read once, then row after row is written.
+constexpr int kGbkRows = 128;  // rows per CTA
+
+__global__ void __launch_bounds__(kThreads)
+groupsum_backward_kernel(const float *__restrict__ grad_out, float *__restrict__ grad_x, int64_t batch, int k, int m, float tau,
+                         int pieces) {
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int c = blockIdx.x / pieces, piece = blockIdx.x % pieces;
+    const int64_t r0 = (int64_t)c * m + ((int64_t)m * piece) / pieces;
+    const int64_t r1 = (int64_t)c * m + ((int64_t)m * (piece + 1)) / pieces;
+    const int64_t col = (int64_t)blockIdx.y * kGsCols + lane * 4;
+    grid_dependency_wait();  // grad_out comes from the loss' backward just before
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = (col + i < batch) ? __ldg(grad_out + (col + i) * k + c) / tau : 0.f;
+    if (batch % 4 == 0) {
+        if (col >= batch) return;
+        const float4 v4 = make_float4(v[0], v[1], v[2], v[3]);
+        for (int64_t r = r0 + warp; r < r1; r += kThreads / 32) *reinterpret_cast<float4 *>(grad_x + r * batch + col) = v4;
+    } else {
+        for (int64_t r = r0 + warp; r < r1; r += kThreads / 32)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (col + i < batch) grad_x[r * batch + col + i] = v[i];
     }
 }
 
@@ -142,6 +207,27 @@ extern "C" DL_API int dl_groupsum_f32(const float *x, float *out, void *workspac
     DL_REQUIRE(batch % 4 != 0 || aligned_to(x, 16), DL_ERR_INVALID_ARG, "dl_groupsum_f32: x must be 16-byte aligned");
     const int64_t chunks = groupsum_chunks(n, batch, k);
     const int64_t colblocks = ceil_div(batch, kGsCols);
+    // Classes of up to 4096 rows: one cluster of 8 CTAs per (class, column block), no scratch needed.
+    // DL_GROUPSUM_KERNEL=ticket forces the workspace kernel below (for A/B measurements).
+    const char *force = getenv("DL_GROUPSUM_KERNEL");
+    const int64_t m_rows = n / k;
+    if (!(force != nullptr && force[0] == 't') && chunks > 1 && m_rows >= 64 && m_rows <= 4096 && colblocks <= 65535) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)colblocks, (unsigned)k, kGcCluster);
+        cfg.blockDim = dim3(kGcThreads);
+        cfg.stream = as_stream(stream);
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = kGcCluster;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        cudaLaunchKernelEx(&cfg, groupsum_cluster_kernel, x, out, batch, (int)k, (int)m_rows, tau);
+        return launch_status("dl_groupsum_f32");
+    }
     DL_REQUIRE(colblocks <= INT32_MAX && chunks <= 65535, DL_ERR_TOO_LARGE, "dl_groupsum_f32: batch too large");
     DL_REQUIRE(chunks == 1 || k * colblocks <= kGsMaxCounters, DL_ERR_TOO_LARGE,
                "dl_groupsum_f32: k * ceil(batch/128) = %lld exceeds %d", (long long)(k * colblocks), kGsMaxCounters);
@@ -160,10 +246,12 @@ extern "C" DL_API int dl_groupsum_backward_f32(const float *grad_out, float *gra
     DL_REQUIRE(grad_out && grad_x, DL_ERR_INVALID_ARG, "dl_groupsum_backward_f32: null pointer");
     DL_REQUIRE(batch % 4 != 0 || aligned_to(grad_x, 16), DL_ERR_INVALID_ARG,
                "dl_groupsum_backward_f32: grad_x must be 16-byte aligned");
-    int64_t blocks = ceil_div(n, 8);
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    groupsum_backward_kernel<<<(unsigned)blocks, kThreads, 0, as_stream(stream)>>>(grad_out, grad_x, n, batch, (int)k,
-                                                                                  (int)(n / k), tau);
+    const int64_t m = n / k;
+    const int64_t pieces = ceil_div(m, kGbkRows);
+    const int64_t colblocks = ceil_div(batch, kGsCols);
+    DL_REQUIRE(k * pieces <= INT32_MAX && colblocks <= 65535, DL_ERR_TOO_LARGE, "dl_groupsum_backward_f32: problem too large");
+    launch_dependent(true, groupsum_backward_kernel, dim3((unsigned)(k * pieces), (unsigned)colblocks), dim3(kThreads), 0,
+                     as_stream(stream), grad_out, grad_x, batch, (int)k, (int)m, tau, (int)pieces);
     return launch_status("dl_groupsum_backward_f32");
 }
 

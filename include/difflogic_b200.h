@@ -201,6 +201,19 @@ DL_API int dl_groupsum_f32_static(const float *x, float *out, int64_t n, int64_t
                                   void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Cross-entropy loss (mean over the batch, int64 class targets) on the [batch][k] scores of a
+ * GroupSum, and its backward.  Replaces torch.nn.CrossEntropyLoss as the reference's training
+ * loop uses it (experiments/main.py:167,175: loss_fn(model(x), y), loss.backward()).
+ *   forward : loss[0] = -(1/B) sum_s log softmax(logits[s])[target[s]];  probs[s][:] = softmax(logits[s])
+ *   backward: grad_logits[s][c] = (probs[s][c] - [c == target[s]]) * grad_loss[0] / B
+ * loss and grad_loss are device scalars.  Targets outside [0, k) contribute nothing.
+ * ---------------------------------------------------------------------------------------- */
+DL_API int dl_cross_entropy_f32(const float *logits, const int64_t *target, float *loss, float *probs, int64_t batch,
+                                int64_t k, void *stream);
+DL_API int dl_cross_entropy_backward_f32(const float *probs, const int64_t *target, const float *grad_loss,
+                                         float *grad_logits, int64_t batch, int64_t k, void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * Adam step over a flat fp32 parameter vector (all layers' gate weights in one buffer).
  * Replaces torch.optim.Adam(model.parameters(), lr).step() of the reference's training loop
  * (experiments/main.py:169,179), same update rule (no weight decay, no amsgrad):

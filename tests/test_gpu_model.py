@@ -298,3 +298,23 @@ def test_captured_train_step_matches_eager():
     assert np.allclose(losses[0], losses[1], rtol=1e-5)
     for l0, l1 in zip(logic_layers(models[0]), logic_layers(models[1])):
         assert torch.allclose(l0.weights, l1.weights, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("shape", [(128, 10), (7, 3), (1000, 2), (2500, 17)])
+def test_cross_entropy_matches_torch(shape):
+    from difflogic_b200.losses import CrossEntropyLoss
+    batch, k = shape
+    g = torch.Generator().manual_seed(batch + k)
+    logits = (torch.randn(batch, k, generator=g) * 3).cuda()
+    target = torch.randint(0, k, (batch,), generator=g).cuda()
+    a = logits.clone().requires_grad_(True)
+    b = logits.clone().requires_grad_(True)
+    la = CrossEntropyLoss()(a, target)
+    lb = torch.nn.functional.cross_entropy(b, target)
+    (la * 1.5).backward()
+    (lb * 1.5).backward()
+    assert abs(la.item() - lb.item()) <= 1e-5 * abs(lb.item()) + 1e-7
+    assert_grad_close(a.grad, b.grad, "cross entropy grad", rtol=1e-5)
+    # a view of a feature-major GroupSum output works too
+    c = logits.t().contiguous().t().requires_grad_(True)
+    assert abs(CrossEntropyLoss()(c, target).item() - lb.item()) <= 1e-5 * abs(lb.item()) + 1e-7
