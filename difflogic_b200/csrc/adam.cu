@@ -13,6 +13,16 @@ __global__ void __launch_bounds__(kThreads)
 adam_kernel(float *__restrict__ p, const float *__restrict__ g, float *__restrict__ m, float *__restrict__ v, int64_t n, float lr,
             float beta1, float beta2, float eps, float grad_scale, int *__restrict__ state) {
     __shared__ float s_step_size, s_bc2_sqrt;
+    {
+        // set-up: pull this thread's slices of the parameters and moments towards L2 (128-byte lines) while the
+        // last backward kernel is still running
+        const int64_t lines = (n * 4 + 127) / 128;
+        for (int64_t l = (int64_t)blockIdx.x * kThreads + threadIdx.x; l < lines; l += (int64_t)gridDim.x * kThreads) {
+            prefetch_l2(reinterpret_cast<const char *>(p) + l * 128);
+            prefetch_l2(reinterpret_cast<const char *>(m) + l * 128);
+            prefetch_l2(reinterpret_cast<const char *>(v) + l * 128);
+        }
+    }
     grid_dependency_wait();  // gradients come from the kernels just before
     if (threadIdx.x == 0) {
         const float t = (float)(state[0] + 1);

@@ -45,6 +45,9 @@ bool pdl_enabled();
 
 #ifdef __CUDACC__
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Asks for a line to be brought into L2 without reading its value: safe before grid_dependency_wait() even
+// when the previous kernel may still be writing the line (L2 is where its writes land anyway).
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename... KArgs, typename... Args>

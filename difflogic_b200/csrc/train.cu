@@ -73,6 +73,8 @@ forward_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const
             offb[u] = __ldg(b + j) * batch;
         }
     }
+    // the neurons' weights are pulled towards L2 meanwhile (after an L2-cold start they come from DRAM)
+    if (tid < NB && n0 + tid < n_out) prefetch_l2(w + (n0 + tid) * 16);
     // Only the connection indices (fixed at construction) are read before this point: the weights may have
     // been written by the kernel just before this one (an optimizer step), the input certainly was.
     grid_dependency_wait();
@@ -152,6 +154,7 @@ backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, co
     if (active) {
         ia = __ldg(a + j) * batch;
         ib = __ldg(b + j) * batch;
+        if (w_mode == DL_W_LOGITS && lane == 0) prefetch_l2(w + j * 16);
     }
     grid_dependency_wait();      // weights, x and grad_y may have been written by the kernels just before
     grid_dependents_launch();
