@@ -297,6 +297,11 @@ static int launch_groupbitsum(const void *x, int32_t *out, int64_t n, int64_t ro
     int64_t kc = (96 * 1024) / per_class;
     if (kc > k) kc = k;
     if (kc < 1) kc = 1;
+    // few column blocks (a short batch): spread the classes over more CTAs so that ~600 of them exist
+    const int64_t colblocks = ceil_div(ncols16, LANES);
+    int64_t class_blocks = ceil_div(592, colblocks);
+    if (class_blocks > k) class_blocks = k;
+    if (ceil_div(k, class_blocks) < kc) kc = ceil_div(k, class_blocks);
     // row chunks: enough tasks for the 256/LANES groups, and no chunk above the counter's range
     const int ng = kThreads / LANES;
     int64_t chunks = ceil_div(ng, kc);
@@ -390,16 +395,23 @@ extern "C" DL_API int dl_groupbitsum(const void *x, int32_t *out, int64_t n, int
     DL_REQUIRE(out && (x || n == 0), DL_ERR_INVALID_ARG, "dl_groupbitsum: null pointer");
     const int64_t row_bytes = words * (bit_count / 8);
     cudaStream_t st = as_stream(stream);
-    // DL_GROUPBITSUM_KERNEL=plain forces the register-staged kernel (for A/B measurements)
+    // DL_GROUPBITSUM_KERNEL=plain / staged forces one of the two kernels (for A/B measurements)
     const char *force = getenv("DL_GROUPBITSUM_KERNEL");
     const bool plain_only = force != nullptr && force[0] == 'p';
-    if (!plain_only && groupbitsum_tma_applicable(x, n, row_bytes, k))
+    const bool staged_only = force != nullptr && force[0] == 's';
+    // The staged kernel splits a class's rows over several units when (column blocks x classes) alone cannot fill
+    // the machine; a split costs a plane expansion and global atomics per unit, which only pays while a unit still
+    // streams a few hundred rows.  Shorter pieces go to the register kernel, which splits rows inside a CTA.
+    int64_t splits = ceil_div(8 * 148, ceil_div(row_bytes, 1024) * k);
+    if (splits < 1) splits = 1;
+    const bool enough_units = (n / k) / splits >= 256;
+    if (!plain_only && (enough_units || staged_only) && groupbitsum_tma_applicable(x, n, row_bytes, k))
         return launch_groupbitsum_tma(x, out, n, row_bytes, batch, k, st);
     if (n > 0 && row_bytes % 16 == 0 && aligned_to(x, 16)) {
         const int64_t ncols16 = row_bytes / 16;
-        // narrower column blocks when the batch alone cannot fill the machine
-        if (ncols16 >= 16 * 296) return launch_groupbitsum<16>(x, out, n, row_bytes, batch, k, st);
-        if (ncols16 >= 8 * 296) return launch_groupbitsum<8>(x, out, n, row_bytes, batch, k, st);
+        // 256-byte row segments when there are enough of them, narrower ones for very short rows
+        if (ncols16 >= 16 * 32) return launch_groupbitsum<16>(x, out, n, row_bytes, batch, k, st);
+        if (ncols16 >= 8 * 32) return launch_groupbitsum<8>(x, out, n, row_bytes, batch, k, st);
         return launch_groupbitsum<4>(x, out, n, row_bytes, batch, k, st);
     }
     const dim3 grid((unsigned)ceil_div(row_bytes, kThreads), (unsigned)k);
