@@ -176,10 +176,7 @@ class LogicLayer(torch.nn.Module):
         """
         assert not self.training
         assert isinstance(x, PackBitsTensor)
-        assert x.t.shape[0] == self.in_dim, (x.t.shape, self.in_dim)
-
-        a, b = self.indices
-        x.t = ops.eval_packed(x.t, a, b, self._gate_ids())
+        x._push_layer(self)  # evaluated when x.t is read, or fused with the other layers by GroupSum
         return x
 
     def _gate_ids(self):
@@ -191,6 +188,15 @@ class LogicLayer(torch.nn.Module):
             with torch.no_grad():
                 cached = (key, ops.argmax_gates(w.detach().contiguous()))
             self._gate_cache = cached
+        return cached[1]
+
+    def _packed_descriptors(self, gate):
+        """uint32 {a:14 | b:14 | gate:4} per neuron for the whole-network eval kernel, cached per gate tensor."""
+        cached = getattr(self, '_desc_cache', None)
+        if cached is None or cached[0] is not gate:
+            a, b = self.indices
+            cached = (gate, ops.pack_net_layer(a, b, gate, self.in_dim))
+            self._desc_cache = cached
         return cached[1]
 
     def extra_repr(self):

@@ -3,7 +3,17 @@
 Drop-in for the reference class (difflogic/packbitstensor.py:6-41): `.t` is the packed tensor
 `[features, ceil(batch / bit_count)]` of dtype int{bit_count}, `.pad_len` the number of unused
 high bits in the last word, sample s being bit s % bit_count (LSB first) of word s // bit_count.
+
+Evaluation is lazy.  A LogicLayer in eval mode does not compute at once; it appends itself to the
+tensor's list of pending layers.  Reading `.t` runs the pending layers one kernel per layer, exactly
+as the reference does.  `group_sum(k)` -- what GroupSum calls -- hands the packed input, all pending
+layers and the bit-sum to ONE kernel when the network fits it (ops.eval_net_packed: activations stay
+in shared memory), and otherwise falls back to layer by layer.  Both give identical counts; the
+in-place semantics of the reference (the layer returns the same object, `.t` then holds the layer's
+output) are kept.  DL_FUSED_EVAL=0 in the environment turns the single-kernel path off.
 """
+import os
+
 import numpy as np
 import torch
 
@@ -16,13 +26,14 @@ class PackBitsTensor:
 
         self.bit_count = bit_count
         self.device = device
+        self._pending = []
 
         if device == 'cuda' or (isinstance(device, (str, torch.device)) and torch.device(device).type == 'cuda'):
             t = t.to(device)
             if t.dtype != torch.bool:
                 t = t != 0
             # transpose and pack in one kernel, straight from the batch-major matrix
-            self.t, self.pad_len = ops.packbits_batch_major(t.contiguous(), self.bit_count)
+            self._t, self.pad_len = ops.packbits_batch_major(t.contiguous(), self.bit_count)
         else:
             raise NotImplementedError(device)
 
@@ -32,12 +43,44 @@ class PackBitsTensor:
         self = cls.__new__(cls)
         self.bit_count = ops.bits_of(words)
         self.device = device
-        self.t = words
+        self._t = words
+        self._pending = []
         self.pad_len = int(pad_len)
         return self
 
+    # -- lazy layer application ------------------------------------------------------------------
+
+    @property
+    def t(self):
+        """The packed tensor after every layer applied so far (pending layers run now, one kernel each)."""
+        self._materialize()
+        return self._t
+
+    @t.setter
+    def t(self, value):
+        self._pending = []
+        self._t = value
+
+    def _push_layer(self, layer):
+        """Called by LogicLayer.forward_cuda_eval: remember the layer (its connections and current arg-max gates)."""
+        rows = self._pending[-1][0].out_dim if self._pending else self._t.shape[0]
+        assert rows == layer.in_dim, ((rows,), layer.in_dim)
+        self._pending.append((layer, layer._gate_ids()))
+
+    def _materialize(self):
+        pending, self._pending = self._pending, []
+        for layer, gate in pending:
+            a, b = layer.indices
+            self._t = ops.eval_packed(self._t, a, b, gate)
+
     def group_sum(self, k):
         assert torch.device(self.device).type == 'cuda', self.device
+        if self._pending and os.environ.get("DL_FUSED_EVAL", "1") != "0":
+            widths = [self._t.shape[0]] + [layer.out_dim for layer, _ in self._pending]
+            row_bytes = self._t.shape[1] * self._t.element_size()
+            if ops.fused_net_fits(widths, row_bytes):
+                metas = [layer._packed_descriptors(gate) for layer, gate in self._pending]
+                return ops.eval_net_packed(self._t, metas, widths, self.pad_len, k)
         return ops.groupbitsum(self.t, self.pad_len, k)
 
     def flatten(self, start_dim=0, end_dim=-1, **kwargs):

@@ -318,3 +318,54 @@ def test_cross_entropy_matches_torch(shape):
     # a view of a feature-major GroupSum output works too
     c = logits.t().contiguous().t().requires_grad_(True)
     assert abs(CrossEntropyLoss()(c, target).item() - lb.item()) <= 1e-5 * abs(lb.item()) + 1e-7
+
+
+@pytest.mark.parametrize("case", [
+    # dims, k, batch, bit_count
+    ([100, 640, 640, 320], 10, 5000, 64),
+    ([784, 8000, 8000, 8000, 8000], 10, 1000, 64),
+    ([33, 50, 70, 36], 3, 777, 64),          # ragged widths (not multiples of 4), words not a multiple of 4
+    ([20, 48], 4, 130, 64),                  # a single layer
+    ([64, 128, 96], 2, 4096 + 64, 32),       # 32-bit words (rows a multiple of 8 bytes)
+    ([64, 128, 96], 96, 300, 64),            # more classes than warps per round
+    ([16, 16000, 16000, 10000], 1, 200, 64),  # close to the shared-memory limit, a single class
+])
+def test_whole_network_packed_kernel_equals_layer_by_layer(case, monkeypatch):
+    dims, k, batch, bits = case
+    torch.manual_seed(sum(dims) + k)
+    net = O.OracleNet.build(dims, k, 1.0)
+    model = build_model(dims, k, 1.0, net.weights, net.idx_a, net.idx_b)
+    model.eval()
+    x = torch.rand(batch, dims[0]) < 0.4
+    from difflogic_b200 import ops
+    row_bytes = -(-batch // bits) * bits // 8
+    assert ops.fused_net_fits(dims, row_bytes) == (row_bytes % 8 == 0)
+    with torch.no_grad():
+        fused = model(D.PackBitsTensor(x.cuda(), bit_count=bits))
+        monkeypatch.setenv("DL_FUSED_EVAL", "0")
+        layerwise = model(D.PackBitsTensor(x.cuda(), bit_count=bits))
+    assert torch.equal(fused, layerwise)
+    if batch <= 1000:
+        ref = O.c_packed_net_counts(x.numpy(), net.idx_a, net.idx_b, net.gate_ids(), k)
+        assert np.array_equal(fused.cpu().numpy(), ref)
+
+
+def test_packbitstensor_is_lazy_but_keeps_the_in_place_contract():
+    torch.manual_seed(0)
+    l1, l2 = D.LogicLayer(20, 48), D.LogicLayer(48, 40)
+    l1.eval(); l2.eval()
+    p = D.PackBitsTensor(torch.rand(70, 20, device='cuda') < 0.5, bit_count=64)
+    base = p.t.clone()
+    assert l2(l1(p)) is p
+    assert p.t.shape == (40, 2)                      # reading .t runs both layers
+    from difflogic_b200 import ops
+    step1 = ops.eval_packed(base, l1.indices[0], l1.indices[1], l1._gate_ids())
+    step2 = ops.eval_packed(step1, l2.indices[0], l2.indices[1], l2._gate_ids())
+    assert torch.equal(p.t, step2)
+    with pytest.raises(AssertionError):
+        l1(p)                                        # 40 rows do not fit a layer with 20 inputs
+    # a network too wide for the fused kernel still works (layer by layer)
+    wide = D.LogicLayer(20, 20000)
+    wide.eval()
+    q = D.PackBitsTensor(torch.rand(64, 20, device='cuda') < 0.5, bit_count=64)
+    assert D.GroupSum(10)(wide(q)).shape == (64, 10)
