@@ -328,7 +328,7 @@ def test_cross_entropy_matches_torch(shape):
     ([20, 48], 4, 130, 64),                  # a single layer
     ([64, 128, 96], 2, 4096 + 64, 32),       # 32-bit words (rows a multiple of 8 bytes)
     ([64, 128, 96], 96, 300, 64),            # more classes than warps per round
-    ([16, 16000, 16000, 10000], 1, 200, 64),  # close to the shared-memory limit, a single class
+    ([16, 13000, 13000, 9000], 1, 200, 64),   # close to the shared-memory limit, a single class
 ])
 def test_whole_network_packed_kernel_equals_layer_by_layer(case, monkeypatch):
     dims, k, batch, bits = case
@@ -341,6 +341,7 @@ def test_whole_network_packed_kernel_equals_layer_by_layer(case, monkeypatch):
     row_bytes = -(-batch // bits) * bits // 8
     assert ops.fused_net_fits(dims, row_bytes) == (row_bytes % 8 == 0)
     with torch.no_grad():
+        monkeypatch.setenv("DL_FUSED_EVAL", "1")
         fused = model(D.PackBitsTensor(x.cuda(), bit_count=bits))
         monkeypatch.setenv("DL_FUSED_EVAL", "0")
         layerwise = model(D.PackBitsTensor(x.cuda(), bit_count=bits))
