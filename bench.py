@@ -267,21 +267,16 @@ def bench_train(args, rank, world):
     t_dev = all_max(t_dev, world)
     final_loss = float(loss.item())
 
-    # ---- end to end: pinned host batch -> H2D -> step -> loss read back on the host, every step.
-    # The input pipeline is double-buffered, as a data loader would do it: while the step on batch i runs, batch
-    # i+1 is copied in on a side stream.  Every timed step contains one whole H2D copy, the step and the D2H read.
+    # ---- end to end: pinned host batch -> H2D -> step -> loss read back on the host, every step
     for i in range(W):
         step(hx[i % pool], hy[i % pool]).item()
-    step.stage(hx[0], hy[0])
     barrier(world)
     t_e2e = 0.0
     for i in range(K):
         flush.zero_()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        step.stage(hx[(i + 1) % pool], hy[(i + 1) % pool])
-        step.run_staged().item()
-        step._copy_stream.synchronize()
+        step(hx[i % pool], hy[i % pool]).item()
         t_e2e += time.perf_counter() - t0
     barrier(world)
     t_e2e = all_max(t_e2e, world)

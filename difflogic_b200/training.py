@@ -140,40 +140,6 @@ class TrainStep:
         self._graph = graph
         return self
 
-    # -- input staging: the copy of the next batch overlaps the current step ------------------------
-
-    def stage(self, x_host, y_host):
-        """Starts the host-to-device copy of a batch (pinned host tensors) on a side stream and returns at once.
-        The batch is consumed by the next `run_staged()`.  Two staging buffers alternate, so a batch can be staged
-        while the step on the previous one is still running."""
-        if getattr(self, "_copy_stream", None) is None:
-            self._copy_stream = torch.cuda.Stream()
-            self._staged = [None, None]
-            self._stage_events = [torch.cuda.Event(), torch.cuda.Event()]
-            self._stage_free = [torch.cuda.Event(), torch.cuda.Event()]
-            self._stage_next = 0
-            self._stage_ready = []
-        slot = self._stage_next
-        self._stage_next ^= 1
-        if self._staged[slot] is None:
-            self._staged[slot] = (torch.empty_like(x_host, device="cuda"), torch.empty_like(y_host, device="cuda"))
-        else:
-            self._copy_stream.wait_event(self._stage_free[slot])   # the step that read this slot has been queued
-        with torch.cuda.stream(self._copy_stream):
-            self._staged[slot][0].copy_(x_host, non_blocking=True)
-            self._staged[slot][1].copy_(y_host, non_blocking=True)
-            self._stage_events[slot].record(self._copy_stream)
-        self._stage_ready.append(slot)
-
-    def run_staged(self):
-        """One step on the oldest staged batch; returns the loss (device scalar)."""
-        slot = self._stage_ready.pop(0)
-        torch.cuda.current_stream().wait_event(self._stage_events[slot])
-        x, y = self._staged[slot]
-        loss = self(x, y)
-        self._stage_free[slot].record(torch.cuda.current_stream())
-        return loss
-
     @property
     def static_inputs(self):
         return self._static_x, self._static_y
