@@ -223,6 +223,8 @@ def bench_train(args, rank, world):
         from difflogic_b200.optim import FlatAdam
         opt = FlatAdam(model.parameters(), lr=TRAIN_LR)
     group = dist.group.WORLD if world > 1 else None
+    if world > 1 and args.exchange == "peer" and args.optimizer == "flat":
+        opt.enable_exchange(group)
     if args.loss == "torch":
         loss_fn = torch.nn.CrossEntropyLoss()
     else:
@@ -527,6 +529,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--loss", default="fused", choices=["fused", "torch"],
                     help="fused: difflogic_b200.losses.CrossEntropyLoss (one kernel each way); torch: torch.nn.CrossEntropyLoss")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: peer = gradient exchange + Adam in one kernel over peer memory; nccl = NCCL all-reduce")
     ap.add_argument("--skip-packed", action="store_true")
     ap.add_argument("--optimizer", default="flat", choices=["flat", "torch"],
                     help="flat: difflogic_b200.optim.FlatAdam (one kernel); torch: torch.optim.Adam(capturable, fused)")
@@ -566,7 +570,9 @@ def main():
             "config": {"workload": "train step: Flatten -> LogicLayer(784,16000) -> 4 x LogicLayer(16000,16000) -> "
                                    "GroupSum(10, tau=30), CrossEntropy, Adam lr=0.01",
                        "batch_per_gpu": TRAIN_BATCH, "global_batch": TRAIN_BATCH * world,
-                       "parallelism": "batch-sharded replicas x%d, weight-gradient all-reduce" % world,
+                       "parallelism": "batch-sharded replicas x%d, weight-gradient exchange: %s" % (
+                           world, "none" if world == 1 else ("reduce-scatter + Adam + all-gather in one kernel over peer memory"
+                                                             if args.exchange == "peer" and args.optimizer == "flat" else "NCCL all-reduce")),
                        "execution": "whole step replayed as one CUDA graph",
                        "loss": "CrossEntropy (%s)" % ("difflogic_b200.losses.CrossEntropyLoss" if args.loss == "fused"
                                                       else "torch.nn.CrossEntropyLoss"),

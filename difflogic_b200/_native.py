@@ -45,6 +45,12 @@ SIGNATURES = {
     "dl_groupsum_f32_static": (_int, [_ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),
     "dl_cross_entropy_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr]),
     "dl_cross_entropy_backward_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr]),
+    "dl_comm_alloc": (_int, [ctypes.c_size_t, _ptr]),
+    "dl_comm_free": (_int, [_ptr]),
+    "dl_comm_export": (_int, [_ptr, _ptr]),
+    "dl_comm_import": (_int, [_ptr, _ptr]),
+    "dl_comm_close": (_int, [_ptr]),
+    "dl_adam_exchange_step_f32": (_int, [_ptr, _ptr, _ptr, _int, _int, _ptr, _ptr, _i64, _f32, _f32, _f32, _f32, _ptr, _ptr]),
     "dl_adam_step_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _f32, _f32, _f32, _f32, _f32, _ptr, _ptr]),
 }
 

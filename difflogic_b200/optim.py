@@ -49,6 +49,80 @@ class FlatAdam(torch.optim.Optimizer):
                 off += sz
         self.grad_scale = 1.0
 
+    # -- batch-sharded training: exchange and step in one kernel over peer memory -------------------------------
+
+    def enable_exchange(self, group=None):
+        """Switches to the peer-memory exchange (dl_adam_exchange_step_f32): the flat parameter and gradient buffers
+        move into memory that the other ranks of `group` (one process per GPU on this machine) map through CUDA IPC;
+        `step()` then averages the gradients over the ranks, applies Adam to this rank's slice and distributes the new
+        parameters in a single kernel.  No NCCL call is made per step.  Collective: every rank of the group calls it."""
+        import ctypes
+        import torch.distributed as dist
+        lib = N.lib()
+        world = dist.get_world_size(group)
+        rank = dist.get_rank(group)
+        dev = self.flat_param.device
+        n = self.flat_param.numel()
+        assert n % 4 == 0
+
+        def alloc(nbytes):
+            ptr = ctypes.c_void_p()
+            with torch.cuda.device(dev):
+                N.check(lib.dl_comm_alloc(nbytes, ctypes.byref(ptr)))
+            return ptr.value
+
+        def as_tensor(ptr, count, typestr, dtype):
+            holder = type("_Raw", (), {})()
+            holder.__cuda_array_interface__ = {"shape": (count,), "typestr": typestr, "data": (ptr, False), "version": 2}
+            t = torch.as_tensor(holder, device=dev)
+            assert t.dtype == dtype and t.data_ptr() == ptr
+            return t
+
+        ptrs = {"param": alloc(n * 4), "grad": alloc(n * 4), "flags": alloc(256)}
+        new_param = as_tensor(ptrs["param"], n, "<f4", torch.float32)
+        new_grad = as_tensor(ptrs["grad"], n, "<f4", torch.float32)
+        with torch.no_grad():
+            new_param.copy_(self.flat_param)
+            dist.broadcast(new_param, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            for p in self._params:
+                off, cnt = self._slices[p]
+                p.data = new_param[off:off + cnt].view_as(p)
+                p._dl_grad_out = new_grad[off:off + cnt].view_as(p)
+        self.flat_param, self.flat_grad = new_param, new_grad
+
+        handles = {}
+        for name, ptr in ptrs.items():
+            buf = (ctypes.c_ubyte * 64)()
+            N.check(lib.dl_comm_export(ptr, buf))
+            handles[name] = bytes(buf)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, handles, group=group)
+        self._peer_ptrs = {}
+        for name in ptrs:
+            arr = (ctypes.c_void_p * world)()
+            for r in range(world):
+                if r == rank:
+                    arr[r] = ptrs[name]
+                else:
+                    out = ctypes.c_void_p()
+                    with torch.cuda.device(dev):
+                        N.check(lib.dl_comm_import(gathered[r][name], ctypes.byref(out)))
+                    arr[r] = out.value
+            self._peer_ptrs[name] = arr
+        per = -(-(n // 4) // world) * 4
+        self.exp_avg = torch.zeros(per, dtype=torch.float32, device=dev)       # moments of this rank's slice only
+        self.exp_avg_sq = torch.zeros(per, dtype=torch.float32, device=dev)
+        self.state_t = torch.zeros(4, dtype=torch.int32, device=dev)
+        self._exchange = (rank, world)
+        self.exchange_enabled = True
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)
+        return self
+
+    def exchange_error(self):
+        """True when a wait for a peer ever ran out of its poll limit (synchronises)."""
+        return bool(int(self.state_t[2].item())) if getattr(self, "exchange_enabled", False) else False
+
     def grad_view(self, p):
         off, n = self._slices[p]
         return self.flat_grad[off:off + n].view_as(p)
@@ -70,6 +144,15 @@ class FlatAdam(torch.optim.Optimizer):
                 self.grad_view(p).copy_(p.grad)
         g = self.param_groups[0]
         beta1, beta2 = g['betas']
+        if getattr(self, "exchange_enabled", False):
+            rank, world = self._exchange
+            with torch.cuda.device(self.flat_param.device):
+                N.check(N.lib().dl_adam_exchange_step_f32(self._peer_ptrs["param"], self._peer_ptrs["grad"],
+                                                          self._peer_ptrs["flags"], rank, world, self.exp_avg.data_ptr(),
+                                                          self.exp_avg_sq.data_ptr(), self.flat_param.numel(), float(g['lr']),
+                                                          float(beta1), float(beta2), float(g['eps']),
+                                                          self.state_t.data_ptr(), N.stream_of(self.flat_param)))
+            return loss
         with torch.cuda.device(self.flat_param.device):
             N.check(N.lib().dl_adam_step_f32(self.flat_param.data_ptr(), self.flat_grad.data_ptr(), self.exp_avg.data_ptr(),
                                              self.exp_avg_sq.data_ptr(), self.flat_param.numel(), float(g['lr']), float(beta1),

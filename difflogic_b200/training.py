@@ -45,7 +45,9 @@ class TrainStep:
         self._bucket_slices = []   # flat gradient slice of each bucket
         self._bucket_sizes = []    # parameters per bucket
         self._pending = []
-        if self.group is not None and self.world_size > 1:
+        # FlatAdam.enable_exchange(): gradients are averaged inside the optimizer's own kernel, nothing to do here
+        self._exchange_in_optimizer = bool(getattr(optimizer, "exchange_enabled", False))
+        if self.group is not None and self.world_size > 1 and not self._exchange_in_optimizer:
             if self._on_gpu:
                 self._comm_stream = torch.cuda.Stream()
                 self._plan_buckets(max(1, int(buckets)))

@@ -3,8 +3,8 @@
  *
  * Every entry point takes plain device pointers and sizes, launches asynchronously on the
  * stream it is given (a cudaStream_t passed as void*; NULL is the legacy default stream),
- * never allocates or frees device memory, never synchronises the device and never exits the
- * process.  The return value is a status code (DL_OK == 0).  After a non-zero status,
+ * never allocates or frees device memory (the dl_comm_* set-up helpers excepted), never
+ * synchronises the device and never exits the process.  The return value is a status code (DL_OK == 0).  After a non-zero status,
  * dl_last_error_string() gives a message for the calling thread.
  *
  * Layouts.  Float activations are feature-major: x[n_in][batch], y[n_out][batch], batch is
@@ -242,6 +242,35 @@ DL_API int dl_cross_entropy_backward_f32(const float *probs, const int64_t *targ
  * ---------------------------------------------------------------------------------------- */
 DL_API int dl_adam_step_f32(float *param, const float *grad, float *exp_avg, float *exp_avg_sq, int64_t n, float lr,
                             float beta1, float beta2, float eps, float grad_scale, int32_t *state, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Batch-sharded training: gradient exchange and Adam in one kernel over peer memory.
+ * No counterpart in the reference (it has no multi-GPU code); it takes the place of an NCCL
+ * all-reduce of the [out_dim,16] gradients followed by dl_adam_step_f32 on every rank.
+ *
+ * Set-up (these DO allocate, once): every rank allocates its flat parameter buffer, flat gradient
+ * buffer and 256 bytes of flag words with dl_comm_alloc, exports them with dl_comm_export (64-byte
+ * handles, to be passed to the other processes of the machine by any means) and maps its peers'
+ * with dl_comm_import.
+ *
+ * Per step: dl_adam_exchange_step_f32 gets HOST arrays of `world` device pointers (index = rank,
+ * own entry = own buffers).  Rank r waits until all ranks' gradients are complete, averages slice r
+ * of all ranks' gradients (peer loads), applies Adam to slice r with its moments (exp_avg,
+ * exp_avg_sq hold ceil(n/4/world)*4 floats), writes the new slice into every rank's parameter
+ * buffer and waits until all ranks have done the same.  n: floats per buffer, a multiple of 4.
+ * state: four int32 on the device, zero at first: {steps done, ticket, error, unused}; error
+ * becomes 1 when a wait for a peer ran out of its poll limit (the step then used stale data).
+ * All ranks must call it the same number of times; the kernels of one step must be able to run at
+ * the same time, i.e. one rank per GPU.
+ * ---------------------------------------------------------------------------------------- */
+DL_API int dl_comm_alloc(size_t bytes, void **ptr);
+DL_API int dl_comm_free(void *ptr);
+DL_API int dl_comm_export(void *ptr, unsigned char *handle);
+DL_API int dl_comm_import(const unsigned char *handle, void **ptr);
+DL_API int dl_comm_close(void *ptr);
+DL_API int dl_adam_exchange_step_f32(void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs, int rank,
+                                     int world, float *exp_avg, float *exp_avg_sq, int64_t n, float lr, float beta1,
+                                     float beta2, float eps, int32_t *state, void *stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,114 @@
+"""Batch-sharded training on more than one GPU: the peer-memory exchange kernel against the NCCL all-reduce path.
+Runs child processes, one per GPU; skipped where fewer than two GPUs are visible.  The single-rank case of the
+exchange kernel (no peers) runs on one GPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import logic_oracle as O
+from tests.helpers import build_model, logic_layers
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _make(dims, k, tau, seed):
+    torch.manual_seed(seed)
+    net = O.OracleNet.build(dims, k, tau)
+    return net, build_model(dims, k, tau, net.weights, net.idx_a, net.idx_b)
+
+
+def test_exchange_kernel_single_rank_equals_flat_adam(tmp_path):
+    from difflogic_b200.optim import FlatAdam
+    dist.init_process_group("gloo", init_method="file://%s" % (tmp_path / "store"), rank=0, world_size=1)
+    try:
+        dims = [30, 64, 52]
+        _, m1 = _make(dims, 4, 2.0, 5)
+        _, m2 = _make(dims, 4, 2.0, 5)
+        o1 = FlatAdam(m1.parameters(), lr=0.01)
+        o2 = FlatAdam(m2.parameters(), lr=0.01).enable_exchange(dist.group.WORLD)
+        x = (torch.rand(40, 30, generator=torch.Generator().manual_seed(1)) < 0.5).float().cuda()
+        y = torch.randint(0, 4, (40,), generator=torch.Generator().manual_seed(2)).cuda()
+        for _ in range(4):
+            for m, o in ((m1, o1), (m2, o2)):
+                m.train()
+                loss = torch.nn.functional.cross_entropy(m(x), y)
+                o.zero_grad()
+                loss.backward()
+                o.step()
+        for l1, l2 in zip(logic_layers(m1), logic_layers(m2)):
+            assert torch.equal(l1.weights, l2.weights)
+        assert not o2.exchange_error() and int(o2.state_t[0].item()) == 4
+    finally:
+        dist.destroy_process_group()
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from difflogic_b200.optim import FlatAdam
+        from difflogic_b200.training import TrainStep, shard_range
+        dims = [24, 160, 160, 80]
+        g = torch.Generator().manual_seed(3)
+        xs = [(torch.rand(64, 24, generator=g) < 0.4).float() for _ in range(3)]
+        ys = [torch.randint(0, 4, (64,), generator=g) for _ in range(3)]
+        lo, hi = shard_range(64, rank, world)
+        results = {}
+        for mode in ("nccl", "peer", "peer_graph"):
+            _, model = _make(dims, 4, 3.0, 11)
+            model.train()
+            opt = FlatAdam(model.parameters(), lr=0.01)
+            if mode != "nccl":
+                opt.enable_exchange(dist.group.WORLD)
+            step = TrainStep(model, opt, process_group=dist.group.WORLD, buckets=1)
+            if mode == "peer_graph":
+                step.capture(xs[0][lo:hi].cuda(), ys[0][lo:hi].cuda(), warmup=0)
+            losses = [float(step(x[lo:hi].cuda(), y[lo:hi].cuda()).item()) for x, y in zip(xs, ys)]
+            torch.cuda.synchronize()
+            results[mode] = {"loss": losses, "w": [l.weights.detach().cpu().clone() for l in logic_layers(model)],
+                             "err": opt.exchange_error()}
+            step.close()
+            dist.barrier()
+        torch.save(results, os.path.join(out_dir, "rank%d.pt" % rank))
+    finally:
+        torch.cuda.synchronize()
+        dist.barrier()
+        os._exit(0)  # skip the NCCL teardown (it can block while graphs with captured kernels are alive)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_memory_exchange_matches_nccl_all_reduce(tmp_path):
+    world = 2
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            pytest.fail("a rank did not finish in time")
+        assert p.exitcode == 0
+    res = [torch.load(os.path.join(tmp_path, "rank%d.pt" % r)) for r in range(world)]
+    for mode in ("peer", "peer_graph"):
+        assert not res[0][mode]["err"] and not res[1][mode]["err"]
+        for w0, w1 in zip(res[0][mode]["w"], res[1][mode]["w"]):
+            assert torch.equal(w0, w1)                       # replicas stay identical
+        for w, ref in zip(res[0][mode]["w"], res[0]["nccl"]["w"]):
+            assert torch.allclose(w, ref, rtol=1e-5, atol=1e-6)   # same update as all-reduce + Adam
+    assert torch.allclose(torch.tensor(res[0]["peer"]["loss"]), torch.tensor(res[0]["nccl"]["loss"]), rtol=1e-5)
