@@ -256,7 +256,10 @@ def bench_train(args, rank, world):
     pairs = []
     with sampler:
         for i in range(K):
-            flush.zero_()
+            if not args.no_flush:
+                flush.zero_()
+            else:
+                flush[:1 << 20].zero_()  # diagnostic: keeps the launch queue ahead without evicting L2
             s, e = event_pair()
             s.record()
             sx.copy_(dx[i % pool], non_blocking=True)
@@ -535,6 +538,7 @@ def main():
     ap.add_argument("--optimizer", default="flat", choices=["flat", "torch"],
                     help="flat: difflogic_b200.optim.FlatAdam (one kernel); torch: torch.optim.Adam(capturable, fused)")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--no-flush", action="store_true", help="diagnostic only: do not flush L2 between the timed steps")
     ap.add_argument("--buckets", type=int, default=2, help="all-reduce pieces of the flat gradient buffer (N > 1)")
     ap.add_argument("--skip-kernel-timing", action="store_true", help="leave out the per-kernel roofline timing")
     args = ap.parse_args()

@@ -19,6 +19,19 @@ from .functional import GradFactor, bin_op_s, get_unique_connections
 from .packbitstensor import PackBitsTensor
 
 
+# Optional side stream for backward_w.  Inside one layer, backward_x (which the next layer's backward waits for)
+# and backward_w (which only the optimizer waits for) are independent; with a side stream set, backward_w leaves
+# the critical path of the backward pass.  Whoever sets it must make the main stream wait for it before the
+# gradients are used (difflogic_b200.training.TrainStep does both).
+_backward_w_stream = None
+
+
+def set_backward_w_stream(stream):
+    """Sets (or, with None, clears) the CUDA stream on which LogicLayer's backward_w kernels are launched."""
+    global _backward_w_stream
+    _backward_w_stream = stream
+
+
 def _is_cuda_device(device):
     try:
         return torch.device(device).type == 'cuda'
@@ -255,14 +268,25 @@ class LogicLayerFunction(torch.autograd.Function):
         x, weights, a, b, start, plan, coef = ctx.saved_tensors
         grad_y = grad_y.contiguous()
         grad_x = grad_w = None
-        if ctx.needs_input_grad[0]:
+        side = _backward_w_stream if (ctx.needs_input_grad[0] and ctx.needs_input_grad[1]) else None
+        if side is not None:
+            # fork: backward_w on the side stream, backward_x stays on the stream the next layer is waiting on
+            main = torch.cuda.current_stream(x.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                grad_w = ops.logic_backward_w(x, a, b, grad_y, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True)
+            for t in (x, grad_y, weights):
+                t.record_stream(side)
             grad_x = ops.logic_backward_x(x, coef, grad_y, start, plan, ctx.grad_factor, overlap=True)
-        if ctx.needs_input_grad[1]:
-            grad_w = ops.logic_backward_w(x, a, b, grad_y, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True)
-            if ctx.grad_out is not None:
-                # a fresh alias that nothing else references: autograd then adopts it as `weights.grad`
-                # instead of copying it, so the gradient stays inside the flat bucket
-                grad_w = grad_w.view(grad_w.shape)
+        else:
+            if ctx.needs_input_grad[0]:
+                grad_x = ops.logic_backward_x(x, coef, grad_y, start, plan, ctx.grad_factor, overlap=True)
+            if ctx.needs_input_grad[1]:
+                grad_w = ops.logic_backward_w(x, a, b, grad_y, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True)
+        if grad_w is not None and ctx.grad_out is not None:
+            # a fresh alias that nothing else references: autograd then adopts it as `weights.grad`
+            # instead of copying it, so the gradient stays inside the flat bucket
+            grad_w = grad_w.view(grad_w.shape)
         return grad_x, grad_w, None, None, None, None, None, None
 
 

@@ -39,6 +39,7 @@ class TrainStep:
         self._graph = None
         self._static_x = self._static_y = self._static_loss = None
         self._comm_stream = None
+        self._bw_stream = torch.cuda.Stream() if all(p.is_cuda for p in self.params) else None
         self._hooks = []
         self._on_gpu = all(p.is_cuda for p in self.params)
         self._bucket_of = {}       # param -> bucket index
@@ -107,10 +108,21 @@ class TrainStep:
     # -- the step --------------------------------------------------------------------------------
 
     def _step(self, x, y):
+        from . import difflogic as _dl
         self._pending = list(self._bucket_sizes)
         loss = self.loss_fn(self.model(x), y)
         self.optimizer.zero_grad(set_to_none=True)
-        loss.backward()
+        # backward_w of every layer runs on a side stream, off the chain of backward_x kernels -- unless gradient
+        # hooks (the NCCL path) need the gradients in stream order
+        side = self._bw_stream if (self._on_gpu and not self._hooks) else None
+        if side is not None:
+            _dl.set_backward_w_stream(side)
+        try:
+            loss.backward()
+        finally:
+            if side is not None:
+                _dl.set_backward_w_stream(None)
+                torch.cuda.current_stream().wait_stream(side)
         self._join_comm()
         self.optimizer.step()
         return loss.detach()
