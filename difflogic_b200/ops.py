@@ -214,6 +214,25 @@ def packbits_batch_major(t, bit_count):
     return out, (bit_count - batch % bit_count) % bit_count
 
 
+def threshold_packbits_batch_major(t, thresholds, bit_count):
+    """uint8 [batch, n] -> (words [len(thresholds)*n, ceil(batch/bit_count)], pad_len); bit s of row i*n+f is
+    t[s, f] > thresholds[i] (thermometer encoding and packing in one kernel)."""
+    import ctypes
+    _check_bit_count(bit_count)
+    N.require_cuda(t)
+    _need(t.dim() == 2 and t.is_contiguous() and t.dtype == torch.uint8, "t must be a contiguous 2-D uint8 tensor")
+    thresholds = [int(v) for v in thresholds]
+    _need(1 <= len(thresholds) <= 16 and all(0 <= v <= 255 for v in thresholds), "1..16 thresholds in 0..255")
+    batch, n = t.shape
+    words = -(-batch // bit_count)
+    out = torch.empty((len(thresholds) * n, words), dtype=_BITS_TO_DTYPE[bit_count], device=t.device)
+    arr = (ctypes.c_ubyte * len(thresholds))(*thresholds)
+    with torch.cuda.device(t.device):
+        N.check(N.lib().dl_threshold_packbits_batch_major(t.data_ptr(), ctypes.addressof(arr), len(thresholds), out.data_ptr(),
+                                                          n, batch, bit_count, N.stream_of(t)))
+    return out, (bit_count - batch % bit_count) % bit_count
+
+
 def groupbitsum(x, pad_len, k):
     """words [n, W] -> int32 [W*bits - pad_len, k] class counts."""
     N.require_cuda(x)

@@ -50,6 +50,15 @@ class PackBitsTensor:
         self.pad_len = int(pad_len)
         return self
 
+    @classmethod
+    def from_uint8_thresholds(cls, t, thresholds=(63, 127, 191), bit_count=64, device='cuda'):
+        """Thermometer-encodes uint8 features (e.g. images `[batch, C, H, W]`) and packs them in one kernel.
+        Feature `i * n + f` of the result is `t[:, f] > thresholds[i]` with f running over the flattened trailing
+        dimensions -- the layout of `torch.cat([x > (i+1)/4 ...], dim=1)` followed by Flatten on `x = t / 255`."""
+        t = t.to(device).reshape(t.shape[0], -1).contiguous()
+        words, pad_len = ops.threshold_packbits_batch_major(t, thresholds, bit_count)
+        return cls.from_packed(words, pad_len, device=device)
+
     # -- lazy layer application ------------------------------------------------------------------
 
     @property

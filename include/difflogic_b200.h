@@ -154,6 +154,14 @@ DL_API int dl_packbits(const uint8_t *t, void *out, int64_t n, int64_t batch, in
 DL_API int dl_packbits_batch_major(const uint8_t *t, void *out, int64_t n, int64_t batch, int bit_count,
                             void *stream);
 
+/* Thermometer encoding + packing from uint8 features (SURVEY "next" item: the step before the path).
+ * t[batch][n] uint8 -> out[n_thresholds*n][words]: bit s of row (i*n + f) is t[s][f] > thresholds[i].
+ * thresholds is a HOST array (at most 16 entries).  Replaces the thermometer features of
+ * experiments/main.py:56-59 (pixel/255 > (i+1)/4 for i = 0..2, i.e. thresholds {63, 127, 191}) followed by
+ * PackBitsTensor(...) (difflogic/packbitstensor.py:15-16). */
+DL_API int dl_threshold_packbits_batch_major(const uint8_t *t, const uint8_t *thresholds, int n_thresholds, void *out,
+                                             int64_t n, int64_t batch, int bit_count, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Group bit-sum.
  * Replaces groupbitsum, difflogic_kernel.cu:666-700 (kernel :631-664), bound at

@@ -271,3 +271,18 @@ def test_bad_arguments_raise_like_the_reference():
     with pytest.raises(ValueError):
         ops.packbits(torch.zeros(3, 8, dtype=torch.bool, device="cuda"), 12)
     assert ops.logic_forward(x[:, :0].contiguous(), a, a, w)[0].shape == (3, 0)  # empty batch is fine
+
+
+@pytest.mark.parametrize("bits", [8, 64])
+@pytest.mark.parametrize("shape", [(37, 3, 4, 5), (1000, 3, 8, 8), (513, 1, 7, 9)])
+def test_thermometer_packing_from_uint8_images(bits, shape):
+    """uint8 pixels -> packed thermometer features, against the reference's float encoding followed by packing."""
+    import difflogic_b200 as D
+    g = torch.Generator().manual_seed(sum(shape))
+    img = torch.randint(0, 256, shape, dtype=torch.uint8, generator=g)
+    x = img.float() / 255.0
+    feats = torch.cat([(x > ((i + 1) / 4)) for i in range(3)], dim=1).reshape(shape[0], -1)   # experiments/main.py:57
+    ref, ref_pad = O.pack_bits(np.ascontiguousarray(feats.numpy().T), bits)
+    p = D.PackBitsTensor.from_uint8_thresholds(img.cuda(), (63, 127, 191), bit_count=bits)
+    assert p.pad_len == ref_pad and p.bit_count == bits
+    assert np.array_equal(p.t.cpu().numpy(), ref)
