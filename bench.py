@@ -254,20 +254,20 @@ def bench_train(args, rank, world):
         step.replay()
     barrier(world)
     pairs = []
-    with sampler:
-        for i in range(K):
-            if not args.no_flush:
-                flush.zero_()
-            else:
-                flush[:1 << 20].zero_()  # diagnostic: keeps the launch queue ahead without evicting L2
-            s, e = event_pair()
-            s.record()
-            sx.copy_(dx[i % pool], non_blocking=True)
-            sy.copy_(dy[i % pool], non_blocking=True)
-            loss = step.replay()
-            e.record()
-            pairs.append((s, e))
-        barrier(world)
+    sampler.__enter__()          # clocks are sampled over both timed loops (device-resident and end to end)
+    for i in range(K):
+        if not args.no_flush:
+            flush.zero_()
+        else:
+            flush[:1 << 20].zero_()  # diagnostic: keeps the launch queue ahead without evicting L2
+        s, e = event_pair()
+        s.record()
+        sx.copy_(dx[i % pool], non_blocking=True)
+        sy.copy_(dy[i % pool], non_blocking=True)
+        loss = step.replay()
+        e.record()
+        pairs.append((s, e))
+    barrier(world)
     t_dev = sum(s.elapsed_time(e) for s, e in pairs) * 1e-3
     t_dev = all_max(t_dev, world)
     final_loss = float(loss.item())
@@ -284,6 +284,7 @@ def bench_train(args, rank, world):
         step(hx[i % pool], hy[i % pool]).item()
         t_e2e += time.perf_counter() - t0
     barrier(world)
+    sampler.__exit__(None, None, None)
     t_e2e = all_max(t_e2e, world)
 
     bytes_step, per_kernel = train_bytes_per_step(TRAIN_DIMS, TRAIN_BATCH, TRAIN_K)
