@@ -40,12 +40,12 @@ P_ONE = 0.19
 METRIC = "train step samples/s"
 UNIT = "samples/s"
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures summarised under
-# profiles/; None until a capture of that kernel exists.
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures of single launches
+# (summaries are kept in the profiles folder); None where no capture of that kernel exists.
 NCU_TRAFFIC = {
-    # profiles/train_kernels_16000x16000_batch128.md: cold-cache captures; inside a step the operands are L2-resident
+    # training kernels at 16000 x 16000, batch 128: cold-cache captures; inside a step the operands are L2-resident
     "forward": 9.49e6, "backward_w": 17.68e6, "backward_x": 17.04e6,
-    # profiles/eval_tma_kernel_8000x8000_4096words.md and groupbitsum_tma_kernel_...: captured at 4096 words per row and
+    # packed eval and group bit-sum: captured at 8000 rows x 4096 words per row and
     # scaled by 4 to the 16384 words of the bench (traffic is proportional to the row length; the part of the
     # output still dirty in L2 at the end of the kernel, ~40 MB, is not)
     "eval_packed": 4 * 262.79e6 + (4 * 262.14e6 - 40.7e6), "groupbitsum": 4 * 272.67e6 + (4 * 10.49e6 - 2.3e6),

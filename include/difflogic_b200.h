@@ -154,7 +154,7 @@ DL_API int dl_packbits(const uint8_t *t, void *out, int64_t n, int64_t batch, in
 DL_API int dl_packbits_batch_major(const uint8_t *t, void *out, int64_t n, int64_t batch, int bit_count,
                             void *stream);
 
-/* Thermometer encoding + packing from uint8 features (SURVEY "next" item: the step before the path).
+/* Thermometer encoding + packing from uint8 features (the step in front of the packed path).
  * t[batch][n] uint8 -> out[n_thresholds*n][words]: bit s of row (i*n + f) is t[s][f] > thresholds[i].
  * thresholds is a HOST array (at most 16 entries).  Replaces the thermometer features of
  * experiments/main.py:56-59 (pixel/255 > (i+1)/4 for i = 0..2, i.e. thresholds {63, 127, 191}) followed by
