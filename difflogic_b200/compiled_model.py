@@ -125,6 +125,12 @@ class CompiledLogicNet(torch.nn.Module):
                 for j, (ga, gb, op) in enumerate(zip(a_idx, b_idx, ops))]
 
     def get_c_code(self):
+        """The whole network as one C translation unit."""
+        return self._c_sources(1)[0]
+
+    def _c_sources(self, n_units):
+        """C source split into `n_units` translation units (the gate functions are spread over them; unit 0 also
+        holds logic_gate_net and apply_logic_gate_net), so that several compiler processes can work in parallel."""
         word = BITS_TO_DTYPE[self.num_bits]
         bits = self.num_bits
         prefix_sums = [0]
@@ -136,15 +142,21 @@ class CompiledLogicNet(torch.nn.Module):
         for layer_id, (layer_a, layer_b, layer_op) in enumerate(self.layers):
             statements.extend(self.get_layer_code(layer_a, layer_b, layer_op, layer_id, prefix_sums))
 
-        code = ["#include <stddef.h>", "#include <stdlib.h>", "#include <stdbool.h>", "#include <string.h>", ""]
-        parts = []
-        for start in range(0, len(statements), _STATEMENTS_PER_FUNCTION):
-            name = "gates_{}".format(len(parts))
-            parts.append(name)
-            code.append("static void {}({w} const *inp, {w} *v, {w} *out) {{".format(name, w=word))
-            code.extend(statements[start:start + _STATEMENTS_PER_FUNCTION])
-            code.append("}")
-            code.append("")
+        includes = ["#include <stddef.h>", "#include <stdlib.h>", "#include <stdbool.h>", "#include <string.h>", ""]
+        starts = list(range(0, len(statements), _STATEMENTS_PER_FUNCTION))
+        parts = ["gates_{}".format(i) for i in range(len(starts))]
+        n_units = max(1, min(n_units, len(parts)))
+        linkage = "static " if n_units == 1 else ""
+        units = [list(includes) for _ in range(n_units)]
+        for i, (name, start) in enumerate(zip(parts, starts)):
+            unit = units[i * n_units // len(parts)]
+            unit.append("{}void {}({w} const *inp, {w} *v, {w} *out) {{".format(linkage, name, w=word))
+            unit.extend(statements[start:start + _STATEMENTS_PER_FUNCTION])
+            unit.append("}")
+            unit.append("")
+        code = units[0]
+        if n_units > 1:
+            code.extend("void {}({w} const *inp, {w} *v, {w} *out);".format(name, w=word) for name in parts)
         code.append("static __thread {} hidden_values[{}];".format(word, hidden))
         code.append("")
         code.append("void logic_gate_net({w} const *inp, {w} *out) {{".format(w=word))
@@ -199,35 +211,54 @@ void apply_logic_gate_net(bool const *inp, int *out, size_t len) {
 }
 """ % dict(bits=bits, n_in=self.num_inputs, n_last=n_last, k=self.num_classes, per_class=per_class, planes=planes,
            word=word))
-        return "\n".join(code)
+        return ["\n".join(unit) for unit in units]
 
     # -- build / load ----------------------------------------------------------------------------
 
-    def compile(self, opt_level=1, save_lib_path=None, verbose=False):
+    def compile(self, opt_level=1, save_lib_path=None, verbose=False, jobs=None):
         """Writes the C source, builds a shared library with the chosen C compiler and binds it.
 
         :param opt_level:     -O level; 0 compiles in seconds, higher levels take longer and run ~2x faster
         :param save_lib_path: (optional) where to keep the shared library for `load()`
+        :param jobs:          compiler processes to run in parallel (default: one per CPU core, at most one per
+                              4096 gates); the source is split into that many translation units
         """
         if self.device != 'cpu':
             assert False, 'Device {} not supported.'.format(self.device)
-        code = self.get_c_code()
-        n_lines = code.count('\n') + 1
+        if jobs is None:
+            jobs = os.cpu_count() or 1
+        sources = self._c_sources(max(1, int(jobs)))
+        code = sources[0]
+        n_lines = sum(src.count('\n') + 1 for src in sources)
         if verbose and n_lines <= 200:
-            print('\n\n' + code + '\n\n')
+            print('\n\n' + '\n'.join(sources) + '\n\n')
 
         workdir = tempfile.mkdtemp(prefix="compiled_logic_net_")
         try:
-            c_path = os.path.join(workdir, "net.c")
             so_path = os.path.join(workdir, "net.so")
-            with open(c_path, "w") as f:
-                f.write(code)
+            c_paths = [os.path.join(workdir, "net_{}.c".format(i)) for i in range(len(sources))]
+            for c_path, src in zip(c_paths, sources):
+                with open(c_path, "w") as f:
+                    f.write(src)
             if verbose:
-                print('C code created and has {} lines. (temp location {})'.format(n_lines, c_path))
+                print('C code created and has {} lines in {} files. (temp location {})'.format(n_lines, len(sources), workdir))
             t_s = time.time()
-            result = subprocess.run([self.cpu_compiler, "-shared", "-fPIC", "-O{}".format(opt_level), "-o", so_path, c_path])
-            if result.returncode != 0:
-                raise RuntimeError(f'compilation exited with error code {result.returncode}')
+            opt = "-O{}".format(opt_level)
+            if len(c_paths) == 1:
+                result = subprocess.run([self.cpu_compiler, "-shared", "-fPIC", opt, "-o", so_path, c_paths[0]])
+                ok = result.returncode == 0
+                code_rc = result.returncode
+            else:
+                procs = [subprocess.Popen([self.cpu_compiler, "-c", "-fPIC", opt, "-o", c_path[:-2] + ".o", c_path])
+                         for c_path in c_paths]
+                rcs = [p.wait() for p in procs]
+                ok = all(rc == 0 for rc in rcs)
+                code_rc = next((rc for rc in rcs if rc != 0), 0)
+                if ok:
+                    result = subprocess.run([self.cpu_compiler, "-shared", "-o", so_path] + [c[:-2] + ".o" for c in c_paths])
+                    ok, code_rc = result.returncode == 0, result.returncode
+            if not ok:
+                raise RuntimeError(f'compilation exited with error code {code_rc}')
             if verbose:
                 print('Compiling finished in {:.3f} seconds.'.format(time.time() - t_s))
             if save_lib_path is not None:
