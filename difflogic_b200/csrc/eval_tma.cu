@@ -12,14 +12,22 @@
 // chunk major, so the CTAs of the persistent grid (one per SM) work on the same column chunk of x at
 // the same time and the second reader of an input row finds it in L2; DRAM reads stay at one pass
 // over x.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "gates.cuh"
 #include "tma.cuh"
 
 namespace dl {
 
-constexpr int kTileRows = 16;       // neurons per tile: 32 row segments = one copy per producer lane
-constexpr int kStages = 2;          // 2 x 64 KB
+// Two shapes of the same kernel (template parameters kTileRows x kStages):
+//   16 x 2, one CTA per SM  -- square layers: every input row is read about twice, HBM reads dominate;
+//    8 x 3, two CTAs per SM -- layers at least twice as wide as their input (e.g. 784 -> 8000): the input rows are
+//                              read many times out of L2 and the output writes dominate; four producer warps
+//                              per SM and smaller tiles keep more independent copies in flight (measured on
+//                              2^20 samples: 784 -> 8000 221 us against 288 us, 4000 -> 8000 254 against 327,
+//                              but 6000 -> 8000 391 against 346).  Also used when the 16 x 2 shape would give a
+//                              CTA fewer than 64 tiles (8000 -> 8000 on 2^17 samples: 48 us against 53 us).
 constexpr int kProducers = 2;       // producer warps; tile i is issued by warp i % kProducers
 constexpr int kConsumerWarps = 8;
 constexpr int kTmaThreads = 32 * (kProducers + kConsumerWarps);
@@ -35,7 +43,8 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
     return false;
 }
 
-__global__ void __launch_bounds__(kTmaThreads, 1)
+template <int kTileRows, int kStages>
+__global__ void __launch_bounds__(kTmaThreads)
 eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
                 const uint8_t *__restrict__ gate, uint8_t *__restrict__ y, uint32_t n_out, int64_t row_bytes, int chunk,
                 uint32_t row_blocks, uint32_t ntiles) {
@@ -63,14 +72,15 @@ eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, co
         // ---------------- producers: one bulk copy per (neuron, input) of the tile ----------------
         // Lane l owns input (l / kTileRows) of neuron (l % kTileRows).  The connection indices of this warp's
         // NEXT tile are fetched while the current stage is still being waited for.
-        const int r = lane % kTileRows, which = lane / kTileRows;
+        const int r = lane % kTileRows, which = (lane / kTileRows) & 1;
+        const bool copier = lane < 2 * kTileRows;
         uint32_t it = warp;
         uint32_t t = blockIdx.x + warp * G;
         uint32_t issued = 0;
         bool ok = true;
         int64_t idx = 0;
         uint32_t op = 0;
-        if (t < ntiles) {
+        if (copier && t < ntiles) {
             const uint32_t j = (t % row_blocks) * kTileRows + r;
             if (j < n_out) {
                 idx = __ldg((which ? b : a) + j);
@@ -83,7 +93,7 @@ eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, co
             int64_t idx_next = 0;
             uint32_t op_next = 0;
             const uint32_t tn = t + kProducers * G;
-            if (tn < ntiles) {
+            if (copier && tn < ntiles) {
                 const uint32_t jn = (tn % row_blocks) * kTileRows + r;
                 if (jn < n_out) {
                     idx_next = __ldg((which ? b : a) + jn);
@@ -94,7 +104,7 @@ eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, co
             const uint32_t cb = t / row_blocks, nb = t % row_blocks;
             const int64_t col0 = (int64_t)cb * chunk;
             const uint32_t bytes = (uint32_t)min((int64_t)chunk, row_bytes - col0);
-            const bool valid = nb * kTileRows + r < n_out;
+            const bool valid = copier && nb * kTileRows + r < n_out;
             const uint32_t nvalid = min((uint32_t)kTileRows, n_out - nb * kTileRows);
             if (valid && which == 0) meta[s * kTileRows + r] = (uint8_t)op;
             __syncwarp();
@@ -170,28 +180,42 @@ static int sm_count() {
     return cached[dev];
 }
 
+constexpr int kMinTileRows = 8;
+
 // True when the staged kernel applies: 16-byte aligned rows of at least 512 bytes, tile count within 32 bits.
 bool eval_tma_applicable(const void *x, const void *y, int64_t row_bytes, int64_t n_out) {
-    if (!(row_bytes % 16 == 0 && row_bytes >= 512 && n_out >= kTileRows && aligned_to(x, 16) && aligned_to(y, 16))) return false;
+    if (!(row_bytes % 16 == 0 && row_bytes >= 512 && n_out >= 16 && aligned_to(x, 16) && aligned_to(y, 16))) return false;
     const int64_t chunk = row_bytes < kMaxChunk ? row_bytes : kMaxChunk;
-    return n_out < ((int64_t)1 << 31) && ceil_div(row_bytes, chunk) * ceil_div(n_out, kTileRows) < ((int64_t)1 << 31) - 4096;
+    return n_out < ((int64_t)1 << 31) && ceil_div(row_bytes, chunk) * ceil_div(n_out, kMinTileRows) < ((int64_t)1 << 31) - 4096;
 }
 
-int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_out,
-                    int64_t row_bytes, cudaStream_t st) {
+template <int ROWS, int STAGES>
+static int launch_eval_tma_shape(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_out,
+                                 int64_t row_bytes, int ctas_per_sm, cudaStream_t st) {
     const int chunk = (int)(row_bytes < kMaxChunk ? row_bytes : kMaxChunk);
     const int64_t col_chunks = ceil_div(row_bytes, chunk);
-    const int64_t row_blocks = ceil_div(n_out, kTileRows);
+    const int64_t row_blocks = ceil_div(n_out, ROWS);
     const int64_t ntiles = col_chunks * row_blocks;
-    const size_t smem = (size_t)kStages * 2 * kTileRows * chunk + 2 * kStages * sizeof(uint64_t) + kStages * kTileRows;
-    if (cudaFuncSetAttribute(eval_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    const size_t smem = (size_t)STAGES * 2 * ROWS * chunk + 2 * STAGES * sizeof(uint64_t) + STAGES * ROWS;
+    if (cudaFuncSetAttribute(eval_tma_kernel<ROWS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return launch_status("dl_eval_packed (shared memory opt-in)");
-    const int64_t sms = sm_count();
-    const unsigned grid = (unsigned)(ntiles < sms ? ntiles : sms);
-    eval_tma_kernel<<<grid, kTmaThreads, smem, st>>>(reinterpret_cast<const uint8_t *>(x), a, b, gate,
-                                                    reinterpret_cast<uint8_t *>(y), (uint32_t)n_out, row_bytes, chunk,
-                                                    (uint32_t)row_blocks, (uint32_t)ntiles);
+    const int64_t slots = (int64_t)sm_count() * ctas_per_sm;
+    const unsigned grid = (unsigned)(ntiles < slots ? ntiles : slots);
+    eval_tma_kernel<ROWS, STAGES><<<grid, kTmaThreads, smem, st>>>(reinterpret_cast<const uint8_t *>(x), a, b, gate,
+                                                                  reinterpret_cast<uint8_t *>(y), (uint32_t)n_out, row_bytes, chunk,
+                                                                  (uint32_t)row_blocks, (uint32_t)ntiles);
     return launch_status("dl_eval_packed");
+}
+
+int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_in, int64_t n_out,
+                    int64_t row_bytes, cudaStream_t st) {
+    // fan-out of an input row: 2 * n_out / n_in.  DL_EVAL_SHAPE=wide|square overrides the choice (for A/B timing).
+    const char *force = getenv("DL_EVAL_SHAPE");
+    const int64_t chunk = row_bytes < kMaxChunk ? row_bytes : kMaxChunk;
+    const bool few_tiles = ceil_div(row_bytes, chunk) * ceil_div(n_out, 16) < (int64_t)64 * sm_count();
+    const bool wide = force && force[0] == 'w' ? true : force && force[0] == 's' ? false : (n_out >= 2 * n_in || few_tiles);
+    if (wide) return launch_eval_tma_shape<8, 3>(x, a, b, gate, y, n_out, row_bytes, 2, st);
+    return launch_eval_tma_shape<16, 2>(x, a, b, gate, y, n_out, row_bytes, 1, st);
 }
 
 }  // namespace dl

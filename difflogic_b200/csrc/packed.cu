@@ -16,7 +16,7 @@ namespace dl {
 
 // packed_tma.cu: the same eval with the gathered rows staged in shared memory by bulk copies
 bool eval_tma_applicable(const void *x, const void *y, int64_t row_bytes, int64_t n_out);
-int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_out,
+int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_in, int64_t n_out,
                     int64_t row_bytes, cudaStream_t st);
 // groupbitsum_tma.cu: the group bit-sum with rows staged the same way
 bool groupbitsum_tma_applicable(const void *x, int64_t n, int64_t row_bytes, int64_t k);
@@ -341,7 +341,7 @@ extern "C" DL_API int dl_eval_packed(const void *x, const int64_t *a, const int6
     // DL_EVAL_KERNEL=plain forces the register-staged kernel (for A/B measurements)
     const char *force = getenv("DL_EVAL_KERNEL");
     const bool plain_only = force != nullptr && force[0] == 'p';
-    if (!plain_only && eval_tma_applicable(x, y, row_bytes, n_out)) return launch_eval_tma(x, a, b, gate, y, n_out, row_bytes, st);
+    if (!plain_only && eval_tma_applicable(x, y, row_bytes, n_out)) return launch_eval_tma(x, a, b, gate, y, n_in, n_out, row_bytes, st);
     if (fits(16)) return launch_eval<uint4>(x, a, b, gate, y, n_out, row_bytes, st);
     if (fits(8)) return launch_eval<unsigned long long>(x, a, b, gate, y, n_out, row_bytes, st);
     if (fits(4)) return launch_eval<uint32_t>(x, a, b, gate, y, n_out, row_bytes, st);

@@ -154,7 +154,7 @@ def test_packbits_treats_any_nonzero_byte_as_true():
 
 @pytest.mark.parametrize("bits", [8, 16, 32, 64])
 @pytest.mark.parametrize("shape", [(20, 32, 1), (33, 50, 3), (64, 100, 16), (100, 333, 70), (8, 5, 257), (50, 37, 300),
-                                   (300, 1000, 1024), (40, 16, 2048 + 64)])
+                                   (300, 1000, 1024), (40, 16, 2048 + 64), (60, 1003, 130), (16, 2500, 600)])
 def test_eval_packed_matches_oracle(bits, shape):
     n_in, n_out, words = shape
     g = torch.Generator().manual_seed(sum(shape) + bits)
