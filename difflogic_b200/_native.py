@@ -36,6 +36,8 @@ SIGNATURES = {
     "dl_packbits_batch_major": (_int, [_ptr, _ptr, _i64, _i64, _int, _ptr]),
     "dl_threshold_packbits_batch_major": (_int, [_ptr, _ptr, _int, _ptr, _i64, _i64, _int, _ptr]),
     "dl_groupbitsum": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
+    "dl_eval_groupbitsum_applicable": (_int, [_ptr, _i64, _i64, _i64, _int, _i64]),
+    "dl_eval_groupbitsum": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
     "dl_pack_net_layer": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr]),
     "dl_eval_net_shared_bytes": (ctypes.c_size_t, [_ptr, _int]),
     "dl_eval_net_packed": (_int, [_ptr, _ptr, _ptr, _int, _ptr, _i64, _i64, _i64, _int, _ptr]),

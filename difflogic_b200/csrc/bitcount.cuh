@@ -20,12 +20,14 @@ constexpr int kHiPlanes = 9;                      // weights 8 .. 2048
 constexpr int kPlanes = 3 + kHiPlanes;            // ones, twos, fours + high planes
 constexpr int kMaxChunkRows = 8 * (1 << kHiPlanes) - 1;  // 4095
 
-struct BitCounter {
-    unsigned long long ones, twos, fours, hi[kHiPlanes];
+// HI = number of planes above ones / twos / fours: counts up to 8 * 2^HI - 1.
+template <int HI>
+struct BitCounterT {
+    unsigned long long ones, twos, fours, hi[HI];
     __device__ __forceinline__ void clear() {
         ones = twos = fours = 0ull;
 #pragma unroll
-        for (int q = 0; q < kHiPlanes; ++q) hi[q] = 0ull;
+        for (int q = 0; q < HI; ++q) hi[q] = 0ull;
     }
     __device__ __forceinline__ void add8(const unsigned long long (&v)[8]) {
         unsigned long long t2a, t2b, t4a, t4b, e8;
@@ -38,7 +40,7 @@ struct BitCounter {
         DL_CSA(e8, fours, fours, t4a, t4b);
         unsigned long long carry = e8;
 #pragma unroll
-        for (int q = 0; q < kHiPlanes; ++q) {
+        for (int q = 0; q < HI; ++q) {
             const unsigned long long t = hi[q] & carry;
             hi[q] ^= carry;
             carry = t;
@@ -50,7 +52,7 @@ struct BitCounter {
         t = twos & carry; twos ^= carry; carry = t;
         t = fours & carry; fours ^= carry; carry = t;
 #pragma unroll
-        for (int q = 0; q < kHiPlanes; ++q) {
+        for (int q = 0; q < HI; ++q) {
             t = hi[q] & carry;
             hi[q] ^= carry;
             carry = t;
@@ -61,5 +63,6 @@ struct BitCounter {
     }
 };
 
+using BitCounter = BitCounterT<kHiPlanes>;
 
 }  // namespace dl

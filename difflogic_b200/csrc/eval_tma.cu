@@ -166,7 +166,8 @@ eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, co
     }
 }
 
-int groupbitsum_async_error();  // groupbitsum_tma.cu
+int groupbitsum_async_error();       // groupbitsum_tma.cu
+int eval_groupbitsum_async_error();  // eval_groupbitsum.cu
 
 static int sm_count() {
     static int cached[64] = {0};
@@ -230,5 +231,7 @@ extern "C" DL_API int dl_async_error(void) {
     }
     const int other = dl::groupbitsum_async_error();
     if (other < 0) return other;
-    return flag | other;
+    const int fused = dl::eval_groupbitsum_async_error();
+    if (fused < 0) return fused;
+    return flag | other | fused;
 }

@@ -250,6 +250,34 @@ def groupbitsum(x, pad_len, k):
     return out
 
 
+def eval_groupbitsum_applicable(x, n_out, k):
+    """True when the fused last-layer + group bit-sum kernel takes a layer of n_out gates on packed words x."""
+    if not (x.is_cuda and x.dim() == 2 and x.is_contiguous()):
+        return False
+    n_in, words = x.shape
+    return N.lib().dl_eval_groupbitsum_applicable(x.data_ptr(), n_in, int(n_out), words, bits_of(x), int(k)) == 1
+
+
+def eval_groupbitsum(x, a, b, gate, pad_len, k):
+    """groupbitsum(eval_packed(x, a, b, gate), pad_len, k) in one kernel; the layer's output is never stored."""
+    N.require_cuda(x, a, b, gate)
+    _need(x.dim() == 2 and x.is_contiguous(), "x must be a contiguous 2-D tensor")
+    _need(a.dtype == torch.int64 and b.dtype == torch.int64 and gate.dtype == torch.uint8, "a, b int64 and gate uint8")
+    _need(a.numel() == b.numel() == gate.numel(), "a, b and gate must have one entry per gate")
+    bits = bits_of(x)
+    n_in, words = x.shape
+    n_out, k = a.numel(), int(k)
+    if k <= 0 or n_out % k != 0:
+        raise ValueError("in_dim (%d) has to be divisible by k (%d) but it is not" % (n_out, k))
+    batch = words * bits - int(pad_len)
+    _need(batch >= 0, "pad_len exceeds the packed batch")
+    out = torch.empty((batch, k), dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_eval_groupbitsum(x.data_ptr(), a.data_ptr(), b.data_ptr(), gate.data_ptr(), out.data_ptr(), n_in, n_out,
+                                            words, int(pad_len), k, bits, N.stream_of(x)))
+    return out
+
+
 # ------------------------------------------------------------------------------------------------
 # whole-network packed inference
 # ------------------------------------------------------------------------------------------------

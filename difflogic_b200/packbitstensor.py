@@ -92,6 +92,14 @@ class PackBitsTensor:
             if ops.fused_net_fits(widths, row_bytes):
                 metas = [layer._packed_descriptors(gate) for layer, gate in self._pending]
                 return ops.eval_net_packed(self._t, metas, widths, self.pad_len, k)
+        if self._pending and os.environ.get("DL_FUSED_LAST_LAYER", "1") != "0":
+            # all layers but the last run now; the last one is counted as it is computed, its output never stored
+            (layer, gate) = self._pending.pop()
+            self._materialize()
+            self._pending.append((layer, gate))  # still pending: `.t` would run it as a kernel of its own
+            if ops.eval_groupbitsum_applicable(self._t, layer.out_dim, k):
+                a, b = layer.indices
+                return ops.eval_groupbitsum(self._t, a, b, gate, self.pad_len, k)
         return ops.groupbitsum(self.t, self.pad_len, k)
 
     def flatten(self, start_dim=0, end_dim=-1, **kwargs):

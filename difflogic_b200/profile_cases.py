@@ -2,6 +2,7 @@
 
     python -m difflogic_b200.profile_cases eval   [words  [neurons]]   # packed eval, default 4096 x 8000
     python -m difflogic_b200.profile_cases gbs    [words  [neurons]]   # group bit-sum, k = 10
+    python -m difflogic_b200.profile_cases tail   [words  [neurons]]   # last layer + group bit-sum in one kernel, k = 10
     python -m difflogic_b200.profile_cases fwd|bw|bx [batch [neurons]] # training kernels, default 128 x 16000
 
 Each case builds a square layer with 'random' connections and launches the kernel three times.  The sizes are
@@ -24,7 +25,7 @@ def main(argv):
     which = argv[0]
     dev = "cuda"
     torch.manual_seed(0)
-    if which in ("eval", "gbs"):
+    if which in ("eval", "gbs", "tail"):
         words = int(argv[1]) if len(argv) > 1 else 4096
         n = int(argv[2]) if len(argv) > 2 else 8000
         a, b = _connections(n, n, dev)
@@ -34,6 +35,8 @@ def main(argv):
         for _ in range(3):
             if which == "eval":
                 ops.eval_packed(x, a, b, gate, out=out)
+            elif which == "tail":
+                ops.eval_groupbitsum(x, a, b, gate, 0, 10)
             else:
                 ops.groupbitsum(x, 0, 10)
     elif which in ("fwd", "bw", "bx"):

@@ -172,6 +172,21 @@ DL_API int dl_groupbitsum(const void *x, int32_t *out, int64_t n, int64_t words,
                    int bit_count, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Last logic layer + group bit-sum in one launch: out equals dl_groupbitsum applied to the y of
+ * dl_eval_packed(x, a, b, gate), but y is never written.  Replaces the last logic_layer_cuda_eval
+ * (difflogic_kernel.cu:503-541) together with groupbitsum (:666-700) in the chain
+ * model(PackBitsTensor) of experiments/main.py:198-210; bit-identical results.
+ * dl_eval_groupbitsum_applicable returns 1 when the sizes are in the kernel's range (rows of at least
+ * 512 bytes and a multiple of 16, x 16-byte aligned, n_out % k == 0, 32 <= n_out/k <= 2040), else 0;
+ * dl_eval_groupbitsum returns DL_ERR_INVALID_ARG outside that range.  out [batch][k] int32,
+ * batch = words*bit_count - pad_len.
+ * ---------------------------------------------------------------------------------------- */
+DL_API int dl_eval_groupbitsum_applicable(const void *x, int64_t n_in, int64_t n_out, int64_t words, int bit_count, int64_t k);
+DL_API int dl_eval_groupbitsum(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, int32_t *out,
+                               int64_t n_in, int64_t n_out, int64_t words, int64_t pad_len, int64_t k, int bit_count,
+                               void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * Whole-network packed-bit inference in one launch: every logic layer and the group bit-sum, the
  * activations of a 64-sample block staying in shared memory.  Replaces the chain
  * model(PackBitsTensor) of experiments/main.py:198-210, i.e. one logic_layer_cuda_eval per layer
