@@ -136,11 +136,13 @@ def train_bytes_per_step(dims, batch, k):
     return total, per_kernel
 
 
-def eval_bytes_per_sample(dims, k):
+def eval_bytes_per_sample(dims, k, fused_tail=False):
     """Packed eval, per sample: each layer reads n_in and writes n_out bits-per-sample (1/8 byte each),
-    groupbitsum reads n bits and writes k int32."""
+    groupbitsum reads n bits and writes k int32.  With the last layer and the group bit-sum in one kernel the
+    last layer's output is neither written nor read back."""
     b = sum((n_in + n_out) / 8.0 for n_in, n_out in zip(dims[:-1], dims[1:]))
-    return b + dims[-1] / 8.0 + 4 * k
+    b += dims[-1] / 8.0 + 4 * k
+    return b - 2 * dims[-1] / 8.0 if fused_tail else b
 
 
 def build_gpu_model(dims, k, tau, seed):
@@ -370,9 +372,16 @@ def bench_packed(args, rank, world):
     # two ping-pong activation buffers, allocated once (the API call allocates per layer)
     bufs = [torch.empty(EVAL_DIMS[1], W, dtype=torch.int64, device=dev) for _ in range(2)]
 
+    # the plan PackBitsTensor.group_sum runs: all layers but the last one kernel each, then the last layer and the
+    # group bit-sum in one kernel when its sizes are in that kernel's range
+    fused_tail = os.environ.get("DL_FUSED_LAST_LAYER", "1") != "0" and ops.eval_groupbitsum_applicable(bufs[0], EVAL_DIMS[-1], EVAL_K)
+
     def run_resident():
         cur = words0
+        last = len(layers) - 1
         for i, l in enumerate(layers):
+            if i == last and fused_tail:
+                return ops.eval_groupbitsum(cur, l.indices[0], l.indices[1], gates[i], pad, EVAL_K)
             cur = ops.eval_packed(cur, l.indices[0], l.indices[1], gates[i], out=bufs[i % 2])
         return ops.groupbitsum(cur, pad, EVAL_K)
 
@@ -416,7 +425,8 @@ def bench_packed(args, rank, world):
         "workload": "784 -> 4 x 8000 -> GroupSum(10), eval mode, 2^20 samples in int64 words, sharded by batch",
         "metric": "packed-bit inference samples/s", "unit": UNIT,
         "value": EVAL_SAMPLES * K / t_dev, "ms_per_pass": t_dev / K * 1e3, "samples_per_gpu": local,
-        "bytes_per_sample": eval_bytes_per_sample(EVAL_DIMS, EVAL_K),
+        "bytes_per_sample": eval_bytes_per_sample(EVAL_DIMS, EVAL_K, fused_tail),
+        "bytes_per_sample_layer_by_layer": eval_bytes_per_sample(EVAL_DIMS, EVAL_K), "fused_last_layer": bool(fused_tail),
         "e2e": {"value": EVAL_SAMPLES * Ke / t_e2e, "unit": UNIT, "h2d_bytes_per_step": host_bool.numel(),
                 "d2h_bytes_per_step": out_host.numel() * 4},
         "gpu_launches": launches, "clocks": sampler.summary(),
@@ -436,6 +446,10 @@ def bench_packed(args, rank, world):
             "groupbitsum": (8 * W * n + 4 * local * EVAL_K, lambda: L.dl_groupbitsum(x.data_ptr(), out_counts.data_ptr(), n, W, pad,
                                                                                      EVAL_K, 64, st)),
         }
+        if fused_tail:
+            kern["eval_groupbitsum"] = (8 * W * n + 4 * local * EVAL_K, lambda: L.dl_eval_groupbitsum(
+                x.data_ptr(), l.indices[0].data_ptr(), l.indices[1].data_ptr(), gates[1].data_ptr(), out_counts.data_ptr(), n, n, W,
+                pad, EVAL_K, 64, st))
         rows = {}
         for name, (nbytes, fn) in kern.items():
             for _ in range(2):

@@ -2,7 +2,7 @@
 // written to memory.
 //
 // Unfused, the last layer writes n_out rows and the group bit-sum reads them back: two passes over the largest
-// array of the network.  Here a thread-block CLUSTER of S CTAs owns one work unit = (column block of 2 KB, class):
+// array of the network.  Here a thread-block CLUSTER of S CTAs owns one work unit = (column block of up to 2 KB, class):
 // CTA q of the cluster takes the q-th share of the class's neurons.  A CTA has three kinds of warps:
 //   * two PRODUCER warps stage the two gathered input rows of 8 neurons at a time in shared memory (one 2 KB bulk
 //     copy per row, ring of 3 stages) together with the neurons' gate masks;
@@ -104,11 +104,11 @@ struct FgUnit {
     uint32_t bytes;  // bytes per row segment
 };
 
-__device__ __forceinline__ FgUnit fg_unit(int64_t u, int64_t row_bytes, int k, int m, int q, int nq) {
+__device__ __forceinline__ FgUnit fg_unit(int64_t u, int64_t row_bytes, int block_bytes, int k, int m, int q, int nq) {
     FgUnit g;
     g.cls = (int)(u % k);
-    g.col0 = (u / k) * kFgChunk;
-    g.bytes = (uint32_t)min((int64_t)kFgChunk, row_bytes - g.col0);
+    g.col0 = (u / k) * block_bytes;
+    g.bytes = (uint32_t)min((int64_t)block_bytes, row_bytes - g.col0);
     const int64_t r0 = ((int64_t)m * q) / nq, r1 = ((int64_t)m * (q + 1)) / nq;
     g.row0 = (int64_t)g.cls * m + r0;
     g.rows = (int)(r1 - r0);
@@ -121,28 +121,28 @@ struct FgCursor {
     int r;          // first row of the stage within the share
     FgUnit g;
     bool valid;
-    __device__ __forceinline__ void seek(int64_t nclusters, int64_t nunits, int64_t row_bytes, int k, int m, int q, int nq) {
+    __device__ __forceinline__ void seek(int64_t nclusters, int64_t nunits, int64_t row_bytes, int block_bytes, int k, int m, int q, int nq) {
         // first unit from u on whose share has rows
         for (valid = false; u < nunits; u += nclusters) {
-            g = fg_unit(u, row_bytes, k, m, q, nq);
+            g = fg_unit(u, row_bytes, block_bytes, k, m, q, nq);
             if (g.rows > 0) { valid = true; break; }
         }
     }
-    __device__ __forceinline__ void start(int64_t cluster_id, int64_t nclusters, int64_t nunits, int64_t row_bytes, int k, int m, int q,
-                                          int nq) {
+    __device__ __forceinline__ void start(int64_t cluster_id, int64_t nclusters, int64_t nunits, int64_t row_bytes, int block_bytes, int k,
+                                          int m, int q, int nq) {
         u = cluster_id;
         it = 0;
         r = 0;
-        seek(nclusters, nunits, row_bytes, k, m, q, nq);
+        seek(nclusters, nunits, row_bytes, block_bytes, k, m, q, nq);
     }
-    __device__ __forceinline__ void next(int64_t nclusters, int64_t nunits, int64_t row_bytes, int k, int m, int q, int nq) {
+    __device__ __forceinline__ void next(int64_t nclusters, int64_t nunits, int64_t row_bytes, int block_bytes, int k, int m, int q, int nq) {
         if (!valid) return;
         ++it;
         r += kFgRows;
         if (r >= g.rows) {
             u += nclusters;
             r = 0;
-            seek(nclusters, nunits, row_bytes, k, m, q, nq);
+            seek(nclusters, nunits, row_bytes, block_bytes, k, m, q, nq);
         }
     }
 };
@@ -203,8 +203,8 @@ __device__ __forceinline__ void planes_to_bytes(const unsigned long long (&P)[8]
 template <int S>
 __global__ void __launch_bounds__(kFgThreads, 2)
 eval_groupbitsum_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
-                        const uint8_t *__restrict__ gate, int32_t *__restrict__ out, int64_t row_bytes, int64_t batch, int k,
-                        int m, int nplanes, int64_t nunits) {
+                        const uint8_t *__restrict__ gate, int32_t *__restrict__ out, int64_t row_bytes, int block_bytes,
+                        int64_t batch, int k, int m, int nplanes, int64_t nunits) {
     extern __shared__ __align__(128) uint8_t smem[];
     unsigned long long *red = reinterpret_cast<unsigned long long *>(smem + kFgStages * kFgStageBytes);  // [planes][words]
     uint4 *meta = reinterpret_cast<uint4 *>(red + kFgRedPlanes * kFgWords);                               // [stages][rows]
@@ -241,8 +241,8 @@ eval_groupbitsum_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict
         int64_t last = -1;  // latest stage this warp filled
         bool ok = true;
         FgCursor cur;
-        cur.start(cluster_id, nclusters, nunits, row_bytes, k, m, q, S);
-        for (int i = 0; i < warp; ++i) cur.next(nclusters, nunits, row_bytes, k, m, q, S);
+        cur.start(cluster_id, nclusters, nunits, row_bytes, block_bytes, k, m, q, S);
+        for (int i = 0; i < warp; ++i) cur.next(nclusters, nunits, row_bytes, block_bytes, k, m, q, S);
         int64_t idx = 0;
         uint32_t op = 0;
         if (cur.valid && copier && r_in < cur.g.rows - cur.r) {
@@ -251,7 +251,7 @@ eval_groupbitsum_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict
         }
         while (cur.valid) {
             FgCursor nxt = cur;
-            for (int i = 0; i < kFgProducers; ++i) nxt.next(nclusters, nunits, row_bytes, k, m, q, S);
+            for (int i = 0; i < kFgProducers; ++i) nxt.next(nclusters, nunits, row_bytes, block_bytes, k, m, q, S);
             int64_t idx_next = 0;
             uint32_t op_next = 0;
             if (nxt.valid && copier && r_in < nxt.g.rows - nxt.r) {
@@ -295,7 +295,7 @@ eval_groupbitsum_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict
         int64_t it = 0;
         uint32_t n = 0;  // units done
         for (int64_t u = cluster_id; u < nunits; u += nclusters, ++n) {
-            const FgUnit g = fg_unit(u, row_bytes, k, m, q, S);
+            const FgUnit g = fg_unit(u, row_bytes, block_bytes, k, m, q, S);
             const bool mine = (uint32_t)ct * 8u < g.bytes;
             BitCounterT<kFgRedPlanes - 3> cn;  // a share is at most 255 neurons
             cn.clear();
@@ -354,7 +354,7 @@ eval_groupbitsum_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict
         const int sum_planes = min(kFgSumPlanes, nplanes + (S == 8 ? 3 : S == 4 ? 2 : 1));
         uint32_t n = 0;
         for (int64_t u = cluster_id; u < nunits; u += nclusters, ++n) {
-            const FgUnit g = fg_unit(u, row_bytes, k, m, q, S);
+            const FgUnit g = fg_unit(u, row_bytes, block_bytes, k, m, q, S);
             if (!fg_wait_cluster(red_full, n & 1u, abort_flag)) {
                 g_fg_async_error = 1;
                 s_abort = 1;
@@ -449,7 +449,6 @@ static int launch_fg(const void *x, const int64_t *a, const int64_t *b, const ui
     const size_t smem = fg_shared_bytes();
     if (cudaFuncSetAttribute(eval_groupbitsum_kernel<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return launch_status("dl_eval_groupbitsum (shared memory opt-in)");
-    const int64_t nunits = ceil_div(row_bytes, kFgChunk) * k;
     int nplanes = 1;
     while (nplanes < kFgRedPlanes && ((int64_t)1 << nplanes) <= ceil_div(m, S)) ++nplanes;
 
@@ -472,11 +471,15 @@ static int launch_fg(const void *x, const int64_t *a, const int64_t *b, const ui
         cudaGetLastError();
         return fail(DL_ERR_CUDA, "dl_eval_groupbitsum: no cluster of %d CTAs can be resident", S);
     }
+    // Column block: 2 KB.  Narrower blocks that would fill the last round of the static round-robin better were
+    // measured slower throughout: the kernel's time goes with the number of stages, not with their width.
+    const int block_bytes = (int)(row_bytes < kFgChunk ? row_bytes : kFgChunk);
+    const int64_t nunits = ceil_div(row_bytes, block_bytes) * k;
     const int64_t nclusters = nunits < resident ? nunits : resident;
     cfg.gridDim = dim3((unsigned)(nclusters * S));
     const uint8_t *xb = reinterpret_cast<const uint8_t *>(x);
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, eval_groupbitsum_kernel<S>, xb, a, b, gate, out, row_bytes, batch, (int)k, (int)m,
-                                             nplanes, nunits);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, eval_groupbitsum_kernel<S>, xb, a, b, gate, out, row_bytes, block_bytes, batch, (int)k,
+                                             (int)m, nplanes, nunits);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail(DL_ERR_CUDA, "dl_eval_groupbitsum: %s", cudaGetErrorString(e));
