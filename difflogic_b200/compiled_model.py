@@ -1,4 +1,6 @@
-"""CompiledLogicNet: a trained (discretised) logic gate network turned into C and run on the CPU.
+"""CompiledLogicNet: a trained (discretised) logic gate network turned into C and run on the CPU, or -- with
+device='cuda', which the reference declares but leaves unimplemented (difflogic/compiled_model.py:263-264,
+293-294) -- frozen into device arrays and run by this package's packed-bit kernels.
 
 Drop-in for the reference class (difflogic/compiled_model.py:43-370): same constructor, the same
 `get_gate_code / get_layer_code / get_c_code / compile / load / forward` methods and the same
@@ -95,6 +97,7 @@ class CompiledLogicNet(torch.nn.Module):
 
         self.lib_fn = None
         self._lib = None
+        self._cuda_plan = None  # device='cuda': [(a, b, gate ids)] per layer, on the GPU
 
     # -- code generation -------------------------------------------------------------------------
 
@@ -223,6 +226,9 @@ void apply_logic_gate_net(bool const *inp, int *out, size_t len) {
         :param jobs:          compiler processes to run in parallel (default: one per CPU core, at most one per
                               4096 gates); the source is split into that many translation units
         """
+        if self.device == 'cuda':
+            self._compile_cuda(verbose)
+            return
         if self.device != 'cpu':
             assert False, 'Device {} not supported.'.format(self.device)
         if jobs is None:
@@ -270,6 +276,43 @@ void apply_logic_gate_net(bool const *inp, int *out, size_t len) {
         finally:
             shutil.rmtree(workdir, ignore_errors=True)
 
+    def _compile_cuda(self, verbose=False):
+        """device='cuda': nothing is compiled.  The network is frozen as it is now -- connections and arg-max gate ids
+        copied to the GPU -- and forward() runs the packed-bit kernels on it (pack, one eval kernel per layer, the
+        last layer fused with the class count).  `num_bits` is the word width of the packed tensor."""
+        from . import ops
+        from ._native import lib
+        lib()  # raises NativeLibraryMissing without the built CUDA library
+        if not torch.cuda.is_available():
+            raise RuntimeError("CompiledLogicNet(device='cuda'): no CUDA device")
+        plan = []
+        for a, b, op in self.layers:
+            plan.append((torch.as_tensor(a).to('cuda', torch.int64).contiguous(), torch.as_tensor(b).to('cuda', torch.int64).contiguous(),
+                         torch.as_tensor(op).to('cuda', torch.uint8).contiguous()))
+        assert plan[-1][0].numel() % self.num_classes == 0, (plan[-1][0].numel(), self.num_classes)
+        self._cuda_plan = plan
+        self._ops = ops
+        if verbose:
+            print('{} layers frozen on the GPU.'.format(len(plan)))
+
+    def _forward_cuda(self, x):
+        ops = self._ops
+        on_gpu = isinstance(x, torch.Tensor) and x.is_cuda
+        x = torch.as_tensor(x)
+        x = x.reshape(x.shape[0], -1).to('cuda')
+        if x.dtype != torch.bool:
+            x = x.ne(0)
+        assert x.shape[1] == self.num_inputs, (x.shape, self.num_inputs)
+        words, pad_len = ops.packbits_batch_major(x.contiguous(), self.num_bits)
+        for a, b, gate in self._cuda_plan[:-1]:
+            words = ops.eval_packed(words, a, b, gate)
+        a, b, gate = self._cuda_plan[-1]
+        if ops.eval_groupbitsum_applicable(words, a.numel(), self.num_classes):
+            out = ops.eval_groupbitsum(words, a, b, gate, pad_len, self.num_classes)
+        else:
+            out = ops.groupbitsum(ops.eval_packed(words, a, b, gate), pad_len, self.num_classes)
+        return out if on_gpu else out.cpu()
+
     @staticmethod
     def load(save_lib_path, num_classes, num_bits):
         self = CompiledLogicNet(None, num_bits=num_bits)
@@ -285,7 +328,10 @@ void apply_logic_gate_net(bool const *inp, int *out, size_t len) {
             x: Union[torch.BoolTensor, numpy.typing.NDArray[np.bool_]],
             verbose: bool = False
     ) -> torch.IntTensor:
-        """bool [batch, features] (numpy or CPU torch) -> int32 [batch, num_classes] class counts."""
+        """bool [batch, features] (numpy or torch) -> int32 [batch, num_classes] class counts.  With device='cuda' the
+        result is on the GPU when x was, else on the CPU."""
+        if self._cuda_plan is not None:
+            return self._forward_cuda(x)
         if self.lib_fn is None:
             raise RuntimeError('CompiledLogicNet: call compile() or load() first')
         if isinstance(x, torch.Tensor):
