@@ -273,6 +273,8 @@ def bench_train(args, rank, world):
     t_dev = sum(s.elapsed_time(e) for s, e in pairs) * 1e-3
     t_dev = all_max(t_dev, world)
     final_loss = float(loss.item())
+    # time stamps the exchange kernel took on the device during the last timed step (peer exchange only)
+    exchange_timing = opt.exchange_timing() if getattr(opt, "exchange_enabled", False) else None
 
     # ---- end to end: pinned host batch -> H2D -> step -> loss read back on the host, every step
     for i in range(W):
@@ -298,6 +300,7 @@ def bench_train(args, rank, world):
                 "h2d_bytes_per_step": hx[0].numel() * 4 + hy[0].numel() * 8, "d2h_bytes_per_step": 4},
         "gpu_launches": launches_per_step * K,
         "launches_per_step": launches_per_step,
+        "exchange_kernel_last_step": exchange_timing,
         "loss": final_loss,
         "step_hbm_frac": (bytes_step / (t_dev / K)) / 1e9 / peak,
         "step_algorithmic_bytes": bytes_step,
@@ -601,6 +604,7 @@ def main():
                                                            else "torch.optim.Adam capturable fused"),
                        "l2": "flushed between timed steps (256 MiB memset, untimed)"},
             "e2e": train["e2e"], "gpu_launches": train["gpu_launches"], "launches_per_step": train["launches_per_step"],
+            "exchange_kernel_last_step": train["exchange_kernel_last_step"],
             "clocks": train["clocks"], "loss": train["loss"],
             "step_algorithmic_bytes": train["step_algorithmic_bytes"], "step_hbm_frac": train["step_hbm_frac"],
             "roofline": train.get("roofline"), "roofline_kernels": train.get("roofline_kernels"),

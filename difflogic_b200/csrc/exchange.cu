@@ -6,10 +6,14 @@
 //   1. barrier A: every rank tells every peer that its gradients are complete (a flag store into the peer's
 //      memory) and waits until all peers have said so;
 //   2. for its slice it reads that slice of ALL ranks' gradients straight from their memory (16-byte loads over
-//      NVLink), averages, applies Adam with its slice of the moments, and stores the new parameters into its own
-//      parameter buffer and into every peer's;
-//   3. barrier B: when all its stores are out (system-wide fence) it tells the peers, and waits for theirs; the
-//      kernel ends with every rank holding the complete updated parameters.
+//      NVLink), averages, applies Adam with its slice of the moments, and stores the new parameters into its OWN
+//      parameter buffer;
+//   3. barrier B: when a rank's slice is complete (a fence over local stores: cheap) it tells the peers; every block
+//      waits until all ranks have said so;
+//   4. it pulls the other ranks' slices of the new parameters from their memory into its own parameter buffer
+//      (peer loads again).  The kernel ends with every rank holding the complete updated parameters.
+// Pulling instead of pushing the new parameters matters: after stores INTO peer memory a rank has to wait for
+// their system-wide visibility before it may raise its flag, and that fence measured 8 us of a 27 us kernel.
 // This replaces an NCCL all-reduce of the gradients followed by a full Adam step on every rank: the bytes that
 // cross NVLink are the same as a reduce-scatter plus all-gather, there is no extra launch, and each rank touches
 // only 1/N of the optimizer state.
@@ -58,13 +62,27 @@ __device__ __forceinline__ bool wait_peers(const int *my_flags, int world, int b
     return true;
 }
 
-// state: [0] steps done, [1] ticket of finished blocks, [2] error (a wait ran out)
-__global__ void __launch_bounds__(kThreads)
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// state: [0] steps done, [1] ticket of blocks that finished their part of the slice, [2] error (a wait ran out),
+// [3] ticket of blocks that finished pulling, [4..15] six 64-bit time stamps of the latest step in nanoseconds:
+// entry, after barrier A (block 0), slice done (last block), after barrier B (block 0), block 0's elements stored, end
+// WORLD = number of ranks when it is 2, 4 or 8 (all loads of an iteration are then issued before the first one is
+// used: 8 peer loads of 16 bytes in flight per thread, i.e. 8 / WORLD elements per iteration), 0 = any number of ranks
+// (one element per iteration, peers read one after the other).
+template <int WORLD>
+__global__ void __launch_bounds__(kThreads, 2)
 adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict__ m, float *__restrict__ v, int64_t n4_total,
                      float lr, float beta1, float beta2, float eps, int *__restrict__ state) {
     __shared__ float s_step_size, s_bc2_sqrt;
     __shared__ int s_ok;
     grid_dependency_wait();  // this rank's gradients come from the kernels just before
+    unsigned long long *stamps = reinterpret_cast<unsigned long long *>(state + 4);
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[0] = global_timer_ns();
     const int epoch = state[0] + 1;
     // barrier A: announce (once per rank), then everybody waits on the local flag words
     if (blockIdx.x == 0 && threadIdx.x < world) st_release_sys(peers.flags[threadIdx.x] + 2 * rank + 0, epoch);
@@ -75,6 +93,7 @@ adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict
         s_bc2_sqrt = sqrtf(1.f - powf(beta2, t));
     }
     __syncthreads();
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[1] = global_timer_ns();
     if (!s_ok && threadIdx.x == 0) state[2] = 1;
     const float step_size = s_step_size, bc2_sqrt = s_bc2_sqrt;
     const float omb1 = 1.f - beta1, omb2 = 1.f - beta2, inv_world = 1.f / (float)world;
@@ -83,14 +102,8 @@ adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict
     const int64_t per = (n4_total + world - 1) / world;
     const int64_t lo = min((int64_t)rank * per, n4_total), hi = min(lo + per, n4_total);
     float4 *m4 = reinterpret_cast<float4 *>(m), *v4 = reinterpret_cast<float4 *>(v);  // moments of the slice only
-    for (int64_t i = lo + (int64_t)blockIdx.x * kThreads + threadIdx.x; i < hi; i += (int64_t)gridDim.x * kThreads) {
-        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int p = 0; p < world; ++p) {
-            const float4 gp = ld_peer(reinterpret_cast<const float4 *>(peers.grad[p]) + i);
-            g.x += gp.x; g.y += gp.y; g.z += gp.z; g.w += gp.w;
-        }
-        float4 pp = reinterpret_cast<float4 *>(peers.param[rank])[i];
-        float4 mm = m4[i - lo], vv = v4[i - lo];
+    float4 *own_param = reinterpret_cast<float4 *>(peers.param[rank]);
+
 #define DL_ADAM1(c)                                          \
     {                                                        \
         const float gr = g.c * inv_world;                    \
@@ -99,24 +112,115 @@ adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict
         const float denom = sqrtf(vv.c) / bc2_sqrt + eps;    \
         pp.c = pp.c - step_size * (mm.c / denom);            \
     }
-        DL_ADAM1(x) DL_ADAM1(y) DL_ADAM1(z) DL_ADAM1(w)
-#undef DL_ADAM1
-        m4[i - lo] = mm;
-        v4[i - lo] = vv;
-        for (int p = 0; p < world; ++p) reinterpret_cast<float4 *>(peers.param[p])[i] = pp;
+    if (WORLD > 0) {
+        constexpr int W = WORLD > 0 ? WORLD : 1;
+        constexpr int U = 8 / W;  // elements per thread and iteration
+        const int64_t stride = (int64_t)gridDim.x * kThreads;
+        for (int64_t base = lo + (int64_t)blockIdx.x * kThreads + threadIdx.x; base < hi; base += stride * U) {
+            float4 gp[U][W], pp_[U], mm_[U], vv_[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t i = base + u * stride;
+                if (i < hi) {
+#pragma unroll
+                    for (int p = 0; p < W; ++p) gp[u][p] = ld_peer(reinterpret_cast<const float4 *>(peers.grad[p]) + i);
+                    pp_[u] = own_param[i];
+                    mm_[u] = m4[i - lo];
+                    vv_[u] = v4[i - lo];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t i = base + u * stride;
+                if (i < hi) {
+                    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int p = 0; p < W; ++p) {  // same order of additions as the generic loop
+                        g.x += gp[u][p].x; g.y += gp[u][p].y; g.z += gp[u][p].z; g.w += gp[u][p].w;
+                    }
+                    float4 pp = pp_[u], mm = mm_[u], vv = vv_[u];
+                    DL_ADAM1(x) DL_ADAM1(y) DL_ADAM1(z) DL_ADAM1(w)
+                    m4[i - lo] = mm;
+                    v4[i - lo] = vv;
+                    own_param[i] = pp;
+                }
+            }
+        }
+    } else {
+        for (int64_t i = lo + (int64_t)blockIdx.x * kThreads + threadIdx.x; i < hi; i += (int64_t)gridDim.x * kThreads) {
+            float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int p = 0; p < world; ++p) {
+                const float4 gp = ld_peer(reinterpret_cast<const float4 *>(peers.grad[p]) + i);
+                g.x += gp.x; g.y += gp.y; g.z += gp.z; g.w += gp.w;
+            }
+            float4 pp = own_param[i];
+            float4 mm = m4[i - lo], vv = v4[i - lo];
+            DL_ADAM1(x) DL_ADAM1(y) DL_ADAM1(z) DL_ADAM1(w)
+            m4[i - lo] = mm;
+            v4[i - lo] = vv;
+            own_param[i] = pp;
+        }
     }
+#undef DL_ADAM1
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[4] = global_timer_ns();  // first block: its elements are stored
 
-    // barrier B: every thread pushes its stores out to system scope; the last block to finish announces, waits
-    // for the peers, and advances the step counter
-    __threadfence_system();
+    // barrier B: the last block of this rank to finish its part of the slice tells the peers; every block then waits
+    // until all ranks' slices are complete.  (All blocks of the grid are resident together -- the host sizes the
+    // grid for that -- so waiting for this grid's own last block cannot starve it.)
+    // Every thread orders its stores at GPU scope (they are stores to this GPU's own memory: once they are visible
+    // on this GPU, a peer's load over NVLink sees them too); only the one thread that raises the flag pays for a
+    // system-scope fence.  A system-scope fence in every thread measured 8 us.
+    __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
         const int done = atomicAdd(state + 1, 1);
         if (done == (int)gridDim.x - 1) {
+            __threadfence_system();
+            stamps[2] = global_timer_ns();
             for (int p = 0; p < world; ++p) st_release_sys(peers.flags[p] + 2 * rank + 1, epoch);
-            if (!wait_peers(peers.flags[rank], world, 1, epoch)) state[2] = 1;
+        }
+        s_ok = wait_peers(peers.flags[rank], world, 1, epoch) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_ok && threadIdx.x == 0) state[2] = 1;
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[3] = global_timer_ns();
+
+    // pull the other ranks' slices; eight 16-byte peer loads in flight per thread
+    {
+        const int64_t others = (int64_t)(world - 1) * per;  // elements to fetch, indexed over the other ranks' slices
+        const int64_t stride = (int64_t)gridDim.x * kThreads;
+        for (int64_t base = (int64_t)blockIdx.x * kThreads + threadIdx.x; base < others; base += stride * 8) {
+            float4 val[8];
+            int64_t at[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int64_t e = base + u * stride;
+                at[u] = -1;
+                if (e < others) {
+                    int src = (int)(e / per);
+                    if (src >= rank) ++src;  // skip this rank's own slice
+                    const int64_t i = (int64_t)src * per + e % per;
+                    if (i < n4_total) {
+                        at[u] = i;
+                        val[u] = ld_peer(reinterpret_cast<const float4 *>(peers.param[src]) + i);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (at[u] >= 0) own_param[at[u]] = val[u];
+        }
+    }
+
+    // the last block to finish everything resets the tickets and advances the step counter
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const int done = atomicAdd(state + 3, 1);
+        if (done == (int)gridDim.x - 1) {
+            stamps[5] = global_timer_ns();
             state[1] = 0;
+            state[3] = 0;
             state[0] = epoch;
         }
     }
@@ -195,9 +299,31 @@ extern "C" DL_API int dl_adam_exchange_step_f32(void *const *param_ptrs, void *c
     }
     const int64_t n4 = n / 4;
     const int64_t per = ceil_div(n4, world);
-    int64_t blocks = ceil_div(per > 0 ? per : 1, kThreads);
-    if (blocks > 148 * 4) blocks = 148 * 4;  // all blocks resident: none of them waits for another one of this grid
-    launch_dependent(true, adam_exchange_kernel, dim3((unsigned)blocks), dim3(kThreads), 0, as_stream(stream), peers, rank, world,
-                     exp_avg, exp_avg_sq, n4, lr, beta1, beta2, eps, reinterpret_cast<int *>(state));
+    // One wave of blocks that are all resident together: every block waits at barrier B for this grid's own last
+    // block, so a block that could not be scheduled would stall the others until their wait limit.  The limit is
+    // what the occupancy calculator gives for the kernel that is launched, not a constant.
+    const int per_thread = (world == 2 || world == 4 || world == 8) ? 8 / world : 1;
+    int *st = reinterpret_cast<int *>(state);
+    cudaStream_t cs = as_stream(stream);
+    auto launch = [&](auto kernel) -> int {
+        int dev = 0, sms = 0, per_sm = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || sms <= 0 || per_sm <= 0)
+            return launch_status("dl_adam_exchange_step_f32 (occupancy query)");
+        int64_t blocks = ceil_div(per > 0 ? per : 1, (int64_t)kThreads * per_thread);
+        const int64_t resident = (int64_t)sms * per_sm;
+        if (blocks > resident) blocks = resident;
+        launch_dependent(true, kernel, dim3((unsigned)blocks), dim3(kThreads), 0, cs, peers, rank, world, exp_avg, exp_avg_sq, n4, lr,
+                         beta1, beta2, eps, st);
+        return DL_OK;
+    };
+    int rc;
+    switch (world) {
+        case 2: rc = launch(adam_exchange_kernel<2>); break;
+        case 4: rc = launch(adam_exchange_kernel<4>); break;
+        case 8: rc = launch(adam_exchange_kernel<8>); break;
+        default: rc = launch(adam_exchange_kernel<0>); break;
+    }
+    if (rc != DL_OK) return rc;
     return launch_status("dl_adam_exchange_step_f32");
 }

@@ -155,9 +155,15 @@ groupsum_cluster_kernel(const float *__restrict__ x, float *__restrict__ out, in
 // 128 batch columns: the class's 128 gradient values are read once, then row after row is written.
 constexpr int kGbkRows = 128;  // rows per CTA
 
+//
+// With FROM_LOSS the class gradients are not read but formed from the softmax probabilities of a cross-entropy
+// loss (mean over the batch) on the GroupSum's scores: (probs[s][c] - [c == target[s]]) * grad_loss / batch, in the
+// same order of operations as the separate loss-backward kernel, so the result is bit-identical to running the two
+// kernels one after the other.
+template <bool FROM_LOSS>
 __global__ void __launch_bounds__(kThreads)
-groupsum_backward_kernel(const float *__restrict__ grad_out, float *__restrict__ grad_x, int64_t batch, int k, int m, float tau,
-                         int pieces) {
+groupsum_backward_kernel(const float *__restrict__ grad_out, const int64_t *__restrict__ target, const float *__restrict__ grad_loss,
+                         float *__restrict__ grad_x, int64_t batch, int k, int m, float tau, int pieces) {
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int c = blockIdx.x / pieces, piece = blockIdx.x % pieces;
     const int64_t r0 = (int64_t)c * m + ((int64_t)m * piece) / pieces;
@@ -165,8 +171,20 @@ groupsum_backward_kernel(const float *__restrict__ grad_out, float *__restrict__
     const int64_t col = (int64_t)blockIdx.y * kGsCols + lane * 4;
     grid_dependency_wait();  // grad_out comes from the loss' backward just before
     float v[4];
+    if (FROM_LOSS) {
+        const float scale = grad_loss[0] / (float)batch;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = (col + i < batch) ? __ldg(grad_out + (col + i) * k + c) / tau : 0.f;
+        for (int i = 0; i < 4; ++i) {
+            v[i] = 0.f;
+            if (col + i < batch) {
+                const float g = (grad_out[(col + i) * k + c] - (target[col + i] == c ? 1.f : 0.f)) * scale;
+                v[i] = g / tau;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = (col + i < batch) ? __ldg(grad_out + (col + i) * k + c) / tau : 0.f;
+    }
     if (batch % 4 == 0) {
         if (col >= batch) return;
         const float4 v4 = make_float4(v[0], v[1], v[2], v[3]);
@@ -250,9 +268,30 @@ extern "C" DL_API int dl_groupsum_backward_f32(const float *grad_out, float *gra
     const int64_t pieces = ceil_div(m, kGbkRows);
     const int64_t colblocks = ceil_div(batch, kGsCols);
     DL_REQUIRE(k * pieces <= INT32_MAX && colblocks <= 65535, DL_ERR_TOO_LARGE, "dl_groupsum_backward_f32: problem too large");
-    launch_dependent(true, groupsum_backward_kernel, dim3((unsigned)(k * pieces), (unsigned)colblocks), dim3(kThreads), 0,
-                     as_stream(stream), grad_out, grad_x, batch, (int)k, (int)m, tau, (int)pieces);
+    launch_dependent(true, groupsum_backward_kernel<false>, dim3((unsigned)(k * pieces), (unsigned)colblocks), dim3(kThreads), 0,
+                     as_stream(stream), grad_out, (const int64_t *)nullptr, (const float *)nullptr, grad_x, batch, (int)k, (int)m, tau,
+                     (int)pieces);
     return launch_status("dl_groupsum_backward_f32");
+}
+
+// Backward of cross_entropy(GroupSum(x)) in one launch: dl_cross_entropy_backward_f32 followed by
+// dl_groupsum_backward_f32 without the [batch][k] gradient in between.
+extern "C" DL_API int dl_groupsum_cross_entropy_backward_f32(const float *probs, const int64_t *target, const float *grad_loss,
+                                                             float *grad_x, int64_t n, int64_t batch, int64_t k, float tau,
+                                                             void *stream) {
+    if (int s = groupsum_check("dl_groupsum_cross_entropy_backward_f32", n, batch, k)) return s;
+    if (batch == 0 || n == 0) return DL_OK;
+    DL_REQUIRE(probs && target && grad_loss && grad_x, DL_ERR_INVALID_ARG, "dl_groupsum_cross_entropy_backward_f32: null pointer");
+    DL_REQUIRE(batch % 4 != 0 || aligned_to(grad_x, 16), DL_ERR_INVALID_ARG,
+               "dl_groupsum_cross_entropy_backward_f32: grad_x must be 16-byte aligned");
+    const int64_t m = n / k;
+    const int64_t pieces = ceil_div(m, kGbkRows);
+    const int64_t colblocks = ceil_div(batch, kGsCols);
+    DL_REQUIRE(k * pieces <= INT32_MAX && colblocks <= 65535, DL_ERR_TOO_LARGE,
+               "dl_groupsum_cross_entropy_backward_f32: problem too large");
+    launch_dependent(true, groupsum_backward_kernel<true>, dim3((unsigned)(k * pieces), (unsigned)colblocks), dim3(kThreads), 0,
+                     as_stream(stream), probs, target, grad_loss, grad_x, batch, (int)k, (int)m, tau, (int)pieces);
+    return launch_status("dl_groupsum_cross_entropy_backward_f32");
 }
 
 // ---------------------------------------------------------------------------------------------

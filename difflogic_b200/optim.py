@@ -112,7 +112,7 @@ class FlatAdam(torch.optim.Optimizer):
         per = -(-(n // 4) // world) * 4
         self.exp_avg = torch.zeros(per, dtype=torch.float32, device=dev)       # moments of this rank's slice only
         self.exp_avg_sq = torch.zeros(per, dtype=torch.float32, device=dev)
-        self.state_t = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.state_t = torch.zeros(16, dtype=torch.int32, device=dev)
         self._exchange = (rank, world)
         self.exchange_enabled = True
         torch.cuda.synchronize(dev)
@@ -122,6 +122,15 @@ class FlatAdam(torch.optim.Optimizer):
     def exchange_error(self):
         """True when a wait for a peer ever ran out of its poll limit (synchronises)."""
         return bool(int(self.state_t[2].item())) if getattr(self, "exchange_enabled", False) else False
+
+    def exchange_timing(self):
+        """Nanoseconds inside the latest exchange kernel on this rank (synchronises): waiting for all ranks' gradients,
+        reduce + Adam on this rank's slice, waiting for all ranks' slices, fetching the other slices."""
+        if not getattr(self, "exchange_enabled", False):
+            return None
+        t = self.state_t[4:16].cpu().view(torch.int64).tolist()
+        return {"wait_gradients_ns": t[1] - t[0], "slice_ns": t[2] - t[1], "wait_slices_ns": t[3] - t[2], "gather_ns": t[5] - t[3],
+                "total_ns": t[5] - t[0], "first_block_slice_ns": t[4] - t[1]}
 
     def grad_view(self, p):
         off, n = self._slices[p]

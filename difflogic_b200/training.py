@@ -18,13 +18,15 @@ import torch.distributed as dist
 
 
 class TrainStep:
-    def __init__(self, model, optimizer, loss_fn=None, process_group=None, world_size=None, buckets=2):
+    def __init__(self, model, optimizer, loss_fn=None, process_group=None, world_size=None, buckets=2, fuse_head=True):
         """
         :param model:         module on the current CUDA device (replicated on every rank)
         :param optimizer:     its optimizer; for `capture()` it must be graph-capturable
                               (difflogic_b200.optim.FlatAdam, or torch.optim.Adam(..., capturable=True))
         :param loss_fn:       defaults to CrossEntropyLoss (mean over the local batch)
         :param process_group: torch.distributed group to average gradients over, or None
+        :param fuse_head:     when the model ends in GroupSum and the loss is a default CrossEntropyLoss, run the two
+                              as one autograd node (same numbers, three kernels instead of five)
         :param buckets:       with FlatAdam: number of contiguous pieces of the flat gradient buffer that are
                               all-reduced separately (the piece holding the last layers first); 1 = one
                               all-reduce after the whole backward pass.  Other optimizers: one per parameter.
@@ -48,12 +50,36 @@ class TrainStep:
         self._pending = []
         # FlatAdam.enable_exchange(): gradients are averaged inside the optimizer's own kernel, nothing to do here
         self._exchange_in_optimizer = bool(getattr(optimizer, "exchange_enabled", False))
+        self._body = self._head = None
+        self._unit_grad = None     # gradient of the loss w.r.t. itself, made once (autograd would fill a new one per step)
+        if fuse_head and self._on_gpu and self._head_is_fusable(model, self.loss_fn):
+            self._body, self._head = model[:-1], model[-1]
         if self.group is not None and self.world_size > 1 and not self._exchange_in_optimizer:
             if self._on_gpu:
                 self._comm_stream = torch.cuda.Stream()
                 self._plan_buckets(max(1, int(buckets)))
             for p in self.params:
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._reduce_when_ready))
+
+    @staticmethod
+    def _head_is_fusable(model, loss_fn):
+        from .difflogic import GroupSum
+        from .losses import CrossEntropyLoss
+        if not (isinstance(model, torch.nn.Sequential) and len(model) >= 2 and isinstance(model[-1], GroupSum)):
+            return False
+        if isinstance(loss_fn, CrossEntropyLoss):
+            return True
+        return (type(loss_fn) is torch.nn.CrossEntropyLoss and loss_fn.weight is None and loss_fn.reduction == "mean"
+                and loss_fn.ignore_index == -100 and loss_fn.label_smoothing == 0.0)
+
+    def _loss(self, x, y):
+        if self._head is not None:
+            h = self._body(x)
+            if h.is_cuda and h.dtype == torch.float32 and h.dim() == 2 and y.dtype == torch.int64 and y.dim() == 1:
+                from .losses import group_sum_cross_entropy
+                return group_sum_cross_entropy(h, y, self._head.k, float(self._head.tau))[0]
+            return self.loss_fn(self._head(h), y)
+        return self.loss_fn(self.model(x), y)
 
     # -- gradient exchange -----------------------------------------------------------------------
 
@@ -110,15 +136,17 @@ class TrainStep:
     def _step(self, x, y):
         from . import difflogic as _dl
         self._pending = list(self._bucket_sizes)
-        loss = self.loss_fn(self.model(x), y)
+        loss = self._loss(x, y)
         self.optimizer.zero_grad(set_to_none=True)
+        if self._on_gpu and (self._unit_grad is None or self._unit_grad.device != loss.device):
+            self._unit_grad = torch.ones((), dtype=loss.dtype, device=loss.device)
         # backward_w of every layer runs on a side stream, off the chain of backward_x kernels -- unless gradient
         # hooks (the NCCL path) need the gradients in stream order
         side = self._bw_stream if (self._on_gpu and not self._hooks) else None
         if side is not None:
             _dl.set_backward_w_stream(side)
         try:
-            loss.backward()
+            loss.backward(gradient=self._unit_grad if self._on_gpu else None)
         finally:
             if side is not None:
                 _dl.set_backward_w_stream(None)

@@ -253,6 +253,11 @@ DL_API int dl_cross_entropy_f32(const float *logits, const int64_t *target, floa
                                 int64_t k, void *stream);
 DL_API int dl_cross_entropy_backward_f32(const float *probs, const int64_t *target, const float *grad_loss,
                                          float *grad_logits, int64_t batch, int64_t k, void *stream);
+/* Backward of loss_fn(GroupSum(x), y) in one launch: dl_cross_entropy_backward_f32 followed by
+ * dl_groupsum_backward_f32 (GroupSum of difflogic/difflogic.py:195-196 under the loss of experiments/main.py:167,175)
+ * without the [batch][k] gradient in between; bit-identical to the two calls.  grad_x is feature-major [n][batch]. */
+DL_API int dl_groupsum_cross_entropy_backward_f32(const float *probs, const int64_t *target, const float *grad_loss,
+                                                  float *grad_x, int64_t n, int64_t batch, int64_t k, float tau, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Adam step over a flat fp32 parameter vector (all layers' gate weights in one buffer).
@@ -279,9 +284,12 @@ DL_API int dl_adam_step_f32(float *param, const float *grad, float *exp_avg, flo
  * Per step: dl_adam_exchange_step_f32 gets HOST arrays of `world` device pointers (index = rank,
  * own entry = own buffers).  Rank r waits until all ranks' gradients are complete, averages slice r
  * of all ranks' gradients (peer loads), applies Adam to slice r with its moments (exp_avg,
- * exp_avg_sq hold ceil(n/4/world)*4 floats), writes the new slice into every rank's parameter
- * buffer and waits until all ranks have done the same.  n: floats per buffer, a multiple of 4.
- * state: four int32 on the device, zero at first: {steps done, ticket, error, unused}; error
+ * exp_avg_sq hold ceil(n/4/world)*4 floats), writes the new slice into its own parameter buffer, waits
+ * until all ranks have done the same and fetches their slices.  n: floats per buffer, a multiple of 4.
+ * state: sixteen int32 on the device, zero at first: {steps done, ticket, error, ticket} followed by six
+ * 64-bit nanosecond time stamps of the latest step (%globaltimer of this GPU: kernel entered, all ranks'
+ * gradients seen complete, this rank's slice done, all ranks' slices seen complete, first block's elements
+ * stored, kernel done); error
  * becomes 1 when a wait for a peer ran out of its poll limit (the step then used stale data).
  * All ranks must call it the same number of times; the kernels of one step must be able to run at
  * the same time, i.e. one rank per GPU.
