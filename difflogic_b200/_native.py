@@ -56,6 +56,7 @@ SIGNATURES = {
     "dl_comm_close": (_int, [_ptr]),
     "dl_adam_exchange_step_f32": (_int, [_ptr, _ptr, _ptr, _int, _int, _ptr, _ptr, _i64, _f32, _f32, _f32, _f32, _ptr, _ptr]),
     "dl_adam_step_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _f32, _f32, _f32, _f32, _f32, _ptr, _ptr]),
+    "dl_prefetch_l2": (_int, [_ptr, ctypes.c_size_t, _ptr]),
 }
 
 _lib = None

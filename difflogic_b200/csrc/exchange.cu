@@ -23,6 +23,7 @@
 // in the state words and carries on, so a missing rank cannot hang the others.
 #include <string.h>
 
+#include "adam_math.cuh"
 #include "common.cuh"
 
 namespace dl {
@@ -104,14 +105,7 @@ adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict
     float4 *m4 = reinterpret_cast<float4 *>(m), *v4 = reinterpret_cast<float4 *>(v);  // moments of the slice only
     float4 *own_param = reinterpret_cast<float4 *>(peers.param[rank]);
 
-#define DL_ADAM1(c)                                          \
-    {                                                        \
-        const float gr = g.c * inv_world;                    \
-        mm.c = mm.c + (gr - mm.c) * omb1;                    \
-        vv.c = vv.c * beta2 + gr * gr * omb2;                \
-        const float denom = sqrtf(vv.c) / bc2_sqrt + eps;    \
-        pp.c = pp.c - step_size * (mm.c / denom);            \
-    }
+    const AdamConsts consts = {omb1, beta2, omb2, step_size, bc2_sqrt, eps};
     if (WORLD > 0) {
         constexpr int W = WORLD > 0 ? WORLD : 1;
         constexpr int U = 8 / W;  // elements per thread and iteration
@@ -139,7 +133,9 @@ adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict
                         g.x += gp[u][p].x; g.y += gp[u][p].y; g.z += gp[u][p].z; g.w += gp[u][p].w;
                     }
                     float4 pp = pp_[u], mm = mm_[u], vv = vv_[u];
-                    DL_ADAM1(x) DL_ADAM1(y) DL_ADAM1(z) DL_ADAM1(w)
+                    g.x = __fmul_rn(g.x, inv_world); g.y = __fmul_rn(g.y, inv_world);
+                    g.z = __fmul_rn(g.z, inv_world); g.w = __fmul_rn(g.w, inv_world);
+                    adam_update4(pp, g, mm, vv, consts);
                     m4[i - lo] = mm;
                     v4[i - lo] = vv;
                     own_param[i] = pp;
@@ -155,13 +151,14 @@ adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict
             }
             float4 pp = own_param[i];
             float4 mm = m4[i - lo], vv = v4[i - lo];
-            DL_ADAM1(x) DL_ADAM1(y) DL_ADAM1(z) DL_ADAM1(w)
+            g.x = __fmul_rn(g.x, inv_world); g.y = __fmul_rn(g.y, inv_world);
+            g.z = __fmul_rn(g.z, inv_world); g.w = __fmul_rn(g.w, inv_world);
+            adam_update4(pp, g, mm, vv, consts);
             m4[i - lo] = mm;
             v4[i - lo] = vv;
             own_param[i] = pp;
         }
     }
-#undef DL_ADAM1
     if (blockIdx.x == 0 && threadIdx.x == 0) stamps[4] = global_timer_ns();  // first block: its elements are stored
 
     // barrier B: the last block of this rank to finish its part of the slice tells the peers; every block then waits

@@ -50,10 +50,13 @@ class _GroupSumCrossEntropyFunction(torch.autograd.Function):
         ctx.save_for_backward(probs, target)
         ctx.k, ctx.tau, ctx.n = k, tau, x.shape[1]
         ctx.mark_non_differentiable(scores)
+        ctx.set_materialize_grads(False)  # no zero-filled gradient for `scores`
         return loss, scores
 
     @staticmethod
     def backward(ctx, grad_loss, _grad_scores):
+        if grad_loss is None:
+            return None, None, None, None
         probs, target = ctx.saved_tensors
         batch = probs.shape[0]
         gx = torch.empty((ctx.n, batch), dtype=torch.float32, device=probs.device)

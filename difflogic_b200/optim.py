@@ -132,6 +132,14 @@ class FlatAdam(torch.optim.Optimizer):
         return {"wait_gradients_ns": t[1] - t[0], "slice_ns": t[2] - t[1], "wait_slices_ns": t[3] - t[2], "gather_ns": t[5] - t[3],
                 "total_ns": t[5] - t[0], "first_block_slice_ns": t[4] - t[1]}
 
+    def prefetch_state(self):
+        """Launches (on the current stream) a kernel that pulls the moments towards L2.  They are touched once per step,
+        so a step that begins with a cold L2 otherwise reads them from HBM at the very end, after the last gradient."""
+        with torch.cuda.device(self.flat_param.device):
+            st = N.stream_of(self.flat_param)
+            for t in (self.exp_avg, self.exp_avg_sq):
+                N.check(N.lib().dl_prefetch_l2(t.data_ptr(), t.numel() * 4, st))
+
     def grad_view(self, p):
         off, n = self._slices[p]
         return self.flat_grad[off:off + n].view_as(p)

@@ -145,6 +145,11 @@ class TrainStep:
         side = self._bw_stream if (self._on_gpu and not self._hooks) else None
         if side is not None:
             _dl.set_backward_w_stream(side)
+            if hasattr(self.optimizer, "prefetch_state"):
+                # warm the optimizer's moments in L2 beside the backward pass
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    self.optimizer.prefetch_state()
         try:
             loss.backward(gradient=self._unit_grad if self._on_gpu else None)
         finally:

@@ -270,6 +270,9 @@ DL_API int dl_groupsum_cross_entropy_backward_f32(const float *probs, const int6
  * ---------------------------------------------------------------------------------------- */
 DL_API int dl_adam_step_f32(float *param, const float *grad, float *exp_avg, float *exp_avg_sq, int64_t n, float lr,
                             float beta1, float beta2, float eps, float grad_scale, int32_t *state, void *stream);
+/* Pulls [ptr, ptr + bytes) towards L2 (prefetch.global.L2, 128-byte lines); no result, no reference counterpart.
+ * Used on a side stream during the backward pass to warm the Adam moments, which are touched once per step. */
+DL_API int dl_prefetch_l2(const void *ptr, size_t bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Batch-sharded training: gradient exchange and Adam in one kernel over peer memory.
