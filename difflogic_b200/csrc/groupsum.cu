@@ -151,6 +151,135 @@ groupsum_cluster_kernel(const float *__restrict__ x, float *__restrict__ out, in
     cluster.sync();  // the other CTAs' shared memory must stay alive until the first one has read it
 }
 
+// GroupSum forward + cross-entropy loss (mean over the batch) + the gradient of the loss w.r.t. the class scores, in
+// ONE launch: the head of a training step.  Same cluster scheme as above with one barrier less (every CTA pushes its
+// piece into the first CTA's shared memory, then one cluster barrier), and the first CTA of the cluster that finishes
+// LAST (a ticket in global memory) computes the loss over all samples:
+//   scores[s][c] = class sums / tau;  p = softmax(scores[s]);  loss = -(1/B) sum_s log p[s][target[s]]
+//   grad_classes[c][s] = ((p[s][c] - [c == target[s]]) * (1/B)) / tau      -- feature-major [k][batch]
+// grad_classes is what the last layer's backward kernels read as "one grad_y row per class"
+// (dl_backward_w_classes_f32 / dl_backward_x_classes_f32): the [n][batch] gradient of the layer's output, whose rows
+// are equal within a class, is never formed.  The arithmetic per sample is that of cross_entropy_kernel followed by
+// cross_entropy_backward_kernel (grad_loss = 1) and groupsum_backward_kernel, in the same order.
+__global__ void __launch_bounds__(kGcThreads)
+groupsum_ce_kernel(const float *__restrict__ x, const int64_t *__restrict__ target, float *__restrict__ scores,
+                   float *__restrict__ loss, float *__restrict__ grad_classes, unsigned int *__restrict__ counter, int64_t batch,
+                   int k, int m, float tau) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float s_part[kGcThreads / 32][kGsCols];
+    __shared__ float s_all[kGcCluster][kGsCols];  // used in the first CTA of the cluster: the pieces of all CTAs
+    __shared__ float s_red[kGcThreads / 32];
+    __shared__ bool s_last;
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int colblock = blockIdx.x, c = blockIdx.y;
+    const int q = (int)cluster.block_rank(), nq = (int)cluster.num_blocks();
+    const int64_t col0 = (int64_t)colblock * kGsCols + lane * 4;
+    const int64_t rbeg = (int64_t)c * m + ((int64_t)m * q) / nq;
+    const int64_t rend = (int64_t)c * m + ((int64_t)m * (q + 1)) / nq;
+
+    grid_dependency_wait();  // x is the output of the kernel just before
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if ((batch % 4 == 0) && col0 + 3 < batch) {
+#pragma unroll 16
+        for (int64_t r = rbeg + warp; r < rend; r += kGcThreads / 32) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(x + r * batch + col0));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    } else {
+        for (int64_t r = rbeg + warp; r < rend; r += kGcThreads / 32) {
+            const float *p = x + r * batch + col0;
+            if (col0 + 0 < batch) acc.x += __ldg(p + 0);
+            if (col0 + 1 < batch) acc.y += __ldg(p + 1);
+            if (col0 + 2 < batch) acc.z += __ldg(p + 2);
+            if (col0 + 3 < batch) acc.w += __ldg(p + 3);
+        }
+    }
+    s_part[warp][lane * 4 + 0] = acc.x;
+    s_part[warp][lane * 4 + 1] = acc.y;
+    s_part[warp][lane * 4 + 2] = acc.z;
+    s_part[warp][lane * 4 + 3] = acc.w;
+    __syncthreads();
+    if (tid < kGsCols) {
+        float sum = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < kGcThreads / 32; ++wv) sum += s_part[wv][tid];
+        *cluster.map_shared_rank(&s_all[q][tid], 0) = sum;  // into the first CTA's shared memory
+    }
+    cluster.sync();
+    if (q != 0) return;
+    const int64_t gcol = (int64_t)colblock * kGsCols + tid;
+    if (tid < kGsCols && gcol < batch) {
+        float total = 0.f;
+        for (int r = 0; r < nq; ++r) total += s_all[r][tid];  // same order as groupsum_cluster_kernel
+        scores[gcol * k + c] = total / tau;
+    }
+    // ---- ticket: the first CTA of the last cluster to get here computes the loss
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int total_units = gridDim.x * gridDim.y;
+        s_last = atomicAdd(counter, 1u) == total_units - 1u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float scale = 1.f / (float)batch;
+    float local = 0.f;
+    constexpr int kRowRegs = 16;  // classes held in registers (one read of the scores instead of three)
+    for (int64_t s = tid; s < batch; s += kGcThreads) {
+        const float *row = scores + s * k;
+        const int64_t t = target[s];
+        if (k <= kRowRegs) {
+            float r[kRowRegs];
+#pragma unroll
+            for (int cc = 0; cc < kRowRegs; ++cc) r[cc] = cc < k ? __ldcg(row + cc) : -INFINITY;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int cc = 0; cc < kRowRegs; ++cc) mx = fmaxf(mx, r[cc]);  // the padding never wins: max is order-free
+            float sum = 0.f;
+#pragma unroll
+            for (int cc = 0; cc < kRowRegs; ++cc)
+                if (cc < k) sum += expf(r[cc] - mx);
+            const float lse = mx + logf(sum);
+#pragma unroll
+            for (int cc = 0; cc < kRowRegs; ++cc) {
+                if (cc < k) {
+                    const float p = expf(r[cc] - lse);
+                    const float g = (p - (t == cc ? 1.f : 0.f)) * scale;
+                    grad_classes[(int64_t)cc * batch + s] = g / tau;
+                    if (t == cc) local += lse - r[cc];
+                }
+            }
+        } else {
+            float mx = -INFINITY;
+            for (int cc = 0; cc < k; ++cc) mx = fmaxf(mx, __ldcg(row + cc));
+            float sum = 0.f;
+            for (int cc = 0; cc < k; ++cc) sum += expf(__ldcg(row + cc) - mx);
+            const float lse = mx + logf(sum);
+            for (int cc = 0; cc < k; ++cc) {
+                const float p = expf(__ldcg(row + cc) - lse);
+                const float g = (p - (t == cc ? 1.f : 0.f)) * scale;
+                grad_classes[(int64_t)cc * batch + s] = g / tau;
+            }
+            if (t >= 0 && t < k) local += lse - __ldcg(row + t);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
+    if (lane == 0) s_red[warp] = local;
+    __syncthreads();
+    if (warp == 0) {
+        float v = lane < kGcThreads / 32 ? s_red[lane] : 0.f;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) {
+            loss[0] = v / (float)batch;
+            *counter = 0u;  // ready for the next call
+        }
+    }
+}
+
 // Backward: grad_x[i][:] = grad_out[:, class(i)] / tau.  A CTA takes a run of rows of one class and a block of
 // 128 batch columns: the class's 128 gradient values are read once, then row after row is written.
 constexpr int kGbkRows = 128;  // rows per CTA
@@ -272,6 +401,41 @@ extern "C" DL_API int dl_groupsum_backward_f32(const float *grad_out, float *gra
                      as_stream(stream), grad_out, (const int64_t *)nullptr, (const float *)nullptr, grad_x, batch, (int)k, (int)m, tau,
                      (int)pieces);
     return launch_status("dl_groupsum_backward_f32");
+}
+
+// 1 when dl_groupsum_cross_entropy_f32 takes these sizes (classes of 64 .. 4096 rows), else 0.
+extern "C" DL_API int dl_groupsum_cross_entropy_applicable(int64_t n, int64_t batch, int64_t k) {
+    if (n <= 0 || batch <= 0 || k <= 0 || k > 65535 || n % k != 0) return 0;
+    const int64_t m = n / k;
+    return m >= 64 && m <= 4096 && ceil_div(batch, kGsCols) <= 65535 ? 1 : 0;
+}
+
+// counter: one uint32 on the device, zero before the first call; the kernel leaves it zero.
+extern "C" DL_API int dl_groupsum_cross_entropy_f32(const float *x, const int64_t *target, float *scores, float *loss,
+                                                    float *grad_classes, void *counter, int64_t n, int64_t batch, int64_t k, float tau,
+                                                    void *stream) {
+    if (int s = groupsum_check("dl_groupsum_cross_entropy_f32", n, batch, k)) return s;
+    DL_REQUIRE(dl_groupsum_cross_entropy_applicable(n, batch, k) == 1, DL_ERR_INVALID_ARG,
+               "dl_groupsum_cross_entropy_f32: classes of %lld rows are outside 64 .. 4096", (long long)(k > 0 ? n / k : 0));
+    DL_REQUIRE(x && target && scores && loss && grad_classes && counter, DL_ERR_INVALID_ARG,
+               "dl_groupsum_cross_entropy_f32: null pointer");
+    DL_REQUIRE(batch % 4 != 0 || aligned_to(x, 16), DL_ERR_INVALID_ARG, "dl_groupsum_cross_entropy_f32: x must be 16-byte aligned");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ceil_div(batch, kGsCols), (unsigned)k, kGcCluster);
+    cfg.blockDim = dim3(kGcThreads);
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = kGcCluster;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    cudaLaunchKernelEx(&cfg, groupsum_ce_kernel, x, target, scores, loss, grad_classes, reinterpret_cast<unsigned int *>(counter), batch,
+                       (int)k, (int)(n / k), tau);
+    return launch_status("dl_groupsum_cross_entropy_f32");
 }
 
 // Backward of cross_entropy(GroupSum(x)) in one launch: dl_cross_entropy_backward_f32 followed by

@@ -133,11 +133,18 @@ __device__ __forceinline__ void acc4(float &s0, float &sa, float &sb, float &sab
     sab += va * vb * g;
 }
 
+// Row of grad_y that holds the gradient of output row j.  gy_group == 1: its own row.  gy_group == g > 1: the layer's
+// outputs are summed in classes of g consecutive rows (GroupSum) and grad_y has one row per CLASS -- the gradient of
+// every row of a class is the same, so it is not expanded to [n_out][batch] in memory.
+__device__ __forceinline__ int64_t gy_row(int64_t j, int gy_group) {
+    return gy_group == 1 ? j : (int64_t)((int)j / gy_group);
+}
+
 template <int G, bool VEC4>
 __global__ void __launch_bounds__(kThreads)
 backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
                   const float *__restrict__ gy, const float *__restrict__ w, int w_mode, float *__restrict__ grad_w,
-                  int64_t n_out, int64_t batch, int64_t ncols) {
+                  int64_t n_out, int64_t batch, int64_t ncols, int gy_group) {
     using V = typename Vec<VEC4>::type;
     constexpr int R = kThreads / G;
     // The 16 gates of the neuron are shared by P lanes of its group, K gates each.
@@ -169,7 +176,7 @@ backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, co
     if (active) {
         const V *xa = reinterpret_cast<const V *>(x + ia);
         const V *xb = reinterpret_cast<const V *>(x + ib);
-        const V *g = reinterpret_cast<const V *>(gy + j * batch);
+        const V *g = reinterpret_cast<const V *>(gy + gy_row(j, gy_group) * batch);
 #pragma unroll 4
         for (int64_t col = lane; col < ncols; col += G) acc4(s0, sa, sb, sab, ldv(xa + col), ldv(xb + col), ldv(g + col));
     }
@@ -237,7 +244,7 @@ template <int G, bool VEC4>
 __global__ void __launch_bounds__(kThreads)
 backward_x_kernel(const float *__restrict__ x, const float4 *__restrict__ coef, const float *__restrict__ gy,
                   const int64_t *__restrict__ start, const int2 *__restrict__ plan, float scale,
-                  float *__restrict__ gx, int64_t n_in, int64_t batch, int64_t ncols, int64_t nslabs) {
+                  float *__restrict__ gx, int64_t n_in, int64_t batch, int64_t ncols, int64_t nslabs, int gy_group) {
     using V = typename Vec<VEC4>::type;
     constexpr int R = kThreads / G;
     constexpr int C = 4;  // columns per lane within a slab: lane, lane+G, lane+2G, lane+3G
@@ -262,8 +269,8 @@ backward_x_kernel(const float *__restrict__ x, const float4 *__restrict__ coef, 
     if (e0 < e1) c0 = __ldg(coef + (p0.x >> 1));
     if (e0 + 1 < e1) c1 = __ldg(coef + (p1.x >> 1));
     const float k0 = (p0.x & 1) ? c0.z : c0.y, k1 = (p1.x & 1) ? c1.z : c1.y;
-    const float *xp0 = x + (int64_t)p0.y * batch, *gp0 = gy + (int64_t)(p0.x >> 1) * batch;
-    const float *xp1 = x + (int64_t)p1.y * batch, *gp1 = gy + (int64_t)(p1.x >> 1) * batch;
+    const float *xp0 = x + (int64_t)p0.y * batch, *gp0 = gy + gy_row(p0.x >> 1, gy_group) * batch;
+    const float *xp1 = x + (int64_t)p1.y * batch, *gp1 = gy + gy_row(p1.x >> 1, gy_group) * batch;
     const bool has0 = e0 < e1, has1 = e0 + 1 < e1;
 
     for (int64_t slab = blockIdx.y; slab < nslabs; slab += gridDim.y) {
@@ -289,7 +296,7 @@ backward_x_kernel(const float *__restrict__ x, const float4 *__restrict__ coef, 
                 const int64_t j = p.x >> 1;
                 const float4 c = __ldg(coef + j);
                 const V vp = ldv(reinterpret_cast<const V *>(x + (int64_t)p.y * batch + off));
-                const V vg = ldv(reinterpret_cast<const V *>(gy + j * batch + off));
+                const V vg = ldv(reinterpret_cast<const V *>(gy + gy_row(j, gy_group) * batch + off));
                 bx_acc(acc, (p.x & 1) ? c.z : c.y, c.w, vp, vg);
             }
             *reinterpret_cast<V *>(gx + i * batch + off) = scaled(acc, scale);
@@ -340,11 +347,11 @@ static int launch_forward(bool overlap, int G, const float *x, const int64_t *a,
 
 template <bool VEC4>
 static int launch_backward_w(bool overlap, int G, const float *x, const int64_t *a, const int64_t *b, const float *gy, const float *w,
-                             int w_mode, float *grad_w, int64_t n_out, int64_t batch, int64_t ncols, cudaStream_t st) {
+                             int w_mode, float *grad_w, int64_t n_out, int64_t batch, int64_t ncols, int gy_group, cudaStream_t st) {
     const unsigned grid = (unsigned)ceil_div(n_out, kThreads / G);
 #define DL_BW(GG)                                                                                          \
     case GG:                                                                                               \
-        launch_dependent(overlap, backward_w_kernel<GG, VEC4>, dim3(grid), dim3(kThreads), 0, st, x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols); \
+        launch_dependent(overlap, backward_w_kernel<GG, VEC4>, dim3(grid), dim3(kThreads), 0, st, x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols, gy_group); \
         break;
     switch (G) {
         DL_BW(1) DL_BW(2) DL_BW(4) DL_BW(8) DL_BW(16) DL_BW(32)
@@ -355,7 +362,7 @@ static int launch_backward_w(bool overlap, int G, const float *x, const int64_t 
 
 template <bool VEC4>
 static int launch_backward_x(bool overlap, int G, const float *x, const float *coef, const float *gy, const int64_t *start,
-                             const int32_t *plan, float scale, float *gx, int64_t n_in, int64_t batch, int64_t ncols,
+                             const int32_t *plan, float scale, float *gx, int64_t n_in, int64_t batch, int64_t ncols, int gy_group,
                              cudaStream_t st) {
     const int64_t nslabs = ceil_div(ncols, G * 4);
     const dim3 grid((unsigned)ceil_div(n_in, kThreads / G), slab_grid(nslabs));
@@ -363,7 +370,7 @@ static int launch_backward_x(bool overlap, int G, const float *x, const float *c
     const int2 *p2 = reinterpret_cast<const int2 *>(plan);
 #define DL_BX(GG)                                                                                               \
     case GG:                                                                                                    \
-        launch_dependent(overlap, backward_x_kernel<GG, VEC4>, grid, dim3(kThreads), 0, st, x, c4, gy, start, p2, scale, gx, n_in, batch, ncols, nslabs); \
+        launch_dependent(overlap, backward_x_kernel<GG, VEC4>, grid, dim3(kThreads), 0, st, x, c4, gy, start, p2, scale, gx, n_in, batch, ncols, nslabs, gy_group); \
         break;
     switch (G) {
         DL_BX(1) DL_BX(2) DL_BX(4) DL_BX(8) DL_BX(16) DL_BX(32)
@@ -394,8 +401,10 @@ extern "C" DL_API int dl_forward_f32(const float *x, const int64_t *a, const int
                : launch_forward<false>(overlap, G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream));
 }
 
-extern "C" DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
-                                 int w_mode, float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int flags, void *stream) {
+static int backward_w_entry(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w, int w_mode,
+                            float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int64_t gy_group, int flags, void *stream) {
+    DL_REQUIRE(gy_group >= 1 && gy_group <= INT32_MAX && n_out % gy_group == 0, DL_ERR_INVALID_ARG,
+               "dl_backward_w_f32: n_out (%lld) is not a multiple of the rows per class (%lld)", (long long)n_out, (long long)gy_group);
     DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_backward_w_f32: negative size");
     DL_REQUIRE(w_mode == DL_W_LOGITS || w_mode == DL_W_PROBS, DL_ERR_INVALID_ARG,
                "dl_backward_w_f32: w_mode must be DL_W_LOGITS or DL_W_PROBS, got %d", w_mode);
@@ -407,13 +416,27 @@ extern "C" DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const 
     const int64_t ncols = vec ? batch / 4 : batch;
     const int G = pow2_at_least(ceil_div(ncols, 4), 32);
     const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
-    return vec ? launch_backward_w<true>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, as_stream(stream))
-               : launch_backward_w<false>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, as_stream(stream));
+    return vec ? launch_backward_w<true>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, as_stream(stream))
+               : launch_backward_w<false>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, as_stream(stream));
 }
 
-extern "C" DL_API int dl_backward_x_f32(const float *x, const float *coef, const float *grad_y, const int64_t *start,
-                                 const int32_t *plan, float grad_scale, float *grad_x, int64_t n_in, int64_t n_out,
-                                 int64_t batch, int flags, void *stream) {
+extern "C" DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
+                                 int w_mode, float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int flags, void *stream) {
+    return backward_w_entry(x, a, b, grad_y, w, w_mode, grad_w, n_in, n_out, batch, 1, flags, stream);
+}
+
+// grad_y has one row per class of `rows_per_class` consecutive outputs ([n_out / rows_per_class][batch]).
+extern "C" DL_API int dl_backward_w_classes_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y_classes,
+                                                const float *w, int w_mode, float *grad_w, int64_t n_in, int64_t n_out, int64_t batch,
+                                                int64_t rows_per_class, int flags, void *stream) {
+    return backward_w_entry(x, a, b, grad_y_classes, w, w_mode, grad_w, n_in, n_out, batch, rows_per_class, flags, stream);
+}
+
+static int backward_x_entry(const float *x, const float *coef, const float *grad_y, const int64_t *start, const int32_t *plan,
+                            float grad_scale, float *grad_x, int64_t n_in, int64_t n_out, int64_t batch, int64_t gy_group, int flags,
+                            void *stream) {
+    DL_REQUIRE(gy_group >= 1 && gy_group <= INT32_MAX && n_out % gy_group == 0, DL_ERR_INVALID_ARG,
+               "dl_backward_x_f32: n_out (%lld) is not a multiple of the rows per class (%lld)", (long long)n_out, (long long)gy_group);
     DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_backward_x_f32: negative size");
     DL_REQUIRE(n_out < kMaxRows && n_in < 2 * kMaxRows, DL_ERR_TOO_LARGE, "dl_backward_x_f32: more than 2^30 neurons");
     if (n_in == 0 || batch == 0) return DL_OK;
@@ -425,8 +448,21 @@ extern "C" DL_API int dl_backward_x_f32(const float *x, const float *coef, const
     const int64_t ncols = vec ? batch / 4 : batch;
     const int G = pow2_at_least(ceil_div(ncols, 4), 32);
     const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
-    return vec ? launch_backward_x<true>(overlap, G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, as_stream(stream))
-               : launch_backward_x<false>(overlap, G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, as_stream(stream));
+    return vec ? launch_backward_x<true>(overlap, G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, (int)gy_group, as_stream(stream))
+               : launch_backward_x<false>(overlap, G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, (int)gy_group, as_stream(stream));
+}
+
+extern "C" DL_API int dl_backward_x_f32(const float *x, const float *coef, const float *grad_y, const int64_t *start,
+                                 const int32_t *plan, float grad_scale, float *grad_x, int64_t n_in, int64_t n_out,
+                                 int64_t batch, int flags, void *stream) {
+    return backward_x_entry(x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, n_out, batch, 1, flags, stream);
+}
+
+// grad_y has one row per class of `rows_per_class` consecutive outputs ([n_out / rows_per_class][batch]).
+extern "C" DL_API int dl_backward_x_classes_f32(const float *x, const float *coef, const float *grad_y_classes, const int64_t *start,
+                                                const int32_t *plan, float grad_scale, float *grad_x, int64_t n_in, int64_t n_out,
+                                                int64_t batch, int64_t rows_per_class, int flags, void *stream) {
+    return backward_x_entry(x, coef, grad_y_classes, start, plan, grad_scale, grad_x, n_in, n_out, batch, rows_per_class, flags, stream);
 }
 
 extern "C" DL_API int dl_build_backward_plan(const int64_t *a, const int64_t *b, const int64_t *start, const int64_t *list,

@@ -290,6 +290,71 @@ class LogicLayerFunction(torch.autograd.Function):
         return grad_x, grad_w, None, None, None, None, None, None
 
 
+class LogicLayerHeadFunction(torch.autograd.Function):
+    """The LAST logic layer, GroupSum and the mean cross-entropy loss as one autograd node (training).
+
+    forward : layer forward, then ONE kernel for the class sums, the loss and the gradient of the loss w.r.t. the
+              class scores (ops.groupsum_cross_entropy);
+    backward: the layer's backward_w / backward_x read that gradient as "one row per class" -- the `[n, batch]`
+              gradient of the layer's output, whose rows are equal within a class, is never formed.
+    Replaces LogicLayerFunction -> GroupSumFunction -> CrossEntropyLoss for the tail of
+    `loss_fn(model(x), y)` (experiments/main.py:175) with the same numbers."""
+
+    @staticmethod
+    def forward(ctx, x, weights, a, b, start, plan, grad_factor, grad_out, target, k, tau):
+        y, coef = ops.logic_forward(x, a, b, weights, ops.W_LOGITS, want_coef=True, overlap=True)
+        loss, scores, grad_classes = ops.groupsum_cross_entropy(y, target, k, tau)
+        ctx.save_for_backward(x, weights, a, b, start, plan, coef, grad_classes)
+        ctx.grad_factor, ctx.grad_out, ctx.rows_per_class = grad_factor, grad_out, y.shape[0] // k
+        ctx.mark_non_differentiable(scores)
+        ctx.set_materialize_grads(False)
+        return loss, scores
+
+    @staticmethod
+    def backward(ctx, grad_loss, _grad_scores):
+        if grad_loss is None:
+            return (None,) * 11
+        x, weights, a, b, start, plan, coef, grad_classes = ctx.saved_tensors
+        if not getattr(grad_loss, '_dl_is_one', False):
+            grad_classes = grad_classes * grad_loss     # a gradient other than the marked unit tensor: scale (one more kernel)
+        m = ctx.rows_per_class
+        grad_x = grad_w = None
+        side = _backward_w_stream if (ctx.needs_input_grad[0] and ctx.needs_input_grad[1]) else None
+        if side is not None:
+            main = torch.cuda.current_stream(x.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                grad_w = ops.logic_backward_w(x, a, b, grad_classes, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True,
+                                              rows_per_class=m)
+            for t in (x, grad_classes, weights):
+                t.record_stream(side)
+            grad_x = ops.logic_backward_x(x, coef, grad_classes, start, plan, ctx.grad_factor, overlap=True, rows_per_class=m)
+        else:
+            if ctx.needs_input_grad[0]:
+                grad_x = ops.logic_backward_x(x, coef, grad_classes, start, plan, ctx.grad_factor, overlap=True, rows_per_class=m)
+            if ctx.needs_input_grad[1]:
+                grad_w = ops.logic_backward_w(x, a, b, grad_classes, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True,
+                                              rows_per_class=m)
+        if grad_w is not None and ctx.grad_out is not None:
+            grad_w = grad_w.view(grad_w.shape)  # a fresh alias: autograd adopts it as `weights.grad` without copying
+        return (grad_x, grad_w) + (None,) * 9
+
+
+def logic_layer_head(layer, x, target, k, tau):
+    """(loss, scores) of `CrossEntropyLoss()(GroupSum(k, tau)(layer(x)), target)` for a CUDA LogicLayer in training mode
+    and `x` of shape `[batch, in_dim]`; None when the fused kernel does not take the sizes (the caller then runs the
+    three modules)."""
+    if not (layer.training and layer._plan is not None and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2
+            and target.dtype == torch.int64 and target.dim() == 1 and layer.out_dim % k == 0
+            and ops.groupsum_cross_entropy_applicable(layer.out_dim, x.shape[0], k)):
+        return None
+    xt = x.transpose(0, 1).contiguous()
+    a, b = layer.indices
+    return LogicLayerHeadFunction.apply(xt, layer.weights, a, b, layer.given_x_indices_of_y_start, layer._plan,
+                                        float(layer.grad_factor), getattr(layer.weights, '_dl_grad_out', None),
+                                        target.contiguous(), int(k), float(tau))
+
+
 class LogicLayerCudaFunction(torch.autograd.Function):
     """The reference's autograd node with its exact signature (difflogic.py:205-221): `w` holds mixing
     weights that are already soft-maxed, and the result is the gradient w.r.t. those."""

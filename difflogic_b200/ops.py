@@ -68,13 +68,16 @@ def logic_coefs(w, w_mode=W_LOGITS):
     return coef
 
 
-def logic_backward_w(x, a, b, grad_y, w=None, w_mode=W_PROBS, out=None, overlap=False):
+def logic_backward_w(x, a, b, grad_y, w=None, w_mode=W_PROBS, out=None, overlap=False, rows_per_class=1):
     """[n_out,16] gradient: w_mode=W_PROBS w.r.t. the mixing weights, W_LOGITS w.r.t. the raw
-    parameters `w` (softmax backward applied in the kernel)."""
+    parameters `w` (softmax backward applied in the kernel).  rows_per_class > 1: grad_y holds one row per class of
+    that many consecutive outputs (the gradient that comes back through a GroupSum), [n_out / rows_per_class, batch]."""
     _f32_matrix(x, "x")
     _f32_matrix(grad_y, "grad_y")
     n_in, batch = x.shape
-    n_out = grad_y.shape[0]
+    rows_per_class = int(rows_per_class)
+    _need(rows_per_class >= 1, "rows_per_class must be positive")
+    n_out = grad_y.shape[0] * rows_per_class
     _need(grad_y.shape[1] == batch, "grad_y and x disagree on the batch size")
     _index(a, "a", n_out)
     _index(b, "b", n_out)
@@ -88,8 +91,13 @@ def logic_backward_w(x, a, b, grad_y, w=None, w_mode=W_PROBS, out=None, overlap=
         _f32_matrix(out, "out")
         _need(tuple(out.shape) == (n_out, 16), "out must be [n_out, 16]")
     with torch.cuda.device(x.device):
-        N.check(N.lib().dl_backward_w_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), grad_y.data_ptr(), N.ptr(w), w_mode,
-                                          out.data_ptr(), n_in, n_out, batch, int(overlap), N.stream_of(x)))
+        if rows_per_class == 1:
+            N.check(N.lib().dl_backward_w_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), grad_y.data_ptr(), N.ptr(w), w_mode,
+                                              out.data_ptr(), n_in, n_out, batch, int(overlap), N.stream_of(x)))
+        else:
+            N.check(N.lib().dl_backward_w_classes_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), grad_y.data_ptr(), N.ptr(w), w_mode,
+                                                      out.data_ptr(), n_in, n_out, batch, rows_per_class, int(overlap),
+                                                      N.stream_of(x)))
     return out
 
 
@@ -119,12 +127,15 @@ def build_backward_plan(a, b, start, lst):
     return plan
 
 
-def logic_backward_x(x, coef, grad_y, start, plan, grad_scale=1.0, overlap=False):
+def logic_backward_x(x, coef, grad_y, start, plan, grad_scale=1.0, overlap=False, rows_per_class=1):
+    """Gradient w.r.t. the layer's input.  rows_per_class > 1: grad_y holds one row per class (see logic_backward_w)."""
     _f32_matrix(x, "x")
     _f32_matrix(grad_y, "grad_y")
     _f32_matrix(coef, "coef")
     n_in, batch = x.shape
-    n_out = grad_y.shape[0]
+    rows_per_class = int(rows_per_class)
+    _need(rows_per_class >= 1, "rows_per_class must be positive")
+    n_out = grad_y.shape[0] * rows_per_class
     _need(grad_y.shape[1] == batch, "grad_y and x disagree on the batch size")
     _need(tuple(coef.shape) == (n_out, 4), "coef must be [n_out, 4]")
     _index(start, "start", n_in + 1)
@@ -133,9 +144,14 @@ def logic_backward_x(x, coef, grad_y, start, plan, grad_scale=1.0, overlap=False
           "plan must be a contiguous int32 [2*n_out, 2] tensor")
     gx = torch.empty_like(x)
     with torch.cuda.device(x.device):
-        N.check(N.lib().dl_backward_x_f32(x.data_ptr(), coef.data_ptr(), grad_y.data_ptr(), start.data_ptr(),
-                                          plan.data_ptr(), float(grad_scale), gx.data_ptr(), n_in, n_out, batch,
-                                          int(overlap), N.stream_of(x)))
+        if rows_per_class == 1:
+            N.check(N.lib().dl_backward_x_f32(x.data_ptr(), coef.data_ptr(), grad_y.data_ptr(), start.data_ptr(),
+                                              plan.data_ptr(), float(grad_scale), gx.data_ptr(), n_in, n_out, batch,
+                                              int(overlap), N.stream_of(x)))
+        else:
+            N.check(N.lib().dl_backward_x_classes_f32(x.data_ptr(), coef.data_ptr(), grad_y.data_ptr(), start.data_ptr(),
+                                                      plan.data_ptr(), float(grad_scale), gx.data_ptr(), n_in, n_out, batch,
+                                                      rows_per_class, int(overlap), N.stream_of(x)))
     return gx
 
 
@@ -369,6 +385,37 @@ def groupsum(x, k, tau):
         ws = _groupsum_workspace(x.device, stream, N.lib().dl_groupsum_workspace_bytes(n, batch, k))
         N.check(N.lib().dl_groupsum_f32(x.data_ptr(), out.data_ptr(), ws.data_ptr(), n, batch, k, float(tau), stream))
     return out
+
+
+_HEAD_COUNTERS = {}
+
+
+def groupsum_cross_entropy_applicable(n, batch, k):
+    return N.lib().dl_groupsum_cross_entropy_applicable(int(n), int(batch), int(k)) == 1
+
+
+def groupsum_cross_entropy(x, target, k, tau):
+    """Head of a training step in one kernel.  feature-major x [n, batch], int64 target [batch] ->
+    (loss scalar, scores [batch, k], grad_classes [k, batch]); grad_classes is the gradient of the mean cross-entropy
+    loss w.r.t. every output row of a class, for logic_backward_w / logic_backward_x with rows_per_class = n / k."""
+    _f32_matrix(x, "x")
+    n, batch = x.shape
+    k = int(k)
+    _need(k > 0 and n % k == 0, "n (%d) must be divisible by k (%d)" % (n, k))
+    _need(target.is_cuda and target.dtype == torch.int64 and target.dim() == 1 and target.is_contiguous()
+          and target.shape[0] == batch and target.device == x.device, "target must be a contiguous int64 [batch] CUDA tensor")
+    _need(groupsum_cross_entropy_applicable(n, batch, k), "classes of %d rows are outside the fused kernel's range" % (n // k))
+    scores = torch.empty((batch, k), dtype=torch.float32, device=x.device)
+    loss = torch.empty((), dtype=torch.float32, device=x.device)
+    grad_classes = torch.empty((k, batch), dtype=torch.float32, device=x.device)
+    counter = _HEAD_COUNTERS.get(x.device)
+    if counter is None:
+        counter = _HEAD_COUNTERS[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_groupsum_cross_entropy_f32(x.data_ptr(), target.data_ptr(), scores.data_ptr(), loss.data_ptr(),
+                                                      grad_classes.data_ptr(), counter.data_ptr(), n, batch, k, float(tau),
+                                                      N.stream_of(x)))
+    return loss, scores, grad_classes
 
 
 def groupsum_backward(grad_out, n, tau):

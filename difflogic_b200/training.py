@@ -50,10 +50,14 @@ class TrainStep:
         self._pending = []
         # FlatAdam.enable_exchange(): gradients are averaged inside the optimizer's own kernel, nothing to do here
         self._exchange_in_optimizer = bool(getattr(optimizer, "exchange_enabled", False))
-        self._body = self._head = None
+        self._body = self._head = self._pre = self._last = None
         self._unit_grad = None     # gradient of the loss w.r.t. itself, made once (autograd would fill a new one per step)
         if fuse_head and self._on_gpu and self._head_is_fusable(model, self.loss_fn):
             self._body, self._head = model[:-1], model[-1]
+            from .difflogic import LogicLayer
+            last = self._body[-1] if len(self._body) > 0 else None
+            if isinstance(last, LogicLayer) and getattr(last, "implementation", None) == "cuda":
+                self._pre, self._last = self._body[:-1], last   # everything before the last logic layer, and that layer
         if self.group is not None and self.world_size > 1 and not self._exchange_in_optimizer:
             if self._on_gpu:
                 self._comm_stream = torch.cuda.Stream()
@@ -74,7 +78,16 @@ class TrainStep:
 
     def _loss(self, x, y):
         if self._head is not None:
-            h = self._body(x)
+            if self._last is not None:
+                # last layer + GroupSum + loss as one autograd node
+                from .difflogic import logic_layer_head
+                h = self._pre(x)
+                out = logic_layer_head(self._last, h, y, self._head.k, float(self._head.tau)) if h.dim() == 2 else None
+                if out is not None:
+                    return out[0]
+                h = self._last(h)
+            else:
+                h = self._body(x)
             if h.is_cuda and h.dtype == torch.float32 and h.dim() == 2 and y.dtype == torch.int64 and y.dim() == 1:
                 from .losses import group_sum_cross_entropy
                 return group_sum_cross_entropy(h, y, self._head.k, float(self._head.tau))[0]
@@ -140,6 +153,7 @@ class TrainStep:
         self.optimizer.zero_grad(set_to_none=True)
         if self._on_gpu and (self._unit_grad is None or self._unit_grad.device != loss.device):
             self._unit_grad = torch.ones((), dtype=loss.dtype, device=loss.device)
+            self._unit_grad._dl_is_one = True   # lets the fused head skip the multiplication by the incoming gradient
         # backward_w of every layer runs on a side stream, off the chain of backward_x kernels -- unless gradient
         # hooks (the NCCL path) need the gradients in stream order
         side = self._bw_stream if (self._on_gpu and not self._hooks) else None

@@ -253,6 +253,24 @@ DL_API int dl_cross_entropy_f32(const float *logits, const int64_t *target, floa
                                 int64_t k, void *stream);
 DL_API int dl_cross_entropy_backward_f32(const float *probs, const int64_t *target, const float *grad_loss,
                                          float *grad_logits, int64_t batch, int64_t k, void *stream);
+/* The head of a training step in one launch: GroupSum (difflogic/difflogic.py:195-196), the cross-entropy loss on
+ * its scores (experiments/main.py:167,175) and the gradient of the loss w.r.t. the scores, laid out as one row per
+ * CLASS: grad_classes [k][batch] = ((softmax(scores) - onehot(target)) / batch) / tau, i.e. the gradient of every
+ * output row of that class (for loss.backward() with unit gradient).  The last layer's backward then runs as
+ * dl_backward_w_classes_f32 / dl_backward_x_classes_f32, which take grad_classes in place of grad_y [n_out][batch].
+ * scores [batch][k], loss a device scalar, counter one zeroed uint32 on the device (left zero).  Sizes:
+ * dl_groupsum_cross_entropy_applicable (classes of 64 .. 4096 rows), else use the separate entry points. */
+DL_API int dl_groupsum_cross_entropy_applicable(int64_t n, int64_t batch, int64_t k);
+DL_API int dl_groupsum_cross_entropy_f32(const float *x, const int64_t *target, float *scores, float *loss, float *grad_classes,
+                                         void *counter, int64_t n, int64_t batch, int64_t k, float tau, void *stream);
+/* backward_w / backward_x of a layer whose output feeds a GroupSum: grad_y_classes has one row per class of
+ * rows_per_class consecutive outputs, [n_out / rows_per_class][batch]; otherwise as dl_backward_w_f32 / dl_backward_x_f32. */
+DL_API int dl_backward_w_classes_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y_classes,
+                                     const float *w, int w_mode, float *grad_w, int64_t n_in, int64_t n_out, int64_t batch,
+                                     int64_t rows_per_class, int flags, void *stream);
+DL_API int dl_backward_x_classes_f32(const float *x, const float *coef, const float *grad_y_classes, const int64_t *start,
+                                     const int32_t *plan, float grad_scale, float *grad_x, int64_t n_in, int64_t n_out,
+                                     int64_t batch, int64_t rows_per_class, int flags, void *stream);
 /* Backward of loss_fn(GroupSum(x), y) in one launch: dl_cross_entropy_backward_f32 followed by
  * dl_groupsum_backward_f32 (GroupSum of difflogic/difflogic.py:195-196 under the loss of experiments/main.py:167,175)
  * without the [batch][k] gradient in between; bit-identical to the two calls.  grad_x is feature-major [n][batch]. */

@@ -91,3 +91,123 @@ def test_label_smoothing_is_not_fused():
     assert step._head is None
     step = TrainStep(model, torch.optim.Adam(model.parameters()), torch.nn.MSELoss())
     assert step._head is None
+
+
+# ---- last layer + GroupSum + loss as one autograd node (class-row gradients) -------------------------------------
+
+from difflogic_b200 import ops  # noqa: E402
+from difflogic_b200.difflogic import logic_layer_head  # noqa: E402
+from tests.helpers import random_layer  # noqa: E402
+
+
+@pytest.mark.parametrize("shape", [(16000, 128, 10, 30.0), (640, 37, 10, 1.0), (4096, 260, 1, 10.0), (6400, 64, 100, 1.0),
+                                   (1280, 1000, 5, 2.0)])
+def test_head_kernel_matches_the_separate_kernels(shape):
+    n, batch, k, tau = shape
+    g = torch.Generator().manual_seed(n + batch)
+    x = torch.rand(n, batch, generator=g).cuda()                     # feature-major
+    y = torch.randint(0, k, (batch,), generator=g).cuda()
+    assert ops.groupsum_cross_entropy_applicable(n, batch, k)
+    for _ in range(2):                                               # the ticket counter is left at zero
+        loss, scores, grad_classes = ops.groupsum_cross_entropy(x, y, k, tau)
+    ref_scores = ops.groupsum(x, k, tau)
+    assert torch.equal(scores, ref_scores)
+    ref_loss = torch.nn.functional.cross_entropy(ref_scores, y)
+    torch.testing.assert_close(loss, ref_loss, rtol=1e-5, atol=1e-6)
+    # gradient rows: the separate kernels' [n, batch] gradient has equal rows within a class
+    sc = ref_scores.clone().requires_grad_(True)
+    CrossEntropyLoss()(sc, y).backward()
+    expanded = ops.groupsum_backward(sc.grad.contiguous(), n, tau)
+    m = n // k
+    assert torch.equal(expanded, grad_classes.repeat_interleave(m, dim=0))
+
+
+def test_head_kernel_range():
+    assert not ops.groupsum_cross_entropy_applicable(630, 16, 10)     # 63 rows per class
+    assert not ops.groupsum_cross_entropy_applicable(50000, 16, 10)   # 5000 rows per class
+    assert not ops.groupsum_cross_entropy_applicable(641, 16, 10)
+    x = torch.rand(630, 16, device='cuda')
+    y = torch.zeros(16, dtype=torch.int64, device='cuda')
+    with pytest.raises(RuntimeError, match="outside"):
+        ops.groupsum_cross_entropy(x, y, 10, 1.0)
+
+
+@pytest.mark.parametrize("shape", [(300, 1000, 128, 100), (33, 60, 100, 20), (50, 64, 7, 64), (12, 24, 516, 3)])
+def test_backward_kernels_with_one_gradient_row_per_class(shape):
+    n_in, n_out, batch, m = shape
+    a, b, w = random_layer(n_in, n_out, seed=sum(shape), force_same_input=True)
+    g = torch.Generator().manual_seed(7)
+    x = torch.rand(n_in, batch, generator=g).cuda()
+    gc = torch.randn(n_out // m, batch, generator=g).cuda()
+    gy = gc.repeat_interleave(m, dim=0).contiguous()
+    a, b, w = a.cuda(), b.cuda(), w.cuda()
+    start, lst = ops.inverse_index(a, b, n_in)
+    plan = ops.build_backward_plan(a, b, start, lst)
+    _, coef = ops.logic_forward(x, a, b, w, ops.W_LOGITS, True)
+    assert torch.equal(ops.logic_backward_w(x, a, b, gc, w, ops.W_LOGITS, rows_per_class=m),
+                       ops.logic_backward_w(x, a, b, gy, w, ops.W_LOGITS))
+    assert torch.equal(ops.logic_backward_x(x, coef, gc, start, plan, 1.5, rows_per_class=m),
+                       ops.logic_backward_x(x, coef, gy, start, plan, 1.5))
+    with pytest.raises(RuntimeError):
+        ops.logic_backward_w(x[:, :4].contiguous(), a, b, gc, w, ops.W_LOGITS, rows_per_class=m)  # batch mismatch is caught
+
+
+@pytest.mark.parametrize("unit", [True, False])
+def test_last_layer_head_node_equals_the_three_modules(unit):
+    torch.manual_seed(3)
+    layer_a = D.LogicLayer(50, 640, device='cuda', grad_factor=1.3)
+    layer_b = D.LogicLayer(50, 640, device='cuda', grad_factor=1.3)
+    layer_b.set_connections(*layer_a.indices)
+    with torch.no_grad():
+        layer_b.weights.copy_(layer_a.weights)
+    x = torch.rand(48, 50, device='cuda')
+    y = torch.randint(0, 10, (48,), device='cuda')
+    up = torch.ones((), device='cuda') if unit else torch.full((), 0.37, device='cuda')
+    if unit:
+        up._dl_is_one = True
+
+    xa = x.clone().requires_grad_(True)
+    loss_a = CrossEntropyLoss()(D.GroupSum(10, 3.0)(layer_a(xa)), y)
+    loss_a.backward(gradient=up)
+
+    xb = x.clone().requires_grad_(True)
+    before = N.launch_count()
+    loss_b, scores = logic_layer_head(layer_b, xb, y, 10, 3.0)
+    loss_b.backward(gradient=up)
+    assert N.launch_count() - before == 4            # forward, head, backward_w, backward_x
+    torch.testing.assert_close(loss_a, loss_b, rtol=1e-6, atol=1e-7)
+    if unit:
+        assert torch.equal(xa.grad, xb.grad) and torch.equal(layer_a.weights.grad, layer_b.weights.grad)
+    else:
+        torch.testing.assert_close(xa.grad, xb.grad, rtol=1e-5, atol=1e-9)
+        torch.testing.assert_close(layer_a.weights.grad, layer_b.weights.grad, rtol=1e-5, atol=1e-9)
+    assert scores.shape == (48, 10) and not scores.requires_grad
+
+
+@pytest.mark.parametrize("captured", [False, True])
+def test_train_step_with_last_layer_head(captured):
+    torch.manual_seed(5)
+    dims = [40, 96, 128, 640]
+    net = O.OracleNet.build(dims, 10, 4.0)
+    g = torch.Generator().manual_seed(2)
+    xs = [(torch.rand(48, 40, generator=g) < 0.4).float().cuda() for _ in range(5)]
+    ys = [torch.randint(0, 10, (48,), generator=g).cuda() for _ in range(5)]
+    results = []
+    for fuse in (False, True):
+        model = build_model(dims, 10, 4.0, net.weights, net.idx_a, net.idx_b)
+        step = TrainStep(model, FlatAdam(model.parameters(), lr=0.01), CrossEntropyLoss(), fuse_head=fuse)
+        assert (step._last is not None) == fuse
+        if captured:
+            step.capture(xs[0], ys[0], warmup=2)
+        before = N.launch_count()
+        losses = [step(x, y).clone() for x, y in zip(xs, ys)]
+        launches = N.launch_count() - before
+        torch.cuda.synchronize()
+        results.append((losses, [l.weights.detach().clone() for l in logic_layers(model)], launches))
+        step.close()
+    (la, wa, na), (lb, wb, nb) = results
+    for p, q in zip(la, lb):
+        torch.testing.assert_close(p, q, rtol=1e-6, atol=1e-7)
+    assert all(torch.equal(p, q) for p, q in zip(wa, wb))          # the gradients are the same bits
+    if not captured:
+        assert nb == na - 5 * 3      # per step: GroupSum + loss -> 1 kernel, loss backward + GroupSum backward -> 0
