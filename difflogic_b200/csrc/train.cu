@@ -10,6 +10,7 @@
 // gathered input rows of a slab stay in L2 for their second reader.
 //
 // No tensor cores: the work is a gather plus a handful of FMAs per element.
+#include "adam_math.cuh"
 #include "common.cuh"
 #include "gates.cuh"
 
@@ -133,6 +134,16 @@ __device__ __forceinline__ void acc4(float &s0, float &sa, float &sb, float &sab
     sab += va * vb * g;
 }
 
+// Optional Adam step in the epilogue of backward_w: a neuron's 16 gradients never leave the registers.  m, v: the
+// layer's slices of the moments; state: two ints of this LAYER, {steps done, ticket}: every block reads the count when it
+// starts, the last block to finish advances it -- no other kernel touches them, so no kernel has to run in between.
+// m == nullptr: off.
+struct AdamInBackward {
+    float *m, *v;
+    int *state;
+    float lr, beta1, beta2, eps, grad_scale;
+};
+
 // Row of grad_y that holds the gradient of output row j.  gy_group == 1: its own row.  gy_group == g > 1: the layer's
 // outputs are summed in classes of g consecutive rows (GroupSum) and grad_y has one row per CLASS -- the gradient of
 // every row of a class is the same, so it is not expanded to [n_out][batch] in memory.
@@ -143,10 +154,11 @@ __device__ __forceinline__ int64_t gy_row(int64_t j, int gy_group) {
 template <int G, bool VEC4>
 __global__ void __launch_bounds__(kThreads)
 backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
-                  const float *__restrict__ gy, const float *__restrict__ w, int w_mode, float *__restrict__ grad_w,
-                  int64_t n_out, int64_t batch, int64_t ncols, int gy_group) {
+                  const float *__restrict__ gy, const float *w, int w_mode, float *__restrict__ grad_w,
+                  int64_t n_out, int64_t batch, int64_t ncols, int gy_group, AdamInBackward adam) {
     using V = typename Vec<VEC4>::type;
     constexpr int R = kThreads / G;
+    __shared__ float s_step_size, s_bc2_sqrt;
     // The 16 gates of the neuron are shared by P lanes of its group, K gates each.
     constexpr int P = G < 16 ? G : 16;
     constexpr int K = 16 / P;
@@ -163,13 +175,29 @@ backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, co
         ib = __ldg(b + j) * batch;
         if (w_mode == DL_W_LOGITS && lane == 0) prefetch_l2(w + j * 16);
     }
+    // Adam in the epilogue (adam.m != nullptr): the moments of this neuron's 16 weights are only ever touched by
+    // this kernel, one step apart, so they are fetched here, before the wait; the bias corrections likewise.
+    float mom1[K], mom2[K];
+    if (adam.m != nullptr) {
+        if (tid == 0) {
+            const float t = (float)(adam.state[0] + 1);
+            s_step_size = adam.lr / (1.f - powf(adam.beta1, t));
+            s_bc2_sqrt = sqrtf(1.f - powf(adam.beta2, t));
+        }
+#pragma unroll
+        for (int q = 0; q < K; ++q) {
+            mom1[q] = (active && lane < P) ? adam.m[j * 16 + gl + q * P] : 0.f;
+            mom2[q] = (active && lane < P) ? adam.v[j * 16 + gl + q * P] : 0.f;
+        }
+        __syncthreads();
+    }
     grid_dependency_wait();      // weights, x and grad_y may have been written by the kernels just before
     grid_dependents_launch();
 
-    float prob[K];
+    float prob[K], raw[K];
     if (w_mode == DL_W_LOGITS) {
 #pragma unroll
-        for (int q = 0; q < K; ++q) prob[q] = active ? __ldg(w + j * 16 + gl + q * P) : 0.f;
+        for (int q = 0; q < K; ++q) raw[q] = prob[q] = active ? w[j * 16 + gl + q * P] : 0.f;
     }
 
     float s0 = 0.f, sa = 0.f, sb = 0.f, sab = 0.f;
@@ -216,8 +244,30 @@ backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, co
         for (int q = 0; q < K; ++q) out[q] = prob[q] * (out[q] - dot);
     }
     if (active && lane < P) {
+        if (grad_w != nullptr) {
 #pragma unroll
-        for (int q = 0; q < K; ++q) grad_w[j * 16 + gl + q * P] = out[q];
+            for (int q = 0; q < K; ++q) grad_w[j * 16 + gl + q * P] = out[q];
+        }
+        if (adam.m != nullptr) {
+            const AdamConsts consts = {1.f - adam.beta1, adam.beta2, 1.f - adam.beta2, s_step_size, s_bc2_sqrt, adam.eps};
+            float *wp = const_cast<float *>(w);
+#pragma unroll
+            for (int q = 0; q < K; ++q) {
+                float pw = raw[q];
+                adam_update(pw, __fmul_rn(out[q], adam.grad_scale), mom1[q], mom2[q], consts);
+                const int64_t at = j * 16 + gl + q * P;
+                wp[at] = pw;
+                adam.m[at] = mom1[q];
+                adam.v[at] = mom2[q];
+            }
+        }
+    }
+    if (adam.m != nullptr && tid == 0) {
+        // thread 0 of every block has read the step count at its start; the last one to get here advances it
+        if (atomicAdd(adam.state + 1, 1) == (int)gridDim.x - 1) {
+            adam.state[1] = 0;
+            adam.state[0] = adam.state[0] + 1;
+        }
     }
 }
 
@@ -347,11 +397,12 @@ static int launch_forward(bool overlap, int G, const float *x, const int64_t *a,
 
 template <bool VEC4>
 static int launch_backward_w(bool overlap, int G, const float *x, const int64_t *a, const int64_t *b, const float *gy, const float *w,
-                             int w_mode, float *grad_w, int64_t n_out, int64_t batch, int64_t ncols, int gy_group, cudaStream_t st) {
+                             int w_mode, float *grad_w, int64_t n_out, int64_t batch, int64_t ncols, int gy_group,
+                             const AdamInBackward &adam, cudaStream_t st) {
     const unsigned grid = (unsigned)ceil_div(n_out, kThreads / G);
 #define DL_BW(GG)                                                                                          \
     case GG:                                                                                               \
-        launch_dependent(overlap, backward_w_kernel<GG, VEC4>, dim3(grid), dim3(kThreads), 0, st, x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols, gy_group); \
+        launch_dependent(overlap, backward_w_kernel<GG, VEC4>, dim3(grid), dim3(kThreads), 0, st, x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols, gy_group, adam); \
         break;
     switch (G) {
         DL_BW(1) DL_BW(2) DL_BW(4) DL_BW(8) DL_BW(16) DL_BW(32)
@@ -402,22 +453,23 @@ extern "C" DL_API int dl_forward_f32(const float *x, const int64_t *a, const int
 }
 
 static int backward_w_entry(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w, int w_mode,
-                            float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int64_t gy_group, int flags, void *stream) {
+                            float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int64_t gy_group, int flags, void *stream,
+                            const AdamInBackward &adam = AdamInBackward{nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, 0.f, 0.f}) {
     DL_REQUIRE(gy_group >= 1 && gy_group <= INT32_MAX && n_out % gy_group == 0, DL_ERR_INVALID_ARG,
                "dl_backward_w_f32: n_out (%lld) is not a multiple of the rows per class (%lld)", (long long)n_out, (long long)gy_group);
     DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_backward_w_f32: negative size");
     DL_REQUIRE(w_mode == DL_W_LOGITS || w_mode == DL_W_PROBS, DL_ERR_INVALID_ARG,
                "dl_backward_w_f32: w_mode must be DL_W_LOGITS or DL_W_PROBS, got %d", w_mode);
     if (n_out == 0) return DL_OK;
-    DL_REQUIRE(a && b && grad_w, DL_ERR_INVALID_ARG, "dl_backward_w_f32: null pointer");
+    DL_REQUIRE(a && b && (grad_w || adam.m), DL_ERR_INVALID_ARG, "dl_backward_w_f32: null pointer");
     DL_REQUIRE(batch == 0 || (x && grad_y), DL_ERR_INVALID_ARG, "dl_backward_w_f32: null pointer");
     DL_REQUIRE(w_mode != DL_W_LOGITS || w, DL_ERR_INVALID_ARG, "dl_backward_w_f32: DL_W_LOGITS needs the raw weights");
     const bool vec = batch % 4 == 0 && aligned_to(x, 16) && aligned_to(grad_y, 16);
     const int64_t ncols = vec ? batch / 4 : batch;
     const int G = pow2_at_least(ceil_div(ncols, 4), 32);
     const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
-    return vec ? launch_backward_w<true>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, as_stream(stream))
-               : launch_backward_w<false>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, as_stream(stream));
+    return vec ? launch_backward_w<true>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, adam, as_stream(stream))
+               : launch_backward_w<false>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, adam, as_stream(stream));
 }
 
 extern "C" DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
@@ -450,6 +502,18 @@ static int backward_x_entry(const float *x, const float *coef, const float *grad
     const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
     return vec ? launch_backward_x<true>(overlap, G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, (int)gy_group, as_stream(stream))
                : launch_backward_x<false>(overlap, G, x, coef, grad_y, start, plan, grad_scale, grad_x, n_in, batch, ncols, (int)gy_group, as_stream(stream));
+}
+
+// backward_w with the Adam step of the layer's weights in its epilogue: w [n_out][16] is UPDATED in place with the
+// layer's slices of the moments; grad_w may be null (the gradient is then not stored at all).  state: this layer's own
+// {steps done, ticket} pair on the device; the kernel uses steps done + 1 and advances it when it is through.
+extern "C" DL_API int dl_backward_w_adam_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, float *w,
+                                             float *exp_avg, float *exp_avg_sq, float *grad_w, int64_t n_in, int64_t n_out, int64_t batch,
+                                             int64_t rows_per_class, float lr, float beta1, float beta2, float eps, float grad_scale,
+                                             int32_t *state, int flags, void *stream) {
+    DL_REQUIRE(n_out == 0 || (w && exp_avg && exp_avg_sq && state), DL_ERR_INVALID_ARG, "dl_backward_w_adam_f32: null pointer");
+    const AdamInBackward adam = {exp_avg, exp_avg_sq, reinterpret_cast<int *>(state), lr, beta1, beta2, eps, grad_scale};
+    return backward_w_entry(x, a, b, grad_y, w, DL_W_LOGITS, grad_w, n_in, n_out, batch, rows_per_class, flags, stream, adam);
 }
 
 extern "C" DL_API int dl_backward_x_f32(const float *x, const float *coef, const float *grad_y, const int64_t *start,

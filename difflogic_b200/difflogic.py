@@ -249,6 +249,17 @@ class GroupSum(torch.nn.Module):
 ########################################################################################################################
 
 
+def _run_backward_w(x, a, b, grad, weights, grad_out, rows_per_class=1):
+    """backward_w of a layer; with an optimizer that steps inside backward (FlatAdam.enable_step_in_backward) the
+    weights are updated by the same kernel and there is no gradient to return."""
+    opt = getattr(weights, '_dl_adam', None)
+    if opt is not None:
+        ops.logic_backward_w_adam(x, a, b, grad, weights.data, overlap=True, rows_per_class=rows_per_class,
+                                  **opt.backward_args(weights))
+        return None
+    return ops.logic_backward_w(x, a, b, grad, weights, ops.W_LOGITS, out=grad_out, overlap=True, rows_per_class=rows_per_class)
+
+
 class LogicLayerFunction(torch.autograd.Function):
     """Autograd node of one logic layer on feature-major tensors, from the raw weights.
 
@@ -274,7 +285,7 @@ class LogicLayerFunction(torch.autograd.Function):
             main = torch.cuda.current_stream(x.device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                grad_w = ops.logic_backward_w(x, a, b, grad_y, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True)
+                grad_w = _run_backward_w(x, a, b, grad_y, weights, ctx.grad_out)
             for t in (x, grad_y, weights):
                 t.record_stream(side)
             grad_x = ops.logic_backward_x(x, coef, grad_y, start, plan, ctx.grad_factor, overlap=True)
@@ -282,7 +293,7 @@ class LogicLayerFunction(torch.autograd.Function):
             if ctx.needs_input_grad[0]:
                 grad_x = ops.logic_backward_x(x, coef, grad_y, start, plan, ctx.grad_factor, overlap=True)
             if ctx.needs_input_grad[1]:
-                grad_w = ops.logic_backward_w(x, a, b, grad_y, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True)
+                grad_w = _run_backward_w(x, a, b, grad_y, weights, ctx.grad_out)
         if grad_w is not None and ctx.grad_out is not None:
             # a fresh alias that nothing else references: autograd then adopts it as `weights.grad`
             # instead of copying it, so the gradient stays inside the flat bucket
@@ -324,8 +335,7 @@ class LogicLayerHeadFunction(torch.autograd.Function):
             main = torch.cuda.current_stream(x.device)
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                grad_w = ops.logic_backward_w(x, a, b, grad_classes, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True,
-                                              rows_per_class=m)
+                grad_w = _run_backward_w(x, a, b, grad_classes, weights, ctx.grad_out, rows_per_class=m)
             for t in (x, grad_classes, weights):
                 t.record_stream(side)
             grad_x = ops.logic_backward_x(x, coef, grad_classes, start, plan, ctx.grad_factor, overlap=True, rows_per_class=m)
@@ -333,8 +343,7 @@ class LogicLayerHeadFunction(torch.autograd.Function):
             if ctx.needs_input_grad[0]:
                 grad_x = ops.logic_backward_x(x, coef, grad_classes, start, plan, ctx.grad_factor, overlap=True, rows_per_class=m)
             if ctx.needs_input_grad[1]:
-                grad_w = ops.logic_backward_w(x, a, b, grad_classes, weights, ops.W_LOGITS, out=ctx.grad_out, overlap=True,
-                                              rows_per_class=m)
+                grad_w = _run_backward_w(x, a, b, grad_classes, weights, ctx.grad_out, rows_per_class=m)
         if grad_w is not None and ctx.grad_out is not None:
             grad_w = grad_w.view(grad_w.shape)  # a fresh alias: autograd adopts it as `weights.grad` without copying
         return (grad_x, grad_w) + (None,) * 9

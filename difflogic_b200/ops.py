@@ -101,6 +101,37 @@ def logic_backward_w(x, a, b, grad_y, w=None, w_mode=W_PROBS, out=None, overlap=
     return out
 
 
+def logic_backward_w_adam(x, a, b, grad_y, w, exp_avg, exp_avg_sq, state, lr, beta1, beta2, eps, grad_scale=1.0, grad_out=None,
+                          overlap=False, rows_per_class=1):
+    """backward_w of a layer with the Adam step of its weights in the kernel's epilogue: `w` [n_out, 16] and its moment
+    slices are updated in place; the gradient is stored only when `grad_out` is given.  `state`: two int32 on the device
+    that belong to this layer, {steps done, 0}; the kernel advances the count."""
+    _f32_matrix(x, "x")
+    _f32_matrix(grad_y, "grad_y")
+    _f32_matrix(w, "w")
+    n_in, batch = x.shape
+    rows_per_class = int(rows_per_class)
+    n_out = grad_y.shape[0] * rows_per_class
+    _need(grad_y.shape[1] == batch, "grad_y and x disagree on the batch size")
+    _need(tuple(w.shape) == (n_out, 16), "w must be [n_out, 16]")
+    _index(a, "a", n_out)
+    _index(b, "b", n_out)
+    for t, name in ((exp_avg, "exp_avg"), (exp_avg_sq, "exp_avg_sq")):
+        _need(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.numel() >= n_out * 16 and t.device == x.device,
+              "%s must be a contiguous float32 CUDA tensor of at least n_out * 16 elements" % name)
+    _need(state.is_cuda and state.dtype == torch.int32 and state.numel() >= 2 and state.is_contiguous(),
+          "state must be a contiguous int32 CUDA tensor of two elements")
+    if grad_out is not None:
+        _f32_matrix(grad_out, "grad_out")
+        _need(tuple(grad_out.shape) == (n_out, 16), "grad_out must be [n_out, 16]")
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_backward_w_adam_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), grad_y.data_ptr(), w.data_ptr(),
+                                               exp_avg.data_ptr(), exp_avg_sq.data_ptr(), N.ptr(grad_out), n_in, n_out, batch,
+                                               rows_per_class, float(lr), float(beta1), float(beta2), float(eps), float(grad_scale),
+                                               state.data_ptr(), int(overlap), N.stream_of(x)))
+    return grad_out
+
+
 def inverse_index(a, b, n_in):
     """The reference's inverse connection index (difflogic/difflogic.py:56-69) built with device
     ops: for every input row the consumer neurons in increasing order, a neuron whose two inputs

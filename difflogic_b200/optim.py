@@ -132,6 +132,44 @@ class FlatAdam(torch.optim.Optimizer):
         return {"wait_gradients_ns": t[1] - t[0], "slice_ns": t[2] - t[1], "wait_slices_ns": t[3] - t[2], "gather_ns": t[5] - t[3],
                 "total_ns": t[5] - t[0], "first_block_slice_ns": t[4] - t[1]}
 
+    # -- Adam inside backward_w ---------------------------------------------------------------------------------------
+
+    def enable_step_in_backward(self, on=True):
+        """With `on`, every LogicLayer whose weights this optimizer holds applies the Adam update in the epilogue of its
+        backward_w kernel (a neuron's 16 gradients go from registers straight into the update); `loss.backward()`
+        then UPDATES the weights and stores no gradient, and the caller must not call `step()` for that pass
+        (`TrainStep` handles this).  Every parameter counts its own steps on the device (`layer_state`);
+        `sync_step_counts()` carries the count over when the way of stepping changes.  Single GPU only."""
+        if on and getattr(self, "exchange_enabled", False):
+            raise RuntimeError("FlatAdam: the step inside backward_w and the peer-memory exchange exclude each other")
+        if on and getattr(self, "layer_state", None) is None:
+            self.layer_state = torch.zeros((len(self._params), 2), dtype=torch.int32, device=self.flat_param.device)
+            self._layer_index = {p: i for i, p in enumerate(self._params)}
+            self.sync_step_counts(to_layers=True)
+        for p in self._params:
+            p._dl_adam = self if on else None
+        return self
+
+    @torch.no_grad()
+    def sync_step_counts(self, to_layers):
+        """to_layers: every parameter's own count := the optimizer's count (before stepping inside backward_w);
+        else the optimizer's count := the first parameter's (before stepping with `step()` again)."""
+        if getattr(self, "layer_state", None) is None:
+            return
+        if to_layers:
+            self.layer_state[:, 0] = self.state_t[0]
+        else:
+            self.state_t[0] = self.layer_state[0, 0]
+
+    def backward_args(self, p):
+        """What ops.logic_backward_w_adam needs for parameter p: its moment slices, its step count and the hyper-parameters."""
+        off, cnt = self._slices[p]
+        g = self.param_groups[0]
+        beta1, beta2 = g['betas']
+        return dict(exp_avg=self.exp_avg[off:off + cnt], exp_avg_sq=self.exp_avg_sq[off:off + cnt],
+                    state=self.layer_state[self._layer_index[p]], lr=g['lr'], beta1=beta1, beta2=beta2, eps=g['eps'],
+                    grad_scale=self.grad_scale)
+
     def prefetch_state(self):
         """Launches (on the current stream) a kernel that pulls the moments towards L2.  They are touched once per step,
         so a step that begins with a cold L2 otherwise reads them from HBM at the very end, after the last gradient."""

@@ -18,7 +18,8 @@ import torch.distributed as dist
 
 
 class TrainStep:
-    def __init__(self, model, optimizer, loss_fn=None, process_group=None, world_size=None, buckets=2, fuse_head=True):
+    def __init__(self, model, optimizer, loss_fn=None, process_group=None, world_size=None, buckets=2, fuse_head=True,
+                 step_in_backward=True):
         """
         :param model:         module on the current CUDA device (replicated on every rank)
         :param optimizer:     its optimizer; for `capture()` it must be graph-capturable
@@ -27,6 +28,9 @@ class TrainStep:
         :param process_group: torch.distributed group to average gradients over, or None
         :param fuse_head:     when the model ends in GroupSum and the loss is a default CrossEntropyLoss, run the two
                               as one autograd node (same numbers, three kernels instead of five)
+        :param step_in_backward: single GPU, FlatAdam, every parameter a CUDA LogicLayer's weights: the Adam update runs
+                              in the epilogue of each layer's backward_w kernel instead of a kernel of its own after
+                              the backward pass (same numbers; `.grad` is then not populated)
         :param buckets:       with FlatAdam: number of contiguous pieces of the flat gradient buffer that are
                               all-reduced separately (the piece holding the last layers first); 1 = one
                               all-reduce after the whole backward pass.  Other optimizers: one per parameter.
@@ -58,12 +62,27 @@ class TrainStep:
             last = self._body[-1] if len(self._body) > 0 else None
             if isinstance(last, LogicLayer) and getattr(last, "implementation", None) == "cuda":
                 self._pre, self._last = self._body[:-1], last   # everything before the last logic layer, and that layer
+        self._in_backward = False
+        if (step_in_backward and self._on_gpu and self.world_size == 1 and not self._exchange_in_optimizer
+                and hasattr(optimizer, "enable_step_in_backward") and self._all_logic_weights(model, optimizer)):
+            self._in_backward = True   # switched on around each backward pass only: outside a step the model is as usual
+            optimizer.enable_step_in_backward(True)    # allocates the per-layer step counts
+            optimizer.enable_step_in_backward(False)
+            optimizer.sync_step_counts(to_layers=True)
         if self.group is not None and self.world_size > 1 and not self._exchange_in_optimizer:
             if self._on_gpu:
                 self._comm_stream = torch.cuda.Stream()
                 self._plan_buckets(max(1, int(buckets)))
             for p in self.params:
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._reduce_when_ready))
+
+    @staticmethod
+    def _all_logic_weights(model, optimizer):
+        """True when the optimizer's parameters are exactly the weights of the model's CUDA LogicLayers."""
+        from .difflogic import LogicLayer
+        mine = {id(m.weights) for m in model.modules() if isinstance(m, LogicLayer) and m.implementation == "cuda"}
+        theirs = [p for g in optimizer.param_groups for p in g["params"]]
+        return len(theirs) > 0 and all(id(p) in mine for p in theirs)
 
     @staticmethod
     def _head_is_fusable(model, loss_fn):
@@ -159,19 +178,24 @@ class TrainStep:
         side = self._bw_stream if (self._on_gpu and not self._hooks) else None
         if side is not None:
             _dl.set_backward_w_stream(side)
-            if hasattr(self.optimizer, "prefetch_state"):
+            if hasattr(self.optimizer, "prefetch_state") and not self._in_backward:
                 # warm the optimizer's moments in L2 beside the backward pass
                 side.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(side):
                     self.optimizer.prefetch_state()
+        if self._in_backward:
+            self.optimizer.enable_step_in_backward(True)
         try:
             loss.backward(gradient=self._unit_grad if self._on_gpu else None)
         finally:
+            if self._in_backward:
+                self.optimizer.enable_step_in_backward(False)
             if side is not None:
                 _dl.set_backward_w_stream(None)
                 torch.cuda.current_stream().wait_stream(side)
         self._join_comm()
-        self.optimizer.step()
+        if not self._in_backward:    # else the backward_w kernels have applied the update
+            self.optimizer.step()
         return loss.detach()
 
     def __call__(self, x, y):
@@ -216,6 +240,9 @@ class TrainStep:
         for h in self._hooks:
             h.remove()
         self._hooks = []
+        if self._in_backward:
+            self.optimizer.sync_step_counts(to_layers=False)   # optimizer.step() can take over from here
+        self._in_backward = False
         if self._on_gpu and torch.cuda.is_available():
             torch.cuda.synchronize()
         self._graph = None

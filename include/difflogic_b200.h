@@ -263,6 +263,18 @@ DL_API int dl_cross_entropy_backward_f32(const float *probs, const int64_t *targ
 DL_API int dl_groupsum_cross_entropy_applicable(int64_t n, int64_t batch, int64_t k);
 DL_API int dl_groupsum_cross_entropy_f32(const float *x, const int64_t *target, float *scores, float *loss, float *grad_classes,
                                          void *counter, int64_t n, int64_t batch, int64_t k, float tau, void *stream);
+/* backward_w with the Adam step (update rule of dl_adam_step_f32) of the layer's weights in its epilogue: the 16
+ * gradients of a neuron go from the registers straight into the update of w [n_out][16], exp_avg and exp_avg_sq (the
+ * layer's slices, same layout as w); grad_w may be null, the gradient is then not stored.  state: two int32 on the
+ * device that belong to THIS layer, {steps done, 0}, zero at first; the kernel takes the step number steps done + 1 and
+ * advances the count when it is through (so each layer needs its own pair, and nothing has to run between the steps).
+ * rows_per_class as in dl_backward_w_classes_f32 (1: grad_y has a row
+ * per output).  Replaces logic_layer_cuda_backward_w (difflogic_kernel.cu:300-364) + softmax backward +
+ * torch.optim.Adam.step for that layer (experiments/main.py:179). */
+DL_API int dl_backward_w_adam_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, float *w, float *exp_avg,
+                                  float *exp_avg_sq, float *grad_w, int64_t n_in, int64_t n_out, int64_t batch,
+                                  int64_t rows_per_class, float lr, float beta1, float beta2, float eps, float grad_scale,
+                                  int32_t *state, int flags, void *stream);
 /* backward_w / backward_x of a layer whose output feeds a GroupSum: grad_y_classes has one row per class of
  * rows_per_class consecutive outputs, [n_out / rows_per_class][batch]; otherwise as dl_backward_w_f32 / dl_backward_x_f32. */
 DL_API int dl_backward_w_classes_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y_classes,

@@ -211,3 +211,70 @@ def test_train_step_with_last_layer_head(captured):
     assert all(torch.equal(p, q) for p, q in zip(wa, wb))          # the gradients are the same bits
     if not captured:
         assert nb == na - 5 * 3      # per step: GroupSum + loss -> 1 kernel, loss backward + GroupSum backward -> 0
+
+
+# ---- the Adam step inside backward_w -------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("shape", [(300, 1000, 128, 1), (33, 60, 100, 20), (16, 40, 7, 1), (12, 24, 516, 3)])
+def test_backward_w_with_adam_epilogue_equals_backward_w_then_adam(shape):
+    n_in, n_out, batch, m = shape
+    a, b, w = random_layer(n_in, n_out, seed=sum(shape), force_same_input=True)
+    g = torch.Generator().manual_seed(11)
+    x = torch.rand(n_in, batch, generator=g).cuda()
+    gy = torch.randn(n_out // m, batch, generator=g).cuda()
+    a, b = a.cuda(), b.cuda()
+    hp = dict(lr=0.01, beta1=0.9, beta2=0.999, eps=1e-8)
+    # reference: backward_w, then the flat Adam kernel
+    w1 = torch.nn.Parameter(w.clone().cuda())
+    opt = FlatAdam([w1], lr=hp["lr"])
+    # fused: same start
+    w2 = w.clone().cuda()
+    m2 = torch.zeros(n_out * 16, device='cuda')
+    v2 = torch.zeros(n_out * 16, device='cuda')
+    state = torch.zeros(2, dtype=torch.int32, device='cuda')
+    for _ in range(3):
+        w1.grad = ops.logic_backward_w(x, a, b, gy, w1.data, ops.W_LOGITS, rows_per_class=m)
+        opt.step()
+        got = ops.logic_backward_w_adam(x, a, b, gy, w2, m2, v2, state, grad_scale=1.0, grad_out=torch.empty_like(w2),
+                                        rows_per_class=m, **hp)
+    assert state.tolist() == [3, 0] and int(opt.state_t[0].item()) == 3
+    assert torch.equal(w1.data, w2)
+    assert torch.equal(opt.exp_avg[:n_out * 16], m2) and torch.equal(opt.exp_avg_sq[:n_out * 16], v2)
+    assert got.shape == (n_out, 16)
+    # without grad_out nothing but the update happens
+    assert ops.logic_backward_w_adam(x, a, b, gy, w2, m2, v2, state, rows_per_class=m, **hp) is None
+
+
+@pytest.mark.parametrize("captured", [False, True])
+def test_train_step_with_adam_inside_backward(captured):
+    torch.manual_seed(5)
+    dims = [40, 96, 128, 640]
+    net = O.OracleNet.build(dims, 10, 4.0)
+    g = torch.Generator().manual_seed(2)
+    xs = [(torch.rand(48, 40, generator=g) < 0.4).float().cuda() for _ in range(5)]
+    ys = [torch.randint(0, 10, (48,), generator=g).cuda() for _ in range(5)]
+    results = []
+    for inside in (False, True):
+        model = build_model(dims, 10, 4.0, net.weights, net.idx_a, net.idx_b)
+        opt = FlatAdam(model.parameters(), lr=0.01)
+        step = TrainStep(model, opt, CrossEntropyLoss(), step_in_backward=inside)
+        assert step._in_backward == inside
+        if captured:
+            step.capture(xs[0], ys[0], warmup=2)
+        losses = [step(x, y).clone() for x, y in zip(xs, ys)]
+        torch.cuda.synchronize()
+        weights_after = [l.weights.detach().clone() for l in logic_layers(model)]
+        moments = (opt.exp_avg.clone(), opt.exp_avg_sq.clone())
+        # outside a step the model behaves as usual: backward fills .grad and does not touch the weights
+        before = [l.weights.detach().clone() for l in logic_layers(model)]
+        model.train()
+        torch.nn.functional.cross_entropy(model(xs[0]), ys[0]).backward()
+        assert all(l.weights.grad is not None for l in logic_layers(model))
+        assert all(torch.equal(p, l.weights.detach()) for p, l in zip(before, logic_layers(model)))
+        step.close()                                   # hands the step count back to optimizer.step()
+        results.append((losses, weights_after, int(opt.state_t[0].item()), moments[0], moments[1]))
+    (la, wa, ca, ma, va), (lb, wb, cb, mb, vb) = results
+    assert ca == cb == (7 if captured else 5)
+    assert all(torch.equal(p, q) for p, q in zip(la, lb))
+    assert all(torch.equal(p, q) for p, q in zip(wa, wb))
+    assert torch.equal(ma, mb) and torch.equal(va, vb)
