@@ -168,6 +168,7 @@ eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, co
 
 int groupbitsum_async_error();       // groupbitsum_tma.cu
 int eval_groupbitsum_async_error();  // eval_groupbitsum.cu
+int forward_tma_async_error();       // forward_tma.cu
 
 static int sm_count() {
     static int cached[64] = {0};
@@ -233,5 +234,7 @@ extern "C" DL_API int dl_async_error(void) {
     if (other < 0) return other;
     const int fused = dl::eval_groupbitsum_async_error();
     if (fused < 0) return fused;
-    return flag | other | fused;
+    const int fwd = dl::forward_tma_async_error();
+    if (fwd < 0) return fwd;
+    return flag | other | fused | fwd;
 }

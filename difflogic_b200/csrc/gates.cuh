@@ -76,6 +76,20 @@ __device__ __forceinline__ float4 quad_coef(const float *__restrict__ wq, bool l
     return make_float4(quad_sum(c0), quad_sum(ca), quad_sum(cb), quad_sum(cab));
 }
 
+// The layer's output from the four coefficients c = {c0, ca, cb, cab}: c0 + ca A + cb B + cab A B, in one fixed order of
+// fused multiply-adds (every forward kernel uses this function, so they agree to the bit).
+__device__ __forceinline__ float4 mixv(const float4 c, const float4 a, const float4 b) {
+    float4 r;
+    r.x = fmaf(c.w, a.x * b.x, fmaf(c.y, a.x, fmaf(c.z, b.x, c.x)));
+    r.y = fmaf(c.w, a.y * b.y, fmaf(c.y, a.y, fmaf(c.z, b.y, c.x)));
+    r.z = fmaf(c.w, a.z * b.z, fmaf(c.y, a.z, fmaf(c.z, b.z, c.x)));
+    r.w = fmaf(c.w, a.w * b.w, fmaf(c.y, a.w, fmaf(c.z, b.w, c.x)));
+    return r;
+}
+__device__ __forceinline__ float mixv(const float4 c, const float a, const float b) {
+    return fmaf(c.w, a * b, fmaf(c.y, a, fmaf(c.z, b, c.x)));
+}
+
 // dL/dp_i from the four batch sums S = {sum g, sum A g, sum B g, sum A B g}.
 __device__ __forceinline__ float gate_grad_from_sums(int i, float s0, float sa, float sb, float sab) {
     const int t00 = (i >> 3) & 1, t01 = (i >> 2) & 1, t10 = (i >> 1) & 1, t11 = i & 1;

@@ -32,18 +32,6 @@ struct Vec<false> {
 __device__ __forceinline__ float4 ldv(const float4 *p) { return __ldg(p); }
 __device__ __forceinline__ float ldv(const float *p) { return __ldg(p); }
 
-__device__ __forceinline__ float4 mixv(const float4 c, const float4 a, const float4 b) {
-    float4 r;
-    r.x = fmaf(c.w, a.x * b.x, fmaf(c.y, a.x, fmaf(c.z, b.x, c.x)));
-    r.y = fmaf(c.w, a.y * b.y, fmaf(c.y, a.y, fmaf(c.z, b.y, c.x)));
-    r.z = fmaf(c.w, a.z * b.z, fmaf(c.y, a.z, fmaf(c.z, b.z, c.x)));
-    r.w = fmaf(c.w, a.w * b.w, fmaf(c.y, a.w, fmaf(c.z, b.w, c.x)));
-    return r;
-}
-__device__ __forceinline__ float mixv(const float4 c, const float a, const float b) {
-    return fmaf(c.w, a * b, fmaf(c.y, a, fmaf(c.z, b, c.x)));
-}
-
 // ---------------------------------------------------------------------------------------------
 // forward:  y[j][:] = c0 + ca*x[a_j][:] + cb*x[b_j][:] + cab*x[a_j][:]*x[b_j][:]
 // Set-up (before the grid dependency is waited for): connection indices into registers.  Then the
@@ -430,6 +418,10 @@ static int launch_backward_x(bool overlap, int G, const float *x, const float *c
     return launch_status("dl_backward_x_f32");
 }
 
+bool forward_tma_applicable(const float *x, const float *y, int64_t n_out, int64_t batch);  // forward_tma.cu
+int launch_forward_tma(bool overlap, const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode, float *y,
+                       float *coef, int64_t n_out, int64_t batch, cudaStream_t st);
+
 }  // namespace dl
 
 using namespace dl;
@@ -448,6 +440,8 @@ extern "C" DL_API int dl_forward_f32(const float *x, const int64_t *a, const int
     const int64_t ncols = vec ? batch / 4 : batch;
     const int G = pow2_at_least(ncols, 32);
     const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
+    if (forward_tma_applicable(x, y, n_out, batch))   // long rows: gathered rows staged in shared memory by bulk copies
+        return launch_forward_tma(overlap, x, a, b, w, w_mode, y, coef, n_out, batch, as_stream(stream));
     return vec ? launch_forward<true>(overlap, G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream))
                : launch_forward<false>(overlap, G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream));
 }
