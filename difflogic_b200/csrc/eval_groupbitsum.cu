@@ -267,10 +267,13 @@ eval_groupbitsum_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict
                 const GateMasks gm = gate_masks((int)op);
                 meta[s * kFgRows + r_in] = make_uint4(gm.m0, gm.ma, gm.mb, gm.mab);
             }
+            // an input that the neuron's gate ignores is not fetched: its mask is zero, whatever the stage holds there
+            const bool needed = valid && gate_needs_input(op, which);
+            const uint32_t copies = (uint32_t)__popc(__ballot_sync(0xffffffffu, needed));
+            __syncwarp();  // the masks / gate ids written above are ordered before lane 0's arrival
+            if (lane == 0) mbar_arrive_expect_tx(full + s, copies * cur.g.bytes);
             __syncwarp();
-            if (lane == 0) mbar_arrive_expect_tx(full + s, 2u * (uint32_t)nr * cur.g.bytes);
-            __syncwarp();
-            if (valid)
+            if (needed)
                 bulk_load(smem + s * kFgStageBytes + (size_t)(which * kFgRows + r_in) * kFgChunk, x + idx * row_bytes + cur.g.col0,
                           cur.g.bytes, full + s);
             last = cur.it;

@@ -105,12 +105,14 @@ eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, co
             const int64_t col0 = (int64_t)cb * chunk;
             const uint32_t bytes = (uint32_t)min((int64_t)chunk, row_bytes - col0);
             const bool valid = copier && nb * kTileRows + r < n_out;
-            const uint32_t nvalid = min((uint32_t)kTileRows, n_out - nb * kTileRows);
             if (valid && which == 0) meta[s * kTileRows + r] = (uint8_t)op;
+            // an input that the neuron's gate ignores is not fetched: its mask is zero, whatever the stage holds there
+            const bool needed = valid && gate_needs_input(op, which);
+            const uint32_t copies = (uint32_t)__popc(__ballot_sync(0xffffffffu, needed));
+            __syncwarp();  // the masks / gate ids written above are ordered before lane 0's arrival
+            if (lane == 0) mbar_arrive_expect_tx(full + s, copies * bytes);
             __syncwarp();
-            if (lane == 0) mbar_arrive_expect_tx(full + s, 2u * nvalid * bytes);
-            __syncwarp();
-            if (valid)
+            if (needed)
                 bulk_load(smem + s * stage_bytes + (size_t)(which * kTileRows + r) * chunk, x + idx * row_bytes + col0, bytes,
                           full + s);
             ++issued;

@@ -110,6 +110,13 @@ __device__ __forceinline__ GateMasks gate_masks(int op) {
     g.mab = 0u - (t00 ^ t01 ^ t10 ^ t11);
     return g;
 }
+// Whether gate `op` depends on its first (which = 0) or second (which = 1) input at all.  Six of the sixteen gates do not
+// need both: false and true need none, A, not A, B and not B need one.  The masks above are zero for an input that
+// is not needed, so whatever stands in its place is ignored.
+__device__ __forceinline__ bool gate_needs_input(uint32_t op, int which) {
+    const uint32_t t00 = (op >> 3) & 1, t01 = (op >> 2) & 1, t10 = (op >> 1) & 1, t11 = op & 1;
+    return which == 0 ? ((t00 ^ t10) | (t01 ^ t11)) != 0 : ((t00 ^ t01) | (t10 ^ t11)) != 0;
+}
 __device__ __forceinline__ uint32_t gate32(uint32_t a, uint32_t b, const GateMasks &g) {
     return g.m0 ^ (g.ma & a) ^ (g.mb & b) ^ (g.mab & a & b);
 }
