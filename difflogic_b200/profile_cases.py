@@ -4,6 +4,8 @@
     python -m difflogic_b200.profile_cases gbs    [words  [neurons]]   # group bit-sum, k = 10
     python -m difflogic_b200.profile_cases tail   [words  [neurons]]   # last layer + group bit-sum in one kernel, k = 10
     python -m difflogic_b200.profile_cases fwd|bw|bx [batch [neurons]] # training kernels, default 128 x 16000
+    python -m difflogic_b200.profile_cases bwadam [batch [neurons]]    # backward_w with the Adam update in its epilogue
+    python -m difflogic_b200.profile_cases head   [batch [neurons]]    # GroupSum + cross-entropy + class-row gradients, k = 10
 
 Each case builds a square layer with 'random' connections and launches the kernel three times.  The sizes are
 chosen so that a full-metric capture of one launch finishes in seconds (a few hundred MB on the device).
@@ -39,7 +41,7 @@ def main(argv):
                 ops.eval_groupbitsum(x, a, b, gate, 0, 10)
             else:
                 ops.groupbitsum(x, 0, 10)
-    elif which in ("fwd", "bw", "bx"):
+    elif which in ("fwd", "bw", "bx", "bwadam", "head"):
         batch = int(argv[1]) if len(argv) > 1 else 128
         n = int(argv[2]) if len(argv) > 2 else 16000
         a, b = _connections(n, n, dev)
@@ -49,9 +51,17 @@ def main(argv):
         start, lst = ops.inverse_index(a, b, n)
         plan = ops.build_backward_plan(a, b, start, lst)
         _, coef = ops.logic_forward(x, a, b, w, ops.W_LOGITS, True)
+        m1 = torch.zeros(n * 16, device=dev)
+        m2 = torch.zeros(n * 16, device=dev)
+        state = torch.zeros(2, dtype=torch.int32, device=dev)
+        target = torch.randint(0, 10, (batch,), device=dev)
         torch.cuda.synchronize()
         for _ in range(3):
-            if which == "fwd":
+            if which == "bwadam":
+                ops.logic_backward_w_adam(x, a, b, gy, w, m1, m2, state, lr=0.01, beta1=0.9, beta2=0.999, eps=1e-8)
+            elif which == "head":
+                ops.groupsum_cross_entropy(x, target, 10, 30.0)
+            elif which == "fwd":
                 ops.logic_forward(x, a, b, w, ops.W_LOGITS, True)
             elif which == "bw":
                 ops.logic_backward_w(x, a, b, gy, w, ops.W_LOGITS)
