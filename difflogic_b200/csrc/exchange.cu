@@ -307,7 +307,11 @@ extern "C" DL_API int dl_adam_exchange_step_f32(void *const *param_ptrs, void *c
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || sms <= 0 || per_sm <= 0)
             return launch_status("dl_adam_exchange_step_f32 (occupancy query)");
+        // enough blocks for one pass over the slice, and for the gather of the other ranks' slices (world - 1 times as
+        // many elements, 8 per thread and pass: loads over NVLink need many requests in flight), never more than fit
         int64_t blocks = ceil_div(per > 0 ? per : 1, (int64_t)kThreads * per_thread);
+        const int64_t for_gather = ceil_div((int64_t)(world - 1) * per, (int64_t)kThreads * 4);
+        if (blocks < for_gather) blocks = for_gather;
         const int64_t resident = (int64_t)sms * per_sm;
         if (blocks > resident) blocks = resident;
         launch_dependent(true, kernel, dim3((unsigned)blocks), dim3(kThreads), 0, cs, peers, rank, world, exp_avg, exp_avg_sq, n4, lr,
