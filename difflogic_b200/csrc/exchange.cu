@@ -54,15 +54,30 @@ __device__ __forceinline__ float4 ld_peer(const float4 *p) {
     return v;
 }
 
-// Waits until every peer's flag for barrier `b` has reached `epoch`; false when the poll limit ran out.
+__device__ __forceinline__ int ld_relaxed_sys(const int *p) {
+    int v;
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Called by ALL threads of a block: waits until every peer's flag for barrier `b` has reached `epoch`; false when a
+// poll limit ran out.  Thread p polls peer p's flag with relaxed loads and reads it once more with acquire when it has seen it: a chain of
+// `world` acquire loads per block, from hundreds of blocks on the same few words, cost tens of microseconds at
+// eight ranks.  The block barrier passes the ordering on to the other threads.
 __device__ __forceinline__ bool wait_peers(const int *my_flags, int world, int b, int epoch) {
-    for (int p = 0; p < world; ++p) {
+    bool ok = true;
+    if ((int)threadIdx.x < world) {
         unsigned spin = 0;
-        while (ld_acquire_sys(my_flags + 2 * p + b) < epoch) {
-            if (++spin > kExchangeSpinLimit) return false;
+        while (ld_relaxed_sys(my_flags + 2 * threadIdx.x + b) < epoch) {
+            if (++spin > kExchangeSpinLimit) {
+                ok = false;
+                break;
+            }
         }
+        (void)ld_acquire_sys(my_flags + 2 * threadIdx.x + b);  // one acquire once the flag is there (a system-scope
+                                                               // fence here cost 10 us per barrier)
     }
-    return true;
+    return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -82,7 +97,6 @@ __global__ void __launch_bounds__(kThreads, 2)
 adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict__ m, float *__restrict__ v, int64_t n4_total,
                      float lr, float beta1, float beta2, float eps, int *__restrict__ state) {
     __shared__ float s_step_size, s_bc2_sqrt;
-    __shared__ int s_ok;
     __shared__ __align__(128) float4 s_gather[2][kGatherVecs];
     __shared__ __align__(8) uint64_t s_gather_bar[2];
     if (threadIdx.x == 0) {
@@ -96,15 +110,14 @@ adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict
     const int epoch = state[0] + 1;
     // barrier A: announce (once per rank), then everybody waits on the local flag words
     if (blockIdx.x == 0 && threadIdx.x < world) st_release_sys(peers.flags[threadIdx.x] + 2 * rank + 0, epoch);
-    if (threadIdx.x == 0) {
-        s_ok = wait_peers(peers.flags[rank], world, 0, epoch) ? 1 : 0;
+    if (threadIdx.x == kThreads - 1) {  // a thread that polls no flag
         const float t = (float)epoch;
         s_step_size = lr / (1.f - powf(beta1, t));
         s_bc2_sqrt = sqrtf(1.f - powf(beta2, t));
     }
-    __syncthreads();
+    const bool ok_a = wait_peers(peers.flags[rank], world, 0, epoch);  // ends with a block barrier
     if (blockIdx.x == 0 && threadIdx.x == 0) stamps[1] = global_timer_ns();
-    if (!s_ok && threadIdx.x == 0) state[2] = 1;
+    if (!ok_a && threadIdx.x == 0) state[2] = 1;
     const float step_size = s_step_size, bc2_sqrt = s_bc2_sqrt;
     const float omb1 = 1.f - beta1, omb2 = 1.f - beta2, inv_world = 1.f / (float)world;
 
@@ -185,10 +198,9 @@ adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict
             stamps[2] = global_timer_ns();
             for (int p = 0; p < world; ++p) st_release_sys(peers.flags[p] + 2 * rank + 1, epoch);
         }
-        s_ok = wait_peers(peers.flags[rank], world, 1, epoch) ? 1 : 0;
     }
-    __syncthreads();
-    if (!s_ok && threadIdx.x == 0) state[2] = 1;
+    const bool ok_b = wait_peers(peers.flags[rank], world, 1, epoch);
+    if (!ok_b && threadIdx.x == 0) state[2] = 1;
     if (blockIdx.x == 0 && threadIdx.x == 0) stamps[3] = global_timer_ns();
 
     // Pull the other ranks' slices: 8 KB pieces, each fetched by ONE bulk asynchronous copy (the 1-D TMA form, peer
