@@ -6,11 +6,7 @@ import torch
 from oracle import logic_oracle as O
 from tests.helpers import assert_forward_close, random_layer
 
-import os  # noqa: E402
-
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("DL_TEST_STAGED_FORWARD", "0") != "1",
-                                 reason="the staged forward kernel is opt-in (DL_FORWARD_KERNEL=staged); set DL_TEST_STAGED_FORWARD=1")]
+pytestmark = pytest.mark.gpu
 
 ops = pytest.importorskip("difflogic_b200.ops")
 from difflogic_b200 import _native as N  # noqa: E402
