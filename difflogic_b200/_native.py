@@ -19,12 +19,16 @@ _f32 = ctypes.c_float
 DL_OK, DL_ERR_INVALID_ARG, DL_ERR_BAD_BIT_COUNT, DL_ERR_NOT_DIVISIBLE, DL_ERR_CUDA, DL_ERR_TOO_LARGE = range(6)
 W_LOGITS, W_PROBS, W_ARGMAX = 0, 1, 2
 LAUNCH_PLAIN, LAUNCH_OVERLAP_SETUP = 0, 1
+(TUNE_NO_PDL, TUNE_EVAL_KERNEL, TUNE_EVAL_SHAPE, TUNE_GROUPBITSUM_KERNEL, TUNE_GROUPSUM_KERNEL, TUNE_FUSED_CLUSTER,
+ TUNE_FORWARD_KERNEL) = range(7)
 
 # name -> (restype, argtypes); mirrors include/difflogic_b200.h one to one
 SIGNATURES = {
     "dl_version": (_int, []),
     "dl_last_error_string": (ctypes.c_char_p, []),
     "dl_async_error": (_int, []),
+    "dl_set_tuning": (_int, [_int, _int]),
+    "dl_get_tuning": (_int, [_int]),
     "dl_forward_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr]),
     "dl_coefs_f32": (_int, [_ptr, _int, _ptr, _i64, _ptr]),
     "dl_backward_w_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _int, _ptr, _i64, _i64, _i64, _int, _ptr]),
@@ -60,7 +64,10 @@ SIGNATURES = {
     "dl_comm_export": (_int, [_ptr, _ptr]),
     "dl_comm_import": (_int, [_ptr, _ptr]),
     "dl_comm_close": (_int, [_ptr]),
-    "dl_adam_exchange_step_f32": (_int, [_ptr, _ptr, _ptr, _int, _int, _ptr, _ptr, _i64, _f32, _f32, _f32, _f32, _ptr, _ptr]),
+    "dl_exchange_flag_bytes": (ctypes.c_size_t, []),
+    "dl_exchange_reduce_adam_f32": (_int, [_ptr, _ptr, _ptr, _int, _int, _ptr, _ptr, _i64, _i64, _int, _f32, _f32, _f32, _f32, _ptr,
+                                           ctypes.c_uint32, _ptr]),
+    "dl_exchange_gather_f32": (_int, [_ptr, _ptr, _int, _int, _i64, _i64, _int, _ptr, ctypes.c_uint32, _ptr]),
     "dl_adam_step_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _f32, _f32, _f32, _f32, _f32, _ptr, _ptr]),
     "dl_prefetch_l2": (_int, [_ptr, ctypes.c_size_t, _ptr]),
 }
@@ -98,6 +105,28 @@ def lib():
             fn.argtypes = args
         _lib = handle
     return _lib
+
+
+class tuning:
+    """Context manager: a kernel-choice switch (dl_set_tuning) set for the duration of a block, for A/B comparisons."""
+
+    def __init__(self, key, value):
+        self.key, self.value = key, value
+
+    def __enter__(self):
+        self.old = lib().dl_get_tuning(self.key)
+        check_status(lib().dl_set_tuning(self.key, self.value))
+        return self
+
+    def __exit__(self, *exc):
+        lib().dl_set_tuning(self.key, self.old)
+
+
+def check_status(status):
+    """check() for entry points that launch nothing."""
+    global _launches
+    check(status)
+    _launches -= 1
 
 
 def last_error():

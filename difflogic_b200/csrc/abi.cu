@@ -18,14 +18,33 @@ int fail(int code, const char *fmt, ...) {
     return code;
 }
 
-bool pdl_enabled() {
-    static int cached = -1;
-    if (cached < 0) {
-        const char *v = getenv("DL_PDL");
-        cached = (v != nullptr && v[0] == '0') ? 0 : 1;
-    }
-    return cached == 1;
+// Kernel-choice switches for A/B measurements (dl_set_tuning).  They are plain ints read on the hot entry points; their
+// initial values are taken from the environment ONCE, when the library is loaded.
+static int g_tuning[DL_TUNE_COUNT];
+
+static int env_choice(const char *name, const char *letters, const int *values, int n) {
+    const char *v = getenv(name);
+    if (v == nullptr) return 0;
+    for (int i = 0; i < n; ++i)
+        if (v[0] == letters[i]) return values[i];
+    return 0;
 }
+
+static const bool g_tuning_loaded = [] {
+    const int pdl[] = {1}, ek[] = {1}, es[] = {1, 2}, gb[] = {1, 2}, gs[] = {1}, fc[] = {2, 4, 8}, fk[] = {1, 2};
+    g_tuning[DL_TUNE_NO_PDL] = env_choice("DL_PDL", "0", pdl, 1);
+    g_tuning[DL_TUNE_EVAL_KERNEL] = env_choice("DL_EVAL_KERNEL", "p", ek, 1);
+    g_tuning[DL_TUNE_EVAL_SHAPE] = env_choice("DL_EVAL_SHAPE", "ws", es, 2);
+    g_tuning[DL_TUNE_GROUPBITSUM_KERNEL] = env_choice("DL_GROUPBITSUM_KERNEL", "ps", gb, 2);
+    g_tuning[DL_TUNE_GROUPSUM_KERNEL] = env_choice("DL_GROUPSUM_KERNEL", "t", gs, 1);
+    g_tuning[DL_TUNE_FUSED_CLUSTER] = env_choice("DL_FUSED_CLUSTER", "248", fc, 3);
+    g_tuning[DL_TUNE_FORWARD_KERNEL] = env_choice("DL_FORWARD_KERNEL", "ps", fk, 2);
+    return true;
+}();
+
+int tuning(int key) { return __atomic_load_n(&g_tuning[key], __ATOMIC_RELAXED); }
+
+bool pdl_enabled() { return tuning(DL_TUNE_NO_PDL) == 0; }
 
 int launch_status(const char *what) {
     cudaError_t e = cudaPeekAtLastError();
@@ -57,6 +76,15 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float *__restric
 extern "C" DL_API int dl_version(void) { return 100; }
 
 extern "C" DL_API const char *dl_last_error_string(void) { return dl::g_error; }
+
+extern "C" DL_API int dl_set_tuning(int key, int value) {
+    DL_REQUIRE(key >= 0 && key < DL_TUNE_COUNT, DL_ERR_INVALID_ARG, "dl_set_tuning: unknown key %d", key);
+    (void)dl::g_tuning_loaded;
+    __atomic_store_n(&dl::g_tuning[key], value, __ATOMIC_RELAXED);
+    return DL_OK;
+}
+
+extern "C" DL_API int dl_get_tuning(int key) { return key >= 0 && key < DL_TUNE_COUNT ? dl::tuning(key) : -1; }
 
 extern "C" DL_API int dl_coefs_f32(const float *w, int w_mode, float *coef, int64_t n_out, void *stream) {
     DL_REQUIRE(w && coef, DL_ERR_INVALID_ARG, "dl_coefs_f32: null pointer");

@@ -36,12 +36,13 @@ static inline int pow2_at_least(int64_t v, int cap) {
 // launched so that a kernel's set-up (reading the connection indices / the gather plan) may run
 // while the previous kernel in the stream is still draining; everything else is touched only
 // after grid_dependency_wait().  Without the launch attribute the two device calls are no-ops,
-// so the same kernels are correct under an ordinary launch.  DL_PDL=0 in the environment turns
-// the attribute off everywhere.
+// so the same kernels are correct under an ordinary launch.  dl_set_tuning(DL_TUNE_NO_PDL, 1) (or DL_PDL=0 in the
+// environment when the library is loaded) turns the attribute off everywhere.
 // ---------------------------------------------------------------------------------------------
 namespace dl {
 
 bool pdl_enabled();
+int tuning(int key);  // current value of a DL_TUNE_* switch (dl_set_tuning); 0 = automatic choice
 
 #ifdef __CUDACC__
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -438,9 +438,9 @@ static size_t fg_shared_bytes() {
 static int fg_cluster_size(int64_t m) {
     // The consumers are instruction bound, and every unit costs a fixed number of instructions for the reduction:
     // the fewer CTAs share a class the better, as long as a share stays within 255 neurons (and above 16).
-    // DL_FUSED_CLUSTER=2|4|8 overrides (for A/B timing).
-    const char *force = getenv("DL_FUSED_CLUSTER");
-    if (force != nullptr && (force[0] == '4' || force[0] == '8' || force[0] == '2')) return force[0] - '0';
+    // DL_TUNE_FUSED_CLUSTER = 2 | 4 | 8 overrides (for A/B timing).
+    const int force = tuning(DL_TUNE_FUSED_CLUSTER);
+    if (force == 2 || force == 4 || force == 8) return force;
     if (m <= 2 * kFgMaxShare && m < 4 * 64) return 2;
     if (m <= 4 * kFgMaxShare) return 4;
     return 8;

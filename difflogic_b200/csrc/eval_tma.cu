@@ -213,11 +213,11 @@ static int launch_eval_tma_shape(const void *x, const int64_t *a, const int64_t 
 
 int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_in, int64_t n_out,
                     int64_t row_bytes, cudaStream_t st) {
-    // fan-out of an input row: 2 * n_out / n_in.  DL_EVAL_SHAPE=wide|square overrides the choice (for A/B timing).
-    const char *force = getenv("DL_EVAL_SHAPE");
+    // fan-out of an input row: 2 * n_out / n_in.  DL_TUNE_EVAL_SHAPE = 1 (wide) | 2 (square) overrides the choice.
+    const int force = tuning(DL_TUNE_EVAL_SHAPE);
     const int64_t chunk = row_bytes < kMaxChunk ? row_bytes : kMaxChunk;
     const bool few_tiles = ceil_div(row_bytes, chunk) * ceil_div(n_out, 16) < (int64_t)64 * sm_count();
-    const bool wide = force && force[0] == 'w' ? true : force && force[0] == 's' ? false : (n_out >= 2 * n_in || few_tiles);
+    const bool wide = force == 1 ? true : force == 2 ? false : (n_out >= 2 * n_in || few_tiles);
     if (wide) return launch_eval_tma_shape<8, 3>(x, a, b, gate, y, n_out, row_bytes, 2, st);
     return launch_eval_tma_shape<16, 2>(x, a, b, gate, y, n_out, row_bytes, 1, st);
 }

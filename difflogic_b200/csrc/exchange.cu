@@ -1,47 +1,55 @@
-// Gradient exchange and optimizer step of batch-sharded training in ONE kernel, over peer memory.
+// Gradient exchange and optimizer step of batch-sharded training over peer memory, one bucket at a time.
 //
 // Every rank (one process per GPU) keeps the flat gradient buffer and the flat parameter buffer of the network in
-// memory that its peers have mapped (CUDA IPC over NVLink).  After the backward pass each rank owns one slice of
-// the parameters:
-//   1. barrier A: every rank tells every peer that its gradients are complete (a flag store into the peer's
-//      memory) and waits until all peers have said so;
-//   2. for its slice it reads that slice of ALL ranks' gradients straight from their memory (16-byte loads over
-//      NVLink), averages, applies Adam with its slice of the moments, and stores the new parameters into its OWN
-//      parameter buffer;
-//   3. barrier B: when a rank's slice is complete (a fence over local stores: cheap) it tells the peers; every block
-//      waits until all ranks have said so;
-//   4. it pulls the other ranks' slices of the new parameters from their memory into its own parameter buffer
-//      (peer loads again).  The kernel ends with every rank holding the complete updated parameters.
-// Pulling instead of pushing the new parameters matters: after stores INTO peer memory a rank has to wait for
-// their system-wide visibility before it may raise its flag, and that fence measured 8 us of a 27 us kernel.
-// This replaces an NCCL all-reduce of the gradients followed by a full Adam step on every rank: the bytes that
-// cross NVLink are the same as a reduce-scatter plus all-gather, there is no extra launch, and each rank touches
-// only 1/N of the optimizer state.
+// memory that its peers have mapped (CUDA IPC over NVLink).  The buffers are cut into buckets (one per layer, say);
+// as soon as a bucket's gradients are complete on a rank -- its backward_w kernel has finished, while the backward
+// pass of the layers below is still running -- that rank launches two small kernels for the bucket on a stream of
+// their own:
+//   reduce + Adam   announces "my gradients of this bucket are complete" to every peer (a flag store into the peer's
+//                   memory), waits until all peers have said so, reads ITS slice of the bucket from all ranks'
+//                   gradient buffers (16-byte loads over NVLink), averages, applies Adam with its slice of the moments
+//                   and stores the new parameters into its OWN parameter buffer; the last block to finish tells the
+//                   peers "my slice of this bucket is complete";
+//   gather          waits until all ranks have said that, and pulls the other ranks' slices of the new parameters
+//                   from their memory into its own parameter buffer.
+// Neither kernel waits for another block of its own grid, so nothing has to be resident together and the kernels
+// can share the GPU with the backward pass; what crosses NVLink is what a reduce-scatter plus an all-gather moves.
+// Only the bucket of the layer whose gradients come last is not hidden behind the backward pass.
+// Pulling instead of pushing the new parameters matters: after stores INTO peer memory a rank has to wait for their
+// system-wide visibility before it may raise its flag, and that fence measured 8 us.
 //
-// The peers are other GPUs of this machine mapped by plain peer-to-peer access; the loads and stores are ordinary
-// ld/st instructions.  Every wait is bounded (kExchangeSpinLimit polls); when one runs out the kernel records it
-// in the state words and carries on, so a missing rank cannot hang the others.
+// The peers are other GPUs of this machine mapped by plain peer-to-peer access; every access to their memory is an
+// ordinary ld/st instruction (no bulk copy, no TMA, no multicast).  Every wait is bounded (poll_limit polls); a kernel
+// whose wait runs out sets the error word of the bucket's state, changes NOTHING else (parameters, moments and step
+// count stay as they were) and returns, so a missing rank cannot hang the others and cannot corrupt the weights.
 #include <string.h>
 
 #include "adam_math.cuh"
 #include "common.cuh"
-#include "tma.cuh"
 
 namespace dl {
 
 constexpr int kMaxRanks = 16;
-constexpr unsigned kExchangeSpinLimit = 1u << 22;
-constexpr int kGatherVecs = 512;  // float4 per piece of the gather phase: 8 KB
+constexpr int kMaxBuckets = 32;
+constexpr unsigned kExchangePollLimit = 1u << 22;  // default poll limit: a second or so
+constexpr int kFlagBytes = kMaxBuckets * kMaxRanks * 2 * 4;
 
 struct ExchangePeers {
     float *param[kMaxRanks];      // flat parameter buffer of each rank (index = rank; own entry is local memory)
     const float *grad[kMaxRanks]; // flat gradient buffer of each rank
-    int *flags[kMaxRanks];        // flag words of each rank: flags[r][2*p + b] is written by rank p for barrier b
+    int *flags[kMaxRanks];        // flag words of each rank: word (bucket, p, which) is written by rank p
 };
+
+__device__ __forceinline__ int flag_index(int bucket, int peer, int which) { return (bucket * kMaxRanks + peer) * 2 + which; }
 
 __device__ __forceinline__ int ld_acquire_sys(const int *p) {
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ int ld_relaxed_sys(const int *p) {
+    int v;
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ void st_release_sys(int *p, int v) {
@@ -54,28 +62,21 @@ __device__ __forceinline__ float4 ld_peer(const float4 *p) {
     return v;
 }
 
-__device__ __forceinline__ int ld_relaxed_sys(const int *p) {
-    int v;
-    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// Called by ALL threads of a block: waits until every peer's flag for barrier `b` has reached `epoch`; false when a
-// poll limit ran out.  Thread p polls peer p's flag with relaxed loads and reads it once more with acquire when it has seen it: a chain of
-// `world` acquire loads per block, from hundreds of blocks on the same few words, cost tens of microseconds at
-// eight ranks.  The block barrier passes the ordering on to the other threads.
-__device__ __forceinline__ bool wait_peers(const int *my_flags, int world, int b, int epoch) {
+// Called by ALL threads of a block: waits until every rank's flag (bucket, rank, which) in this rank's flag words has
+// reached `epoch`; false when a poll limit ran out.  Thread p polls rank p's flag with relaxed loads and reads it once
+// more with acquire when it has seen it; the block barrier passes the ordering on to the other threads.
+__device__ __forceinline__ bool wait_peers(const int *my_flags, int world, int bucket, int which, int epoch, unsigned limit) {
     bool ok = true;
     if ((int)threadIdx.x < world) {
+        const int *f = my_flags + flag_index(bucket, threadIdx.x, which);
         unsigned spin = 0;
-        while (ld_relaxed_sys(my_flags + 2 * threadIdx.x + b) < epoch) {
-            if (++spin > kExchangeSpinLimit) {
+        while (ld_relaxed_sys(f) < epoch) {
+            if (++spin > limit) {
                 ok = false;
                 break;
             }
         }
-        (void)ld_acquire_sys(my_flags + 2 * threadIdx.x + b);  // one acquire once the flag is there (a system-scope
-                                                               // fence here cost 10 us per barrier)
+        (void)ld_acquire_sys(f);
     }
     return __syncthreads_and(ok ? 1 : 0) != 0;
 }
@@ -86,190 +87,172 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
-// state: [0] steps done, [1] ticket of blocks that finished their part of the slice, [2] error (a wait ran out),
-// [3] ticket of blocks that finished pulling, [4..15] six 64-bit time stamps of the latest step in nanoseconds:
-// entry, after barrier A (block 0), slice done (last block), after barrier B (block 0), block 0's elements stored, end
+// state of a bucket, 16 ints: [0] steps done, [1] ticket of the reduce kernel, [2] error (a wait ran out), [3] ticket
+// of the gather kernel, [4..15] six 64-bit time stamps of the latest step in nanoseconds: reduce kernel entered,
+// all ranks' gradients seen (block 0), slice complete (last block), gather kernel entered, all ranks' slices seen
+// (block 0), gather done (last block).
+//
 // WORLD = number of ranks when it is 2, 4 or 8 (all loads of an iteration are then issued before the first one is
 // used: 8 peer loads of 16 bytes in flight per thread, i.e. 8 / WORLD elements per iteration), 0 = any number of ranks
-// (one element per iteration, peers read one after the other).
+// (one element per iteration, peers read one after the other).  The sum over the ranks is formed in rank order in
+// every variant, so all of them give the same bits.
 template <int WORLD>
-__global__ void __launch_bounds__(kThreads, 2)
-adam_exchange_kernel(ExchangePeers peers, int rank, int world, float *__restrict__ m, float *__restrict__ v, int64_t n4_total,
-                     float lr, float beta1, float beta2, float eps, int *__restrict__ state) {
+__global__ void __launch_bounds__(kThreads)
+exchange_reduce_adam_kernel(ExchangePeers peers, int rank, int world, float *__restrict__ m, float *__restrict__ v, int64_t off4,
+                            int64_t n4, int bucket, float lr, float beta1, float beta2, float eps, int *__restrict__ state,
+                            unsigned poll_limit) {
     __shared__ float s_step_size, s_bc2_sqrt;
-    __shared__ __align__(128) float4 s_gather[2][kGatherVecs];
-    __shared__ __align__(8) uint64_t s_gather_bar[2];
-    if (threadIdx.x == 0) {
-        mbar_init(&s_gather_bar[0], 1);
-        mbar_init(&s_gather_bar[1], 1);
-        mbar_fence_init();
-    }
-    grid_dependency_wait();  // this rank's gradients come from the kernels just before
     unsigned long long *stamps = reinterpret_cast<unsigned long long *>(state + 4);
     if (blockIdx.x == 0 && threadIdx.x == 0) stamps[0] = global_timer_ns();
     const int epoch = state[0] + 1;
-    // barrier A: announce (once per rank), then everybody waits on the local flag words
-    if (blockIdx.x == 0 && threadIdx.x < world) st_release_sys(peers.flags[threadIdx.x] + 2 * rank + 0, epoch);
+    // announce (once per rank): this rank's gradients of the bucket were written by kernels that completed before this
+    // one started; the fence orders them before the flag for observers on other GPUs
+    if (blockIdx.x == 0 && (int)threadIdx.x < world) {
+        __threadfence_system();
+        st_release_sys(peers.flags[threadIdx.x] + flag_index(bucket, rank, 0), epoch);
+    }
     if (threadIdx.x == kThreads - 1) {  // a thread that polls no flag
         const float t = (float)epoch;
         s_step_size = lr / (1.f - powf(beta1, t));
         s_bc2_sqrt = sqrtf(1.f - powf(beta2, t));
     }
-    const bool ok_a = wait_peers(peers.flags[rank], world, 0, epoch);  // ends with a block barrier
+    const bool ok = wait_peers(peers.flags[rank], world, bucket, 0, epoch, poll_limit);  // ends with a block barrier
     if (blockIdx.x == 0 && threadIdx.x == 0) stamps[1] = global_timer_ns();
-    if (!ok_a && threadIdx.x == 0) state[2] = 1;
-    const float step_size = s_step_size, bc2_sqrt = s_bc2_sqrt;
-    const float omb1 = 1.f - beta1, omb2 = 1.f - beta2, inv_world = 1.f / (float)world;
 
-    // this rank's slice, in float4 units
-    const int64_t per = (n4_total + world - 1) / world;
-    const int64_t lo = min((int64_t)rank * per, n4_total), hi = min(lo + per, n4_total);
-    float4 *m4 = reinterpret_cast<float4 *>(m), *v4 = reinterpret_cast<float4 *>(v);  // moments of the slice only
-    float4 *own_param = reinterpret_cast<float4 *>(peers.param[rank]);
-
-    const AdamConsts consts = {omb1, beta2, omb2, step_size, bc2_sqrt, eps};
-    if (WORLD > 0) {
+    if (ok) {
+        const AdamConsts consts = {1.f - beta1, beta2, 1.f - beta2, s_step_size, s_bc2_sqrt, eps};
+        const float inv_world = 1.f / (float)world;
+        // this rank's slice of the bucket, in float4 units of the flat buffers
+        const int64_t per = (n4 + world - 1) / world;
+        const int64_t lo = off4 + min((int64_t)rank * per, n4), hi = min(lo + per, off4 + n4);
+        float4 *m4 = reinterpret_cast<float4 *>(m), *v4 = reinterpret_cast<float4 *>(v);
+        float4 *own_param = reinterpret_cast<float4 *>(peers.param[rank]);
         constexpr int W = WORLD > 0 ? WORLD : 1;
-        constexpr int U = 8 / W;  // elements per thread and iteration
+        constexpr int U = WORLD > 0 ? 8 / W : 1;  // elements per thread and iteration
         const int64_t stride = (int64_t)gridDim.x * kThreads;
         for (int64_t base = lo + (int64_t)blockIdx.x * kThreads + threadIdx.x; base < hi; base += stride * U) {
-            float4 gp[U][W], pp_[U], mm_[U], vv_[U];
+            float4 gp[U][W], g[U], pp[U], mm[U], vv[U];
+            // every load of the iteration is issued before the first one is used
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int64_t i = base + u * stride;
+                g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (i < hi) {
+                    if (WORLD > 0) {
 #pragma unroll
-                    for (int p = 0; p < W; ++p) gp[u][p] = ld_peer(reinterpret_cast<const float4 *>(peers.grad[p]) + i);
-                    pp_[u] = own_param[i];
-                    mm_[u] = m4[i - lo];
-                    vv_[u] = v4[i - lo];
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int64_t i = base + u * stride;
-                if (i < hi) {
-                    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                    for (int p = 0; p < W; ++p) {  // same order of additions as the generic loop
-                        g.x += gp[u][p].x; g.y += gp[u][p].y; g.z += gp[u][p].z; g.w += gp[u][p].w;
+                        for (int p = 0; p < W; ++p) gp[u][p] = ld_peer(reinterpret_cast<const float4 *>(peers.grad[p]) + i);
+                    } else {
+                        for (int p = 0; p < world; ++p) {
+                            const float4 one = ld_peer(reinterpret_cast<const float4 *>(peers.grad[p]) + i);
+                            g[u].x += one.x; g[u].y += one.y; g[u].z += one.z; g[u].w += one.w;
+                        }
                     }
-                    float4 pp = pp_[u], mm = mm_[u], vv = vv_[u];
-                    g.x = __fmul_rn(g.x, inv_world); g.y = __fmul_rn(g.y, inv_world);
-                    g.z = __fmul_rn(g.z, inv_world); g.w = __fmul_rn(g.w, inv_world);
-                    adam_update4(pp, g, mm, vv, consts);
-                    m4[i - lo] = mm;
-                    v4[i - lo] = vv;
-                    own_param[i] = pp;
+                    pp[u] = own_param[i];
+                    mm[u] = m4[i];
+                    vv[u] = v4[i];
                 }
             }
-        }
-    } else {
-        for (int64_t i = lo + (int64_t)blockIdx.x * kThreads + threadIdx.x; i < hi; i += (int64_t)gridDim.x * kThreads) {
-            float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int p = 0; p < world; ++p) {
-                const float4 gp = ld_peer(reinterpret_cast<const float4 *>(peers.grad[p]) + i);
-                g.x += gp.x; g.y += gp.y; g.z += gp.z; g.w += gp.w;
+            if (WORLD > 0) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (base + u * stride < hi) {
+#pragma unroll
+                        for (int p = 0; p < W; ++p) {  // rank order, as in the generic loop
+                            g[u].x += gp[u][p].x; g[u].y += gp[u][p].y; g[u].z += gp[u][p].z; g[u].w += gp[u][p].w;
+                        }
+                    }
+                }
             }
-            float4 pp = own_param[i];
-            float4 mm = m4[i - lo], vv = v4[i - lo];
-            g.x = __fmul_rn(g.x, inv_world); g.y = __fmul_rn(g.y, inv_world);
-            g.z = __fmul_rn(g.z, inv_world); g.w = __fmul_rn(g.w, inv_world);
-            adam_update4(pp, g, mm, vv, consts);
-            m4[i - lo] = mm;
-            v4[i - lo] = vv;
-            own_param[i] = pp;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t i = base + u * stride;
+                if (i < hi) {
+                    g[u].x = __fmul_rn(g[u].x, inv_world); g[u].y = __fmul_rn(g[u].y, inv_world);
+                    g[u].z = __fmul_rn(g[u].z, inv_world); g[u].w = __fmul_rn(g[u].w, inv_world);
+                    adam_update4(pp[u], g[u], mm[u], vv[u], consts);
+                    m4[i] = mm[u];
+                    v4[i] = vv[u];
+                    own_param[i] = pp[u];
+                }
+            }
         }
     }
-    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[4] = global_timer_ns();  // first block: its elements are stored
 
-    // barrier B: the last block of this rank to finish its part of the slice tells the peers; every block then waits
-    // until all ranks' slices are complete.  (All blocks of the grid are resident together -- the host sizes the
-    // grid for that -- so waiting for this grid's own last block cannot starve it.)
-    // Every thread orders its stores at GPU scope (they are stores to this GPU's own memory: once they are visible
-    // on this GPU, a peer's load over NVLink sees them too); only the one thread that raises the flag pays for a
-    // system-scope fence.  A system-scope fence in every thread measured 8 us.
+    // The last block of this rank to finish its part of the slice tells the peers -- unless a wait ran out in any block
+    // of this launch: then the flag stays down and the peers' gather kernels run out too, instead of fetching
+    // a slice that is only partly updated.  Every thread orders its stores at GPU scope (they are stores to this
+    // GPU's own memory: once they are visible on this GPU, a peer's load over NVLink sees them too); only the one
+    // thread that raises the flags pays for a system-scope fence.
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        const int done = atomicAdd(state + 1, 1);
-        if (done == (int)gridDim.x - 1) {
-            __threadfence_system();
-            stamps[2] = global_timer_ns();
-            for (int p = 0; p < world; ++p) st_release_sys(peers.flags[p] + 2 * rank + 1, epoch);
+        if (!ok) atomicExch(state + 2, 1);
+        __threadfence();
+        const int add = ok ? 1 : 0x10001;  // low half: blocks that are through; high half: those whose wait ran out
+        const int all = atomicAdd(state + 1, add) + add;
+        if ((all & 0xffff) == (int)gridDim.x) {
+            state[1] = 0;
+            if ((all >> 16) == 0) {
+                __threadfence_system();
+                stamps[2] = global_timer_ns();
+                for (int p = 0; p < world; ++p) st_release_sys(peers.flags[p] + flag_index(bucket, rank, 1), epoch);
+            }
         }
     }
-    const bool ok_b = wait_peers(peers.flags[rank], world, 1, epoch);
-    if (!ok_b && threadIdx.x == 0) state[2] = 1;
+}
+
+// Pulls the other ranks' slices of the bucket's new parameters, 8 peer loads of 16 bytes in flight per thread.
+__global__ void __launch_bounds__(kThreads)
+exchange_gather_kernel(ExchangePeers peers, int rank, int world, int64_t off4, int64_t n4, int bucket, int *__restrict__ state,
+                       unsigned poll_limit) {
+    constexpr int U = 8;
+    unsigned long long *stamps = reinterpret_cast<unsigned long long *>(state + 4);
     if (blockIdx.x == 0 && threadIdx.x == 0) stamps[3] = global_timer_ns();
-
-    // Pull the other ranks' slices: 8 KB pieces, each fetched by ONE bulk asynchronous copy (the 1-D TMA form, peer
-    // memory -> this CTA's shared memory, no multicast) and written to this rank's parameter buffer with 16-byte stores.
-    // Two pieces per block are in flight at a time; the copy engine needs no registers for its requests.  (With eight
-    // ranks this phase measured the same 22 us for 4.5 MB as plain 16-byte peer loads, eight in flight per thread.)
-    {
-        const int64_t per_pieces = (per + kGatherVecs - 1) / kGatherVecs;  // pieces per source slice
-        const int64_t npieces = (int64_t)(world - 1) * per_pieces;
-        uint32_t fills[2] = {0u, 0u};  // how often each buffer has been filled: the parity of its barrier's phase
-        bool ok = true;
-        // the peers' slices were written with ordinary stores; order the asynchronous copies below behind the flags
-        // that announced them
-        if (threadIdx.x == 0) asm volatile("fence.proxy.async;" ::: "memory");
-        for (int64_t c0 = blockIdx.x; c0 < npieces; c0 += 2 * (int64_t)gridDim.x) {
-            int64_t start[2];
-            int count[2], src_of[2];
+    const int epoch = state[0] + 1;
+    const bool ok = wait_peers(peers.flags[rank], world, bucket, 1, epoch, poll_limit);
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[4] = global_timer_ns();
+    if (ok && world > 1) {
+        const int64_t per = (n4 + world - 1) / world;
+        const int64_t total = (int64_t)(world - 1) * per;  // positions in the other ranks' slices (the tail may be short)
+        const int64_t end4 = off4 + n4;
+        float4 *own_param = reinterpret_cast<float4 *>(peers.param[rank]);
+        const int64_t stride = (int64_t)gridDim.x * kThreads;
+        for (int64_t base = (int64_t)blockIdx.x * kThreads + threadIdx.x; base < total; base += stride * U) {
+            float4 val[U];
+            int64_t at[U];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int64_t c = c0 + (int64_t)i * gridDim.x;
-                count[i] = 0;
-                start[i] = 0;
-                src_of[i] = 0;
-                if (c < npieces) {
-                    int src = (int)(c / per_pieces);
+            for (int u = 0; u < U; ++u) {
+                const int64_t idx = base + u * stride;
+                at[u] = -1;
+                if (idx < total) {
+                    int src = (int)(idx / per);
+                    const int64_t within = idx - (int64_t)src * per;
                     if (src >= rank) ++src;  // skip this rank's own slice
-                    const int64_t first = (int64_t)src * per + (c % per_pieces) * kGatherVecs;
-                    const int64_t end = min((int64_t)(src + 1) * per, n4_total);
-                    if (first < end) {
-                        start[i] = first;
-                        count[i] = (int)min((int64_t)kGatherVecs, end - first);
-                        src_of[i] = src;
-                    }
-                }
-            }
-            if (threadIdx.x == 0) {
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    if (count[i] > 0) {
-                        mbar_arrive_expect_tx(&s_gather_bar[i], (uint32_t)count[i] * 16u);
-                        bulk_load(s_gather[i], reinterpret_cast<const float4 *>(peers.param[src_of[i]]) + start[i],
-                                  (uint32_t)count[i] * 16u, &s_gather_bar[i]);
+                    const int64_t i = off4 + (int64_t)src * per + within;
+                    if (i < end4) {
+                        at[u] = i;
+                        val[u] = ld_peer(reinterpret_cast<const float4 *>(peers.param[src]) + i);
                     }
                 }
             }
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                if (count[i] > 0) {
-                    if (ok && !mbar_wait(&s_gather_bar[i], fills[i] & 1u)) ok = false;  // bounded
-                    ++fills[i];
-                    if (ok)
-                        for (int v = threadIdx.x; v < count[i]; v += kThreads) own_param[start[i] + v] = s_gather[i][v];
-                }
-            }
-            __syncthreads();  // the pieces are consumed before their buffers are refilled
+            for (int u = 0; u < U; ++u)
+                if (at[u] >= 0) own_param[at[u]] = val[u];
         }
-        if (!ok && threadIdx.x == 0) state[2] = 1;
     }
-
-    // the last block to finish everything resets the tickets and advances the step counter
+    // the last block to finish advances the bucket's step count -- only when no block's wait ran out
     __syncthreads();
     if (threadIdx.x == 0) {
+        if (!ok) atomicExch(state + 2, 1);
         __threadfence();
-        const int done = atomicAdd(state + 3, 1);
-        if (done == (int)gridDim.x - 1) {
-            stamps[5] = global_timer_ns();
-            state[1] = 0;
+        const int add = ok ? 1 : 0x10001;
+        const int all = atomicAdd(state + 3, add) + add;
+        if ((all & 0xffff) == (int)gridDim.x) {
             state[3] = 0;
-            state[0] = epoch;
+            if ((all >> 16) == 0) {
+                stamps[5] = global_timer_ns();
+                state[0] = epoch;
+            }
         }
     }
 }
@@ -327,55 +310,67 @@ extern "C" DL_API int dl_comm_close(void *ptr) {
     return DL_OK;
 }
 
-// param_ptrs / grad_ptrs / flag_ptrs: HOST arrays of `world` device pointers, index = rank (own entry: own buffers).
-extern "C" DL_API int dl_adam_exchange_step_f32(void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs, int rank,
-                                                int world, float *exp_avg, float *exp_avg_sq, int64_t n, float lr, float beta1,
-                                                float beta2, float eps, int32_t *state, void *stream) {
-    DL_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, DL_ERR_INVALID_ARG,
-               "dl_adam_exchange_step_f32: rank %d of %d (at most %d ranks)", rank, world, kMaxRanks);
-    DL_REQUIRE(n >= 0 && n % 4 == 0, DL_ERR_INVALID_ARG, "dl_adam_exchange_step_f32: n must be a multiple of 4");
-    DL_REQUIRE(param_ptrs && grad_ptrs && flag_ptrs && state && exp_avg && exp_avg_sq, DL_ERR_INVALID_ARG,
-               "dl_adam_exchange_step_f32: null pointer");
-    ExchangePeers peers;
+extern "C" DL_API size_t dl_exchange_flag_bytes(void) { return (size_t)kFlagBytes; }
+
+static int exchange_peers(const char *who, ExchangePeers &peers, void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs,
+                          int rank, int world, int64_t offset, int64_t count, int bucket, const int32_t *state) {
+    DL_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, DL_ERR_INVALID_ARG, "%s: rank %d of %d (at most %d ranks)",
+               who, rank, world, kMaxRanks);
+    DL_REQUIRE(bucket >= 0 && bucket < kMaxBuckets, DL_ERR_INVALID_ARG, "%s: bucket %d outside 0 .. %d", who, bucket, kMaxBuckets - 1);
+    DL_REQUIRE(offset >= 0 && count >= 0 && offset % 4 == 0 && count % 4 == 0, DL_ERR_INVALID_ARG,
+               "%s: offset and count must be non-negative multiples of 4", who);
+    DL_REQUIRE(param_ptrs && flag_ptrs && state, DL_ERR_INVALID_ARG, "%s: null pointer", who);
     for (int p = 0; p < world; ++p) {
-        DL_REQUIRE(param_ptrs[p] && grad_ptrs[p] && flag_ptrs[p], DL_ERR_INVALID_ARG, "dl_adam_exchange_step_f32: null peer pointer");
-        DL_REQUIRE(aligned_to(param_ptrs[p], 16) && aligned_to(grad_ptrs[p], 16), DL_ERR_INVALID_ARG,
-                   "dl_adam_exchange_step_f32: buffers must be 16-byte aligned");
+        DL_REQUIRE(param_ptrs[p] && flag_ptrs[p] && (grad_ptrs == nullptr || grad_ptrs[p]), DL_ERR_INVALID_ARG, "%s: null peer pointer", who);
+        DL_REQUIRE(aligned_to(param_ptrs[p], 16) && (grad_ptrs == nullptr || aligned_to(grad_ptrs[p], 16)), DL_ERR_INVALID_ARG,
+                   "%s: buffers must be 16-byte aligned", who);
         peers.param[p] = reinterpret_cast<float *>(param_ptrs[p]);
-        peers.grad[p] = reinterpret_cast<const float *>(grad_ptrs[p]);
+        peers.grad[p] = grad_ptrs ? reinterpret_cast<const float *>(grad_ptrs[p]) : nullptr;
         peers.flags[p] = reinterpret_cast<int *>(flag_ptrs[p]);
     }
-    const int64_t n4 = n / 4;
-    const int64_t per = ceil_div(n4, world);
-    // One wave of blocks that are all resident together: every block waits at barrier B for this grid's own last
-    // block, so a block that could not be scheduled would stall the others until their wait limit.  The limit is
-    // what the occupancy calculator gives for the kernel that is launched, not a constant.
+    return DL_OK;
+}
+
+// param_ptrs / grad_ptrs / flag_ptrs: HOST arrays of `world` device pointers, index = rank (own entry: own buffers).
+extern "C" DL_API int dl_exchange_reduce_adam_f32(void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs, int rank, int world,
+                                                  float *exp_avg, float *exp_avg_sq, int64_t offset, int64_t count, int bucket, float lr,
+                                                  float beta1, float beta2, float eps, int32_t *state, uint32_t poll_limit, void *stream) {
+    ExchangePeers peers;
+    DL_REQUIRE(grad_ptrs != nullptr, DL_ERR_INVALID_ARG, "dl_exchange_reduce_adam_f32: null pointer");
+    if (int s = exchange_peers("dl_exchange_reduce_adam_f32", peers, param_ptrs, grad_ptrs, flag_ptrs, rank, world, offset, count, bucket, state))
+        return s;
+    DL_REQUIRE(exp_avg && exp_avg_sq && aligned_to(exp_avg, 16) && aligned_to(exp_avg_sq, 16), DL_ERR_INVALID_ARG,
+               "dl_exchange_reduce_adam_f32: moments must be non-null and 16-byte aligned");
+    const int64_t n4 = count / 4, per = ceil_div(n4, world);
     const int per_thread = (world == 2 || world == 4 || world == 8) ? 8 / world : 1;
+    int64_t blocks = ceil_div(per > 0 ? per : 1, (int64_t)kThreads * per_thread);
+    if (blocks > 4 * 148) blocks = 4 * 148;  // beyond that the grid-stride loop takes over; the ticket holds 16 bits
+    const unsigned limit = poll_limit ? poll_limit : kExchangePollLimit;
     int *st = reinterpret_cast<int *>(state);
     cudaStream_t cs = as_stream(stream);
-    auto launch = [&](auto kernel) -> int {
-        int dev = 0, sms = 0, per_sm = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || sms <= 0 || per_sm <= 0)
-            return launch_status("dl_adam_exchange_step_f32 (occupancy query)");
-        // enough blocks for one pass over the slice, and for the gather of the other ranks' slices (world - 1 times as
-        // many elements, 8 per thread and pass: loads over NVLink need many requests in flight), never more than fit
-        int64_t blocks = ceil_div(per > 0 ? per : 1, (int64_t)kThreads * per_thread);
-        const int64_t for_gather = ceil_div((int64_t)(world - 1) * ceil_div(per, (int64_t)kGatherVecs), (int64_t)2);  // two pieces per block
-        if (blocks < for_gather) blocks = for_gather;
-        const int64_t resident = (int64_t)sms * per_sm;
-        if (blocks > resident) blocks = resident;
-        launch_dependent(true, kernel, dim3((unsigned)blocks), dim3(kThreads), 0, cs, peers, rank, world, exp_avg, exp_avg_sq, n4, lr,
-                         beta1, beta2, eps, st);
-        return DL_OK;
-    };
-    int rc;
+#define DL_EXCHANGE_REDUCE(WW)                                                                                                     \
+    exchange_reduce_adam_kernel<WW><<<(unsigned)blocks, kThreads, 0, cs>>>(peers, rank, world, exp_avg, exp_avg_sq, offset / 4, n4, \
+                                                                          bucket, lr, beta1, beta2, eps, st, limit)
     switch (world) {
-        case 2: rc = launch(adam_exchange_kernel<2>); break;
-        case 4: rc = launch(adam_exchange_kernel<4>); break;
-        case 8: rc = launch(adam_exchange_kernel<8>); break;
-        default: rc = launch(adam_exchange_kernel<0>); break;
+        case 2: DL_EXCHANGE_REDUCE(2); break;
+        case 4: DL_EXCHANGE_REDUCE(4); break;
+        case 8: DL_EXCHANGE_REDUCE(8); break;
+        default: DL_EXCHANGE_REDUCE(0); break;
     }
-    if (rc != DL_OK) return rc;
-    return launch_status("dl_adam_exchange_step_f32");
+#undef DL_EXCHANGE_REDUCE
+    return launch_status("dl_exchange_reduce_adam_f32");
+}
+
+extern "C" DL_API int dl_exchange_gather_f32(void *const *param_ptrs, void *const *flag_ptrs, int rank, int world, int64_t offset,
+                                             int64_t count, int bucket, int32_t *state, uint32_t poll_limit, void *stream) {
+    ExchangePeers peers;
+    if (int s = exchange_peers("dl_exchange_gather_f32", peers, param_ptrs, nullptr, flag_ptrs, rank, world, offset, count, bucket, state))
+        return s;
+    const int64_t n4 = count / 4, per = ceil_div(n4, world);
+    int64_t blocks = ceil_div((int64_t)(world - 1) * per > 0 ? (int64_t)(world - 1) * per : 1, (int64_t)kThreads * 8);
+    if (blocks > 4 * 148) blocks = 4 * 148;
+    const unsigned limit = poll_limit ? poll_limit : kExchangePollLimit;
+    exchange_gather_kernel<<<(unsigned)blocks, kThreads, 0, as_stream(stream)>>>(peers, rank, world, offset / 4, n4, bucket,
+                                                                                 reinterpret_cast<int *>(state), limit);
+    return launch_status("dl_exchange_gather_f32");
 }

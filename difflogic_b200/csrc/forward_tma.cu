@@ -167,10 +167,9 @@ int forward_tma_async_error() {
 }
 
 // True when the staged kernel applies and pays: rows of whole float4s and at least 1 KB (batch >= 256), 16-byte aligned
-// buffers.  DL_FORWARD_KERNEL=plain switches it off, =staged forces it from 512-byte rows on (for A/B timing).
+// buffers.  Opt-in: DL_TUNE_FORWARD_KERNEL = 2 (staged) selects it from 512-byte rows on (for A/B timing).
 bool forward_tma_applicable(const float *x, const float *y, int64_t n_out, int64_t batch) {
-    const char *force = getenv("DL_FORWARD_KERNEL");
-    if (force == nullptr || force[0] != 's') return false;  // opt-in for now
+    if (tuning(DL_TUNE_FORWARD_KERNEL) != 2) return false;  // opt-in for now
     const int64_t row_bytes = batch * 4;
     const int64_t least = 512;
     if (!(batch % 4 == 0 && row_bytes >= least && n_out >= kFwRows && aligned_to(x, 16) && aligned_to(y, 16))) return false;

@@ -29,6 +29,14 @@ static int64_t groupsum_chunks(int64_t n, int64_t batch, int64_t k) {
     return chunks;
 }
 
+// True when dl_groupsum_f32 runs the cluster kernel (no scratch) for this shape: several pieces per class and classes
+// of 64 .. 4096 rows.  DL_TUNE_GROUPSUM_KERNEL = 1 forces the workspace kernel (for A/B measurements).
+static bool groupsum_takes_cluster_kernel(int64_t n, int64_t batch, int64_t k) {
+    const int64_t m_rows = n / k;
+    return tuning(DL_TUNE_GROUPSUM_KERNEL) != 1 && groupsum_chunks(n, batch, k) > 1 && m_rows >= 64 && m_rows <= 4096 &&
+           ceil_div(batch, kGsCols) <= 65535;
+}
+
 __global__ void __launch_bounds__(kThreads)
 groupsum_kernel(const float *__restrict__ x, float *__restrict__ out, unsigned int *__restrict__ counters,
                 float *__restrict__ partial, int64_t batch, int k, int m, int chunks, float tau) {
@@ -355,10 +363,8 @@ extern "C" DL_API int dl_groupsum_f32(const float *x, float *out, void *workspac
     const int64_t chunks = groupsum_chunks(n, batch, k);
     const int64_t colblocks = ceil_div(batch, kGsCols);
     // Classes of up to 4096 rows: one cluster of 8 CTAs per (class, column block), no scratch needed.
-    // DL_GROUPSUM_KERNEL=ticket forces the workspace kernel below (for A/B measurements).
-    const char *force = getenv("DL_GROUPSUM_KERNEL");
     const int64_t m_rows = n / k;
-    if (!(force != nullptr && force[0] == 't') && chunks > 1 && m_rows >= 64 && m_rows <= 4096 && colblocks <= 65535) {
+    if (groupsum_takes_cluster_kernel(n, batch, k)) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)colblocks, (unsigned)k, kGcCluster);
         cfg.blockDim = dim3(kGcThreads);
@@ -504,8 +510,10 @@ extern "C" DL_API int dl_groupsum_f32_static(const float *x, float *out, int64_t
                                              void *stream) {
     if (int s = groupsum_check("dl_groupsum_f32_static", n, batch, k)) return s;
     if (batch == 0) return DL_OK;
+    // Shapes that dl_groupsum_f32 sends to its cluster kernel use no scratch at all: no limit applies to them.
+    const bool uses_scratch = !groupsum_takes_cluster_kernel(n, batch, k);
     const size_t need = dl_groupsum_workspace_bytes(n, batch, k);
-    DL_REQUIRE(need <= kStaticScratchBytes, DL_ERR_TOO_LARGE,
+    DL_REQUIRE(!uses_scratch || need <= kStaticScratchBytes, DL_ERR_TOO_LARGE,
                "dl_groupsum_f32_static: this shape needs %zu bytes of scratch, the built-in array holds %zu; "
                "use dl_groupsum_f32 with a workspace of your own",
                need, (size_t)kStaticScratchBytes);
@@ -513,7 +521,7 @@ extern "C" DL_API int dl_groupsum_f32_static(const float *x, float *out, int64_t
     if (int s = static_scratch(&scratch)) return s;
     // The array keeps whatever the previous call left.  The partial sums are overwritten before they are
     // read; the counters must start at zero, so they are cleared on the caller's stream first.
-    if (cudaMemsetAsync(scratch, 0, kGsCounterBytes, as_stream(stream)) != cudaSuccess)
+    if (uses_scratch && cudaMemsetAsync(scratch, 0, kGsCounterBytes, as_stream(stream)) != cudaSuccess)
         return launch_status("dl_groupsum_f32_static (clearing the counters)");
     return dl_groupsum_f32(x, out, scratch, n, batch, k, tau, stream);
 }

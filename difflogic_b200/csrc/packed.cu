@@ -338,9 +338,8 @@ extern "C" DL_API int dl_eval_packed(const void *x, const int64_t *a, const int6
     const int64_t row_bytes = words * (bit_count / 8);
     cudaStream_t st = as_stream(stream);
     auto fits = [&](int64_t sz) { return row_bytes % sz == 0 && aligned_to(x, sz) && aligned_to(y, sz); };
-    // DL_EVAL_KERNEL=plain forces the register-staged kernel (for A/B measurements)
-    const char *force = getenv("DL_EVAL_KERNEL");
-    const bool plain_only = force != nullptr && force[0] == 'p';
+    // DL_TUNE_EVAL_KERNEL = 1 forces the register-staged kernel (for A/B measurements)
+    const bool plain_only = tuning(DL_TUNE_EVAL_KERNEL) == 1;
     if (!plain_only && eval_tma_applicable(x, y, row_bytes, n_out)) return launch_eval_tma(x, a, b, gate, y, n_in, n_out, row_bytes, st);
     if (fits(16)) return launch_eval<uint4>(x, a, b, gate, y, n_out, row_bytes, st);
     if (fits(8)) return launch_eval<unsigned long long>(x, a, b, gate, y, n_out, row_bytes, st);
@@ -395,10 +394,9 @@ extern "C" DL_API int dl_groupbitsum(const void *x, int32_t *out, int64_t n, int
     DL_REQUIRE(out && (x || n == 0), DL_ERR_INVALID_ARG, "dl_groupbitsum: null pointer");
     const int64_t row_bytes = words * (bit_count / 8);
     cudaStream_t st = as_stream(stream);
-    // DL_GROUPBITSUM_KERNEL=plain / staged forces one of the two kernels (for A/B measurements)
-    const char *force = getenv("DL_GROUPBITSUM_KERNEL");
-    const bool plain_only = force != nullptr && force[0] == 'p';
-    const bool staged_only = force != nullptr && force[0] == 's';
+    // DL_TUNE_GROUPBITSUM_KERNEL = 1 (plain) / 2 (staged) forces one of the two kernels (for A/B measurements)
+    const bool plain_only = tuning(DL_TUNE_GROUPBITSUM_KERNEL) == 1;
+    const bool staged_only = tuning(DL_TUNE_GROUPBITSUM_KERNEL) == 2;
     // The staged kernel splits a class's rows over several units when (column blocks x classes) alone cannot fill
     // the machine; a split costs a plane expansion and global atomics per unit, which only pays while a unit still
     // streams a few hundred rows.  Shorter pieces go to the register kernel, which splits rows inside a CTA.

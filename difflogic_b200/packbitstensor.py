@@ -10,7 +10,8 @@ as the reference does.  `group_sum(k)` -- what GroupSum calls -- hands the packe
 layers and the bit-sum to ONE kernel when the network fits it (ops.eval_net_packed: activations stay
 in shared memory), and otherwise falls back to layer by layer.  Both give identical counts; the
 in-place semantics of the reference (the layer returns the same object, `.t` then holds the layer's
-output) are kept.  The single-kernel path is opt-in (DL_FUSED_EVAL=1 in the environment): on B200 it is bound by
+output) are kept.  The single-kernel path is opt-in (module switch FUSED_NET; DL_FUSED_EVAL=1 in the environment
+when the module is imported): on B200 it is bound by
 shared-memory bank conflicts of the random 8-byte gathers (measured 0.9 gates per clock and SM) and is slower
 than the layer-by-layer path, which already runs at 80-90 % of the HBM copy bandwidth.
 """
@@ -20,6 +21,11 @@ import numpy as np
 import torch
 
 from . import ops
+
+
+# Module switches, read from the environment once at import (set the attributes to change them afterwards).
+FUSED_NET = os.environ.get("DL_FUSED_EVAL", "0") == "1"                # all layers + bit-sum in ONE kernel (opt-in)
+FUSED_LAST_LAYER = os.environ.get("DL_FUSED_LAST_LAYER", "1") != "0"   # last layer + bit-sum in one kernel
 
 
 class PackBitsTensor:
@@ -86,13 +92,13 @@ class PackBitsTensor:
 
     def group_sum(self, k):
         assert torch.device(self.device).type == 'cuda', self.device
-        if self._pending and os.environ.get("DL_FUSED_EVAL", "0") == "1":
+        if self._pending and FUSED_NET:
             widths = [self._t.shape[0]] + [layer.out_dim for layer, _ in self._pending]
             row_bytes = self._t.shape[1] * self._t.element_size()
             if ops.fused_net_fits(widths, row_bytes):
                 metas = [layer._packed_descriptors(gate) for layer, gate in self._pending]
                 return ops.eval_net_packed(self._t, metas, widths, self.pad_len, k)
-        if self._pending and os.environ.get("DL_FUSED_LAST_LAYER", "1") != "0":
+        if self._pending and FUSED_LAST_LAYER:
             # all layers but the last run now; the last one is counted as it is computed, its output never stored
             (layer, gate) = self._pending.pop()
             self._materialize()

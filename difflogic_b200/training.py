@@ -5,9 +5,10 @@ The reference has no multi-GPU code; its step is `loss_fn(model(x), y) -> zero_g
 optimizer.step` (experiments/main.py:174-181).  `TrainStep` runs exactly that.  When a process
 group is given, every rank holds a full replica of the weights and connection indices, works on
 its own shard of the batch, and only the `[out_dim, 16]` weight gradients are averaged over the
-ranks (NCCL all-reduce on a side stream, launched as soon as the gradients of a bucket of layers
-have been written by their backward_w, so that it overlaps the rest of the backward pass).
-Nothing else crosses GPUs.
+ranks: by FlatAdam's peer-memory exchange (two small kernels per layer, launched on a stream of
+their own as soon as the layer's backward_w is in the queue) or by NCCL all-reduces on a side
+stream, launched as soon as the gradients of a bucket of layers have been written; either way
+the exchange overlaps the rest of the backward pass.  Nothing else crosses GPUs.
 
 `capture()` records the whole step (H2D staging excluded) in one CUDA graph: the model's kernels
 launch on torch's current stream, allocate nothing themselves and never synchronise, so a step of
@@ -52,7 +53,7 @@ class TrainStep:
         self._bucket_slices = []   # flat gradient slice of each bucket
         self._bucket_sizes = []    # parameters per bucket
         self._pending = []
-        # FlatAdam.enable_exchange(): gradients are averaged inside the optimizer's own kernel, nothing to do here
+        # FlatAdam.enable_exchange(): the optimizer launches the exchange itself, from the layers' backward
         self._exchange_in_optimizer = bool(getattr(optimizer, "exchange_enabled", False))
         self._body = self._head = self._pre = self._last = None
         self._unit_grad = None     # gradient of the loss w.r.t. itself, made once (autograd would fill a new one per step)
@@ -247,6 +248,9 @@ class TrainStep:
             torch.cuda.synchronize()
         self._graph = None
         self._static_loss = None
+        if self._exchange_in_optimizer and hasattr(self.optimizer, "close"):
+            self.optimizer.close()   # unmaps the peers' buffers; the parameters move back to ordinary memory
+            self._exchange_in_optimizer = False
 
 
 def shard_range(n_samples, rank, world_size, multiple=1):

@@ -60,6 +60,23 @@ enum { DL_LAUNCH_PLAIN = 0, DL_LAUNCH_OVERLAP_SETUP = 1 };
 DL_API int dl_version(void);
 DL_API const char *dl_last_error_string(void);
 
+/* Kernel-choice switches for A/B measurements; 0 = the library chooses (the default).  Process-wide.  Their initial
+ * values come from the environment once, when the library is loaded (DL_PDL=0, DL_EVAL_KERNEL=plain,
+ * DL_EVAL_SHAPE=wide|square, DL_GROUPBITSUM_KERNEL=plain|staged, DL_GROUPSUM_KERNEL=ticket, DL_FUSED_CLUSTER=2|4|8,
+ * DL_FORWARD_KERNEL=plain|staged); no entry point reads the environment afterwards.  No counterpart in the reference. */
+enum {
+    DL_TUNE_NO_PDL = 0,             /* 1: never launch with programmatic stream serialisation                    */
+    DL_TUNE_EVAL_KERNEL = 1,        /* 1: dl_eval_packed always takes the register-staged kernel                 */
+    DL_TUNE_EVAL_SHAPE = 2,         /* staged eval kernel: 1 = 8 neurons x 3 stages, 2 = 16 neurons x 2 stages   */
+    DL_TUNE_GROUPBITSUM_KERNEL = 3, /* 1: register kernel, 2: staged kernel                                      */
+    DL_TUNE_GROUPSUM_KERNEL = 4,    /* 1: dl_groupsum_f32 always takes the workspace (ticket) kernel             */
+    DL_TUNE_FUSED_CLUSTER = 5,      /* dl_eval_groupbitsum: CTAs per class, 2, 4 or 8                            */
+    DL_TUNE_FORWARD_KERNEL = 6,     /* dl_forward_f32: 1 = register kernel, 2 = staged (bulk-copy) kernel        */
+    DL_TUNE_COUNT = 7
+};
+DL_API int dl_set_tuning(int key, int value);
+DL_API int dl_get_tuning(int key);
+
 /* Kernels that stage data with asynchronous copies poll their barriers a bounded number of times
  * instead of waiting forever.  Returns 1 if such a wait ever ran out on the current device (the
  * launch it happened in wrote incomplete output), 0 if not, negative on a CUDA error.  This call
@@ -230,7 +247,9 @@ DL_API int dl_groupsum_backward_f32(const float *grad_out, float *grad_x, int64_
  * scratch lives in a device array inside the library: dl_groupsum_static_limit_bytes() bytes (256 KiB)
  * per GPU, held from the first use of the library on that GPU until the process exits.  The call
  * allocates and frees nothing.  Limits and rules:
- *   - shapes with dl_groupsum_workspace_bytes(n, batch, k) above the limit get DL_ERR_TOO_LARGE;
+ *   - shapes that need more scratch than the limit (dl_groupsum_workspace_bytes(n, batch, k)) get
+ *     DL_ERR_TOO_LARGE; shapes that dl_groupsum_f32 computes without scratch (several pieces per class and
+ *     classes of 64 .. 4096 rows) are never refused;
  *   - the first call on a device looks up the array's device address (with that device current);
  *     make that first call outside any stream capture;
  *   - every call on a GPU uses the same array: calls that may overlap on the GPU (different
@@ -305,36 +324,47 @@ DL_API int dl_adam_step_f32(float *param, const float *grad, float *exp_avg, flo
 DL_API int dl_prefetch_l2(const void *ptr, size_t bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------------
- * Batch-sharded training: gradient exchange and Adam in one kernel over peer memory.
- * No counterpart in the reference (it has no multi-GPU code); it takes the place of an NCCL
- * all-reduce of the [out_dim,16] gradients followed by dl_adam_step_f32 on every rank.
+ * Batch-sharded training: gradient exchange and Adam over peer memory, bucket by bucket.
+ * No counterpart in the reference (it has no multi-GPU code); the two kernels take the place of an
+ * NCCL all-reduce of the [out_dim,16] gradients followed by dl_adam_step_f32 on every rank.
  *
  * Set-up (these DO allocate, once): every rank allocates its flat parameter buffer, flat gradient
- * buffer and 256 bytes of flag words with dl_comm_alloc, exports them with dl_comm_export (64-byte
- * handles, to be passed to the other processes of the machine by any means) and maps its peers'
- * with dl_comm_import.
+ * buffer and dl_exchange_flag_bytes() bytes of flag words with dl_comm_alloc (zero-filled), exports
+ * them with dl_comm_export (64-byte handles, to be passed to the other processes of the machine by
+ * any means) and maps its peers' with dl_comm_import; dl_comm_close / dl_comm_free undo that.
  *
- * Per step: dl_adam_exchange_step_f32 gets HOST arrays of `world` device pointers (index = rank,
- * own entry = own buffers).  Rank r waits until all ranks' gradients are complete, averages slice r
- * of all ranks' gradients (peer loads), applies Adam to slice r with its moments (exp_avg,
- * exp_avg_sq hold ceil(n/4/world)*4 floats), writes the new slice into its own parameter buffer, waits
- * until all ranks have done the same and fetches their slices.  n: floats per buffer, a multiple of 4.
- * state: sixteen int32 on the device, zero at first: {steps done, ticket, error, ticket} followed by six
- * 64-bit nanosecond time stamps of the latest step (%globaltimer of this GPU: kernel entered, all ranks'
- * gradients seen complete, this rank's slice done, all ranks' slices seen complete, first block's elements
- * stored, kernel done); error
- * becomes 1 when a wait for a peer ran out of its poll limit (the step then used stale data).
- * All ranks must call it the same number of times; the kernels of one step must be able to run at
- * the same time, i.e. one rank per GPU.
+ * Per step and bucket -- a bucket is the range [offset, offset + count) of the flat buffers (floats,
+ * multiples of 4), e.g. one layer's weights, numbered 0 .. 31 -- two launches, typically on a stream of
+ * their own as soon as the bucket's gradients are complete, beside the rest of the backward pass:
+ *   dl_exchange_reduce_adam_f32: tells every peer that this rank's gradients of the bucket are
+ *     complete, waits until all peers have said so, averages slice `rank` of the bucket over all ranks'
+ *     gradient buffers (peer loads), applies Adam to that slice (exp_avg / exp_avg_sq: buffers of the
+ *     flat layout, of which every rank touches only its slices) and writes the new parameters into its
+ *     own parameter buffer; then tells the peers that its slice is complete;
+ *   dl_exchange_gather_f32: waits until all ranks' slices are complete and fetches the other ranks'
+ *     slices (peer loads) into this rank's parameter buffer; advances the bucket's step count.
+ * The pointer arguments are HOST arrays of `world` device pointers (index = rank, own entry = own
+ * buffers).  state: sixteen int32 on the device PER BUCKET, zero at first: {steps done, ticket, error,
+ * ticket} and six 64-bit nanosecond time stamps of the latest step (%globaltimer: reduce kernel
+ * entered, all ranks' gradients seen, own slice complete, gather kernel entered, all ranks' slices
+ * seen, gather done).  Waits on peers poll at most poll_limit times (0: the default of 2^22, about a
+ * second); when a wait runs out the kernel sets `error` to 1, leaves parameters, moments and step
+ * count untouched and returns -- the run cannot continue, but nothing hangs and nothing is corrupted.
+ * All ranks must launch the same buckets in the same order, one rank per GPU (the kernels of one
+ * step must be able to run at the same time on their GPUs).
  * ---------------------------------------------------------------------------------------- */
 DL_API int dl_comm_alloc(size_t bytes, void **ptr);
 DL_API int dl_comm_free(void *ptr);
 DL_API int dl_comm_export(void *ptr, unsigned char *handle);
 DL_API int dl_comm_import(const unsigned char *handle, void **ptr);
 DL_API int dl_comm_close(void *ptr);
-DL_API int dl_adam_exchange_step_f32(void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs, int rank,
-                                     int world, float *exp_avg, float *exp_avg_sq, int64_t n, float lr, float beta1,
-                                     float beta2, float eps, int32_t *state, void *stream);
+DL_API size_t dl_exchange_flag_bytes(void);
+DL_API int dl_exchange_reduce_adam_f32(void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs, int rank,
+                                       int world, float *exp_avg, float *exp_avg_sq, int64_t offset, int64_t count, int bucket,
+                                       float lr, float beta1, float beta2, float eps, int32_t *state, uint32_t poll_limit,
+                                       void *stream);
+DL_API int dl_exchange_gather_f32(void *const *param_ptrs, void *const *flag_ptrs, int rank, int world, int64_t offset,
+                                  int64_t count, int bucket, int32_t *state, uint32_t poll_limit, void *stream);
 
 #ifdef __cplusplus
 }

@@ -5,7 +5,6 @@ import os
 import torch
 
 import difflogic_b200 as D
-from difflogic_b200 import report_configs as R
 from difflogic_b200.training import TrainStep
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -20,24 +19,22 @@ def _bench():
 
 def test_algorithmic_bytes_of_the_baseline_configurations():
     # per-GPU figures of the baseline's table: config 2, 4 and 5 training steps, config 3 and 5 packed inference
-    assert R.train_bytes_per_step([784] + [16000] * 5, 128, 10) == 343_853_088
-    dims4, k4, _, batch4, _, _ = R.CONFIGS["c4"]
-    dims5, k5, _, batch5, _, _ = R.CONFIGS["c5"]
-    assert R.train_bytes_per_step(dims4, batch4, k4) == 3_810_766_872
-    assert R.train_bytes_per_step(dims5, batch5, k5) == 22_021_697_624
-    assert R.eval_bytes_per_sample([784] + [8000] * 4, 10, False) == 8138
-    assert R.eval_bytes_per_sample([784] + [8000] * 4, 10, True) == 6138
-    assert R.eval_bytes_per_sample(dims5, k5, False) == 192_040
-
-
-def test_bench_and_report_use_the_same_accounting():
     bench = _bench()
     total, per_kernel = bench.train_bytes_per_step(bench.TRAIN_DIMS, bench.TRAIN_BATCH, bench.TRAIN_K)
-    assert total == R.train_bytes_per_step(bench.TRAIN_DIMS, bench.TRAIN_BATCH, bench.TRAIN_K)
+    assert total == 343_853_088
     assert per_kernel["forward"] == 17_664_000 and per_kernel["backward_x"] == 26_240_008
-    for fused in (False, True):
-        assert bench.eval_bytes_per_sample(bench.EVAL_DIMS, bench.EVAL_K, fused) == R.eval_bytes_per_sample(
-            bench.EVAL_DIMS, bench.EVAL_K, fused)
+    c4, c5 = bench.CONFIGS["c4"], bench.CONFIGS["c5"]
+    assert bench.train_bytes_per_step(c4["dims"], c4["batch"], c4["k"])[0] == 3_810_766_872
+    assert bench.train_bytes_per_step(c5["dims"], c5["batch"], c5["k"])[0] == 22_021_697_624
+    assert bench.eval_bytes_per_sample(bench.EVAL_DIMS, bench.EVAL_K, False) == 8138
+    assert bench.eval_bytes_per_sample(bench.EVAL_DIMS, bench.EVAL_K, True) == 6138
+    assert bench.eval_bytes_per_sample(c5["dims"], c5["k"], False) == 192_040
+
+
+def test_both_bench_arms_name_the_same_configuration():
+    bench = _bench()
+    assert bench.train_config(4) == bench.train_config(4) and bench.train_config(1)["global_batch"] == 128
+    assert bench.train_config(8)["global_batch"] == 1024
 
 
 def test_train_step_fuses_the_head_only_for_a_default_cross_entropy():

@@ -1,0 +1,89 @@
+"""The bounded waits of the peer-memory exchange kernels, made to run out on ONE GPU.
+
+Rank 0 of a world of two is driven through the C ABI; its "peer" is a second set of buffers in the same process
+(same GPU, ordinary memory) that no kernel ever drives, so the flags rank 0 waits for are never raised.  With a
+small poll limit the kernels must give up, report through the error word of the bucket's state, and leave
+parameters, moments and step count exactly as they were.  Then the test plays the peer by hand (raises its flags)
+and the next call must work.  Nothing here faults or waits without a limit.
+"""
+import ctypes
+
+import pytest
+import torch
+
+from difflogic_b200 import _native as N
+
+pytestmark = pytest.mark.gpu
+
+MAX_RANKS = 16
+
+
+def _flag(bucket, peer, which):
+    return (bucket * MAX_RANKS + peer) * 2 + which
+
+
+def _ptrs(*tensors):
+    return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
+@pytest.mark.parametrize("bucket", [0, 3])
+def test_exchange_wait_runs_out_and_leaves_everything_untouched(bucket):
+    lib = N.lib()
+    n, lr, beta1, beta2, eps = 4096, 0.01, 0.9, 0.999, 1e-8
+    g = torch.Generator().manual_seed(17 + bucket)
+    own_p, peer_p = torch.randn(n, generator=g).cuda(), torch.randn(n, generator=g).cuda()
+    own_g, peer_g = torch.randn(n, generator=g).cuda(), torch.randn(n, generator=g).cuda()
+    words = lib.dl_exchange_flag_bytes() // 4
+    own_f = torch.zeros(words, dtype=torch.int32, device="cuda")
+    peer_f = torch.zeros(words, dtype=torch.int32, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    state = torch.zeros(16, dtype=torch.int32, device="cuda")
+    params, grads, flags = _ptrs(own_p, peer_p), _ptrs(own_g, peer_g), _ptrs(own_f, peer_f)
+    stream = torch.cuda.current_stream().cuda_stream
+    before = own_p.clone()
+
+    def one_step(limit):
+        N.check(lib.dl_exchange_reduce_adam_f32(params, grads, flags, 0, 2, m.data_ptr(), v.data_ptr(), 0, n, bucket, lr, beta1,
+                                                beta2, eps, state.data_ptr(), limit, stream))
+        N.check(lib.dl_exchange_gather_f32(params, flags, 0, 2, 0, n, bucket, state.data_ptr(), limit, stream))
+        torch.cuda.synchronize()
+
+    one_step(4096)   # nobody raises the peer's flags: both waits run out
+    s = state.tolist()
+    assert s[2] == 1, "the error word must be set"
+    assert s[0] == 0 and s[1] == 0 and s[3] == 0, "step count untouched, tickets re-armed"
+    assert torch.equal(own_p, before) and not m.any() and not v.any()
+    # rank 0 did announce its gradients to itself and to the peer, and never announced a finished slice
+    assert int(own_f[_flag(bucket, 0, 0)]) == 1 and int(peer_f[_flag(bucket, 0, 0)]) == 1
+    assert int(own_f[_flag(bucket, 0, 1)]) == 0 and int(peer_f[_flag(bucket, 0, 1)]) == 0
+
+    # the peer "arrives": its gradients and its slice (the second half of peer_p) are declared complete
+    own_f[_flag(bucket, 1, 0)] = 1
+    own_f[_flag(bucket, 1, 1)] = 1
+    state[2] = 0
+    one_step(0)      # default limit; every flag is there already
+    s = state.tolist()
+    assert s[2] == 0 and s[0] == 1 and s[1] == 0 and s[3] == 0
+    half = n // 2
+    ref = before[:half].cpu().clone().requires_grad_(True)
+    ref.grad = ((own_g[:half] + peer_g[:half]) * 0.5).cpu()
+    torch.optim.Adam([ref], lr=lr, betas=(beta1, beta2), eps=eps).step()
+    assert torch.allclose(own_p[:half].cpu(), ref.detach(), rtol=1e-6, atol=1e-7)   # own slice: Adam on the mean gradient
+    assert torch.equal(own_p[half:], peer_p[half:])                                 # other slice: fetched from the peer
+    assert m[half:].abs().max().item() == 0.0                                       # moments of the peer's slice untouched
+
+
+def test_exchange_entry_points_validate_their_arguments():
+    lib = N.lib()
+    t = torch.zeros(64, device="cuda")
+    f = torch.zeros(lib.dl_exchange_flag_bytes() // 4, dtype=torch.int32, device="cuda")
+    st = torch.zeros(16, dtype=torch.int32, device="cuda")
+    one = _ptrs(t)
+    flags = _ptrs(f)
+    args = (t.data_ptr(), t.data_ptr())
+    assert lib.dl_exchange_reduce_adam_f32(one, one, flags, 1, 1, *args, 0, 64, 0, 0.01, 0.9, 0.999, 1e-8, st.data_ptr(), 0, None) \
+        == N.DL_ERR_INVALID_ARG                                   # rank outside the world
+    assert lib.dl_exchange_reduce_adam_f32(one, one, flags, 0, 1, *args, 0, 62, 0, 0.01, 0.9, 0.999, 1e-8, st.data_ptr(), 0, None) \
+        == N.DL_ERR_INVALID_ARG                                   # count not a multiple of 4
+    assert lib.dl_exchange_gather_f32(one, flags, 0, 1, 0, 64, 32, st.data_ptr(), 0, None) == N.DL_ERR_INVALID_ARG   # bucket
+    assert lib.dl_exchange_gather_f32(one, flags, 0, 17, 0, 64, 0, st.data_ptr(), 0, None) == N.DL_ERR_INVALID_ARG   # world

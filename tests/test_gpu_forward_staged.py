@@ -30,10 +30,10 @@ def test_staged_forward_equals_plain_forward_and_oracle(shape, mode, monkeypatch
         ref, w_in, w_mode = O.layer_forward(x, a, b, w, training=False), w, ops.W_ARGMAX
     xd = x.t().contiguous().cuda()
     args = (xd, a.cuda(), b.cuda(), w_in.cuda(), w_mode, True)
-    monkeypatch.setenv("DL_FORWARD_KERNEL", "staged")
-    y_staged, c_staged = ops.logic_forward(*args)
-    monkeypatch.setenv("DL_FORWARD_KERNEL", "plain")
-    y_plain, c_plain = ops.logic_forward(*args)
+    with N.tuning(N.TUNE_FORWARD_KERNEL, 2):
+        y_staged, c_staged = ops.logic_forward(*args)
+    with N.tuning(N.TUNE_FORWARD_KERNEL, 1):
+        y_plain, c_plain = ops.logic_forward(*args)
     assert torch.equal(y_staged, y_plain) and torch.equal(c_staged, c_plain)     # same arithmetic, to the bit
     assert_forward_close(y_staged.t().cpu(), ref, "staged forward")
     assert N.lib().dl_async_error() == 0
@@ -41,12 +41,10 @@ def test_staged_forward_equals_plain_forward_and_oracle(shape, mode, monkeypatch
 
 def test_default_and_plain_agree(monkeypatch):
     """Whatever kernel the library picks by default gives the same numbers as the register kernel."""
-    monkeypatch.delenv("DL_FORWARD_KERNEL", raising=False)
     a, b, w = random_layer(64, 96, seed=1)
     for batch in (128, 256):
         x = torch.rand(64, batch, device='cuda')
         y, _ = ops.logic_forward(x, a.cuda(), b.cuda(), w.cuda(), ops.W_LOGITS, True)
-        monkeypatch.setenv("DL_FORWARD_KERNEL", "plain")
-        y2, _ = ops.logic_forward(x, a.cuda(), b.cuda(), w.cuda(), ops.W_LOGITS, True)
-        monkeypatch.delenv("DL_FORWARD_KERNEL")
+        with N.tuning(N.TUNE_FORWARD_KERNEL, 1):
+            y2, _ = ops.logic_forward(x, a.cuda(), b.cuda(), w.cuda(), ops.W_LOGITS, True)
         assert torch.equal(y, y2)

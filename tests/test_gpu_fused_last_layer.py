@@ -77,14 +77,14 @@ def test_model_uses_fused_last_layer_and_matches_layerwise(monkeypatch):
         before = N.launch_count()
         fused = model(D.PackBitsTensor(x.cuda(), bit_count=64))
         fused_launches = N.launch_count() - before
-        monkeypatch.setenv("DL_FUSED_LAST_LAYER", "0")
+        monkeypatch.setattr(D.packbitstensor, "FUSED_LAST_LAYER", False)
         before = N.launch_count()
         layerwise = model(D.PackBitsTensor(x.cuda(), bit_count=64))
         layerwise_launches = N.launch_count() - before
     assert np.array_equal(fused.cpu().numpy(), ref) and torch.equal(fused, layerwise)
     assert fused_launches == layerwise_launches - 1   # pack, two layers, fused tail  vs  pack, three layers, bit-sum
     # the object stays usable: reading .t afterwards still gives the last layer's output
-    monkeypatch.delenv("DL_FUSED_LAST_LAYER")
+    monkeypatch.setattr(D.packbitstensor, "FUSED_LAST_LAYER", True)
     p = D.PackBitsTensor(x.cuda(), bit_count=64)
     layers = [m for m in model if isinstance(m, D.LogicLayer)]
     with torch.no_grad():

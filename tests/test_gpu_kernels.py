@@ -170,7 +170,7 @@ def test_eval_packed_matches_oracle(bits, shape):
 
 
 def test_eval_packed_staged_and_plain_kernels_agree(monkeypatch):
-    """Rows of 8 KB: the bulk-copy staged kernel is chosen; DL_EVAL_KERNEL=plain forces the register kernel."""
+    """Rows of 8 KB: the bulk-copy staged kernel is chosen; the switch DL_TUNE_EVAL_KERNEL forces the register kernel."""
     n_in, n_out, words = 500, 777, 1024 + 6
     g = torch.Generator().manual_seed(1)
     x = torch.randint(-2**62, 2**62, (n_in, words), dtype=torch.int64, generator=g)
@@ -179,8 +179,8 @@ def test_eval_packed_staged_and_plain_kernels_agree(monkeypatch):
     gate = torch.randint(0, 16, (n_out,), generator=g).to(torch.uint8)
     ref = O.eval_packed(x.numpy(), a.numpy(), b.numpy(), gate.numpy())
     staged = ops.eval_packed(_dev(x), _dev(a), _dev(b), _dev(gate))
-    monkeypatch.setenv("DL_EVAL_KERNEL", "plain")
-    plain = ops.eval_packed(_dev(x), _dev(a), _dev(b), _dev(gate))
+    with N.tuning(N.TUNE_EVAL_KERNEL, 1):
+        plain = ops.eval_packed(_dev(x), _dev(a), _dev(b), _dev(gate))
     assert np.array_equal(staged.cpu().numpy(), ref) and np.array_equal(plain.cpu().numpy(), ref)
     assert N.lib().dl_async_error() == 0
 
@@ -213,15 +213,15 @@ def test_groupbitsum_matches_oracle(bits, case):
 
 
 def test_groupbitsum_staged_and_plain_kernels_agree(monkeypatch):
-    """Rows of 2 KB: the bulk-copy staged kernel is chosen; DL_GROUPBITSUM_KERNEL=plain forces the register kernel."""
+    """Rows of 2 KB: the bulk-copy staged kernel is chosen; the switch DL_TUNE_GROUPBITSUM_KERNEL forces the register kernel."""
     n, k, batch = 3000, 10, 16384 - 5
     t = torch.rand(n, batch, generator=torch.Generator().manual_seed(12)) < 0.5
     words, pad = O.pack_bits(t.numpy(), 64)
     ref = O.group_bit_sum(words, pad, k)
     xd = _dev(torch.from_numpy(words))
     staged = ops.groupbitsum(xd, pad, k)
-    monkeypatch.setenv("DL_GROUPBITSUM_KERNEL", "plain")
-    plain = ops.groupbitsum(xd, pad, k)
+    with N.tuning(N.TUNE_GROUPBITSUM_KERNEL, 1):
+        plain = ops.groupbitsum(xd, pad, k)
     assert np.array_equal(staged.cpu().numpy(), ref) and np.array_equal(plain.cpu().numpy(), ref)
     assert N.lib().dl_async_error() == 0
 

@@ -111,3 +111,60 @@ def test_deep_tabular_net_trains_and_packs():
         fl = model(x.float())
         counts = model(D.PackBitsTensor(x, bit_count=64))
     assert torch.equal(torch.round(fl * 20.0).to(torch.int32), counts)
+
+
+def test_packed_inference_at_the_benchmark_size_is_bit_exact():
+    """784 -> 4 x 8000 -> GroupSum(10) on 2^20 samples in int64 words (the packed benchmark, staged kernels, last layer
+    fused with the class count): every one of the 2^20 x 10 counts equals the C oracle's."""
+    import difflogic_b200 as D
+    from tests.helpers import build_model
+    torch.manual_seed(0)
+    dims, k = [784] + [8000] * 4, 10
+    net = O.OracleNet.build(dims, k, 10.0)
+    model = build_model(dims, k, 10.0, net.weights, net.idx_a, net.idx_b)
+    model.eval()
+    samples = 1 << 20
+    g = torch.Generator().manual_seed(11)
+    x = torch.empty(samples, dims[0], dtype=torch.bool)
+    for s in range(0, samples, 1 << 16):
+        x[s:s + (1 << 16)] = torch.rand(1 << 16, dims[0], generator=g) < 0.19
+    with torch.no_grad():
+        counts = model(D.PackBitsTensor(x.cuda(), bit_count=64))
+    ref = O.c_packed_net_counts(x.numpy(), net.idx_a, net.idx_b, net.gate_ids(), k, threads=torch.get_num_threads())
+    assert counts.shape == (samples, k)
+    assert np.array_equal(counts.cpu().numpy(), np.asarray(ref))
+    from difflogic_b200 import _native as N
+    assert N.lib().dl_async_error() == 0
+
+
+def test_captured_training_step_at_the_benchmark_size_against_oracle():
+    """784 -> 5 x 16000 -> GroupSum(10, tau=30), batch 128, through a CUDA-graph-captured TrainStep (fused head, Adam
+    inside backward_w): loss, weight gradients (read back from Adam's first moments of the first step) and updated
+    weights against the oracle's step."""
+    from difflogic_b200.optim import FlatAdam
+    from difflogic_b200.training import TrainStep
+    from tests.helpers import build_model, logic_layers
+    torch.manual_seed(0)
+    dims, k, tau, batch, lr = [784] + [16000] * 5, 10, 30.0, 128, 0.01
+    net = O.OracleNet.build(dims, k, tau)
+    model = build_model(dims, k, tau, net.weights, net.idx_a, net.idx_b)
+    model.train()
+    g = torch.Generator().manual_seed(21)
+    x = (torch.rand(batch, dims[0], generator=g) < 0.19).float()
+    y = torch.randint(0, k, (batch,), generator=g)
+    opt = FlatAdam(model.parameters(), lr=lr)
+    step = TrainStep(model, opt, torch.nn.CrossEntropyLoss())
+    step.capture(x.cuda(), y.cuda(), warmup=0)          # nothing runs before the first replay
+    loss = step(x.cuda(), y.cuda())
+    torch.cuda.synchronize()
+    start = [w.detach().clone() for w in net.weights]
+    ref_loss, _, ref_grads = net.train_step(x, y, lr=lr)
+    assert abs(float(loss) - float(ref_loss)) <= 1e-5 * abs(float(ref_loss))
+    for p, ref in zip(opt._params, ref_grads):
+        off, cnt = opt._slices[p]
+        assert_grad_close((opt.exp_avg[off:off + cnt] / 0.1).view_as(p), ref, "weight gradient via the first moment")
+    for layer, w0, gr in zip(logic_layers(model), start, ref_grads):
+        want = w0 - lr * gr / (gr.abs() + 1e-8)          # first Adam step from zero moments
+        sure = gr.abs() > 1e-3 * gr.abs().max()          # where the sign of the gradient is beyond doubt
+        assert float((layer.weights.detach().cpu() - want)[sure].abs().max()) <= 2e-3 * lr
+    step.close()

@@ -341,9 +341,9 @@ def test_whole_network_packed_kernel_equals_layer_by_layer(case, monkeypatch):
     row_bytes = -(-batch // bits) * bits // 8
     assert ops.fused_net_fits(dims, row_bytes) == (row_bytes % 8 == 0)
     with torch.no_grad():
-        monkeypatch.setenv("DL_FUSED_EVAL", "1")
+        monkeypatch.setattr(D.packbitstensor, "FUSED_NET", True)
         fused = model(D.PackBitsTensor(x.cuda(), bit_count=bits))
-        monkeypatch.setenv("DL_FUSED_EVAL", "0")
+        monkeypatch.setattr(D.packbitstensor, "FUSED_NET", False)
         layerwise = model(D.PackBitsTensor(x.cuda(), bit_count=bits))
     assert torch.equal(fused, layerwise)
     if batch <= 1000:

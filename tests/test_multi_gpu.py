@@ -1,6 +1,7 @@
-"""Batch-sharded training on more than one GPU: the peer-memory exchange kernel against the NCCL all-reduce path.
+"""Batch-sharded training on more than one GPU: the peer-memory exchange (two kernels per layer, launched beside the
+backward pass) against the NCCL all-reduce path and against the oracle's step on the whole batch.
 Runs child processes, one per GPU; skipped where fewer than two GPUs are visible.  The single-rank case of the
-exchange kernel (no peers) runs on one GPU."""
+exchange kernels (no peers) runs on one GPU."""
 import os
 import socket
 
@@ -47,7 +48,9 @@ def test_exchange_kernel_single_rank_equals_flat_adam(tmp_path):
                 o.step()
         for l1, l2 in zip(logic_layers(m1), logic_layers(m2)):
             assert torch.equal(l1.weights, l2.weights)
-        assert not o2.exchange_error() and int(o2.state_t[0].item()) == 4
+        assert not o2.exchange_error() and o2.state_t[:, 0].tolist() == [4] * len(logic_layers(m2))
+        o2.close()
+        assert all(l.weights.data_ptr() != 0 for l in logic_layers(m2))
     finally:
         dist.destroy_process_group()
 
@@ -76,10 +79,20 @@ def _worker(rank, world, port, out_dir):
             step = TrainStep(model, opt, process_group=dist.group.WORLD, buckets=1)
             if mode == "peer_graph":
                 step.capture(xs[0][lo:hi].cuda(), ys[0][lo:hi].cuda(), warmup=0)
-            losses = [float(step(x[lo:hi].cuda(), y[lo:hi].cuda()).item()) for x, y in zip(xs, ys)]
+            losses, first = [], None
+            for x, y in zip(xs, ys):
+                losses.append(float(step(x[lo:hi].cuda(), y[lo:hi].cuda()).item()))
+                if first is None:
+                    first = {"w": [l.weights.detach().cpu().clone() for l in logic_layers(model)]}
+                    if mode != "nccl":
+                        # first moments after one step from zero are (1 - beta1) * averaged gradient; every rank holds its slices
+                        m = opt.exp_avg.clone()
+                        dist.all_reduce(m)
+                        first["grad"] = [(m[off:off + cnt] / 0.1).view_as(p).cpu() for p in opt._params
+                                         for off, cnt in [opt._slices[p]]]
             torch.cuda.synchronize()
             results[mode] = {"loss": losses, "w": [l.weights.detach().cpu().clone() for l in logic_layers(model)],
-                             "err": opt.exchange_error()}
+                             "err": opt.exchange_error(), "first": first}
             step.close()
             dist.barrier()
         torch.save(results, os.path.join(out_dir, "rank%d.pt" % rank))
@@ -112,3 +125,32 @@ def test_peer_memory_exchange_matches_nccl_all_reduce(tmp_path):
         for w, ref in zip(res[0][mode]["w"], res[0]["nccl"]["w"]):
             assert torch.allclose(w, ref, rtol=1e-5, atol=1e-6)   # same update as all-reduce + Adam
     assert torch.allclose(torch.tensor(res[0]["peer"]["loss"]), torch.tensor(res[0]["nccl"]["loss"]), rtol=1e-5)
+
+    # against the oracle: the same three steps on the WHOLE batch (experiments/main.py:174-181) with torch's Adam
+    from tests.helpers import assert_grad_close
+    dims = [24, 160, 160, 80]
+    torch.manual_seed(11)
+    net = O.OracleNet.build(dims, 4, 3.0)
+    start = [w.detach().clone() for w in net.weights]
+    g = torch.Generator().manual_seed(3)
+    xs = [(torch.rand(64, 24, generator=g) < 0.4).float() for _ in range(3)]
+    ys = [torch.randint(0, 4, (64,), generator=g) for _ in range(3)]
+    adam = torch.optim.Adam(net.weights, lr=0.01)
+    ref_losses, ref_first_grads = [], None
+    for x, y in zip(xs, ys):
+        loss = torch.nn.functional.cross_entropy(net.forward(x, True), y)
+        adam.zero_grad()
+        loss.backward()
+        if ref_first_grads is None:
+            ref_first_grads = [w.grad.detach().clone() for w in net.weights]
+        adam.step()
+        ref_losses.append(float(loss))
+    for mode in ("peer", "peer_graph"):
+        mean_losses = [0.5 * (a + b) for a, b in zip(res[0][mode]["loss"], res[1][mode]["loss"])]   # equal shards
+        assert torch.allclose(torch.tensor(mean_losses), torch.tensor(ref_losses), rtol=1e-4), (mode, mean_losses, ref_losses)
+        for got, ref in zip(res[0][mode]["first"]["grad"], ref_first_grads):
+            assert_grad_close(got, ref, "%s: averaged gradient of the first step" % mode)
+        for w, w0, gr in zip(res[0][mode]["first"]["w"], start, ref_first_grads):
+            want = w0 - 0.01 * gr / (gr.abs() + 1e-8)       # first Adam step from zero moments
+            moved = gr.abs() > 1e-3 * gr.abs().max()        # where the sign of the gradient is beyond doubt
+            assert (w - want)[moved].abs().max().item() <= 2e-3 * 0.01
