@@ -256,12 +256,11 @@ def oracle_parity(model, opt, step, name, rank, world):
     loss = step(x.cuda(), y.cuda())
     torch.cuda.synchronize()
     losses = all_reduce_list([float(loss.item())], world, dist.ReduceOp.SUM)
-    m = opt.exp_avg.detach().clone()
-    if world > 1 and getattr(opt, "exchange_enabled", False):
-        dist.all_reduce(m)                 # every rank holds the moments of its slices only; the rest is zero
+    m = opt.full_exp_avg()                 # under the peer exchange every rank holds the moments of its slices only
     grads = [(m[off:off + cnt] / 0.1).view_as(p).cpu() for p in opt._params for off, cnt in [opt._slices[p]]]
     after = [l.weights.detach().cpu().clone() for l in logic]
     if rank != 0:
+        barrier(world)                     # rank 0 is busy on the CPU for a while: nobody starts the next step without it
         return None
     net = O.OracleNet([w.clone() for w in start], [l.indices[0].cpu() for l in logic], [l.indices[1].cpu() for l in logic], k, tau,
                       cfg["grad_factor"])
@@ -277,6 +276,7 @@ def oracle_parity(model, opt, step, name, rank, world):
     out["update_rel_err"] = worst
     out["ok"] = bool(out["loss_rel_err"] <= 1e-5 and out["grad_rel_err"] <= 1e-4 and worst <= 2e-3)
     out["tolerance"] = "loss 1e-5 relative, gradients 1e-4 of the largest entry per tensor, update 2e-3 of lr"
+    barrier(world)
     return out
 
 
@@ -306,7 +306,8 @@ def bench_train(name, args, rank, world, headline):
     group = dist.group.WORLD if world > 1 else None
     peer = world > 1 and args.exchange == "peer" and args.optimizer == "flat"
     if peer:
-        opt.enable_exchange(group, buckets=args.exchange_buckets)
+        opt.enable_exchange(group, buckets=args.exchange_buckets, announce_in_backward=args.announce_in_backward,
+                            one_pass_bytes=args.one_pass_bytes)
     loss_fn = torch.nn.CrossEntropyLoss() if args.loss == "torch" else CrossEntropyLoss()
     step = TrainStep(model, opt, loss_fn, process_group=group, world_size=world, buckets=args.buckets)
 
@@ -380,7 +381,10 @@ def bench_train(name, args, rank, world, headline):
         first = min(exchange_timing, key=lambda b: b["entered_ns"])
         out["exchange_last_step"] = {
             "buckets": len(exchange_timing), "first_bucket_entered_to_last_done_ns": last["done_ns"] - first["entered_ns"],
-            "last_bucket": {k_: v for k_, v in last.items() if k_ not in ("entered_ns", "done_ns")}}
+            "last_bucket": {k_: v for k_, v in last.items() if k_ not in ("entered_ns", "done_ns", "stamps_ns")},
+            # per bucket (parameter order): entered, all gradients seen, own slice done, all slices seen, done -- ns after
+            # the first bucket's entry
+            "timeline_ns": [[t - first["entered_ns"] for t in b_["stamps_ns"]] for b_ in exchange_timing]}
 
     if headline:
         # ---- end to end: pinned host batch -> H2D -> step -> loss read back on the host, every step
@@ -753,7 +757,8 @@ def cpu_packed_baselines(threads):
     t0 = time.perf_counter()
     compiled.forward(x[:one])
     out["compiled_single_core"] = {"value": one / (time.perf_counter() - t0), "cores": 1, "samples": one}
-    chunks = [x[s:s + one] for s in range(0, len(x), one)]
+    per = max(1 << 11, len(x) // max(threads, 1))          # one chunk per host thread
+    chunks = [x[s:s + per] for s in range(0, len(x), per)]
     with ThreadPoolExecutor(max_workers=threads) as pool:
         t0 = time.perf_counter()
         list(pool.map(compiled.forward, chunks))          # ctypes releases the interpreter lock during the call
@@ -872,6 +877,10 @@ def main():
                     help="N > 1: peer = gradient exchange + Adam over peer memory, per layer, beside the backward pass; "
                          "nccl = NCCL all-reduce")
     ap.add_argument("--exchange-buckets", type=int, default=None, help="peer exchange: buckets (default: one per layer)")
+    ap.add_argument("--announce-in-backward", action="store_true",
+                    help="peer exchange: backward_w's last block tells the peers (default: the exchange kernel does)")
+    ap.add_argument("--one-pass-bytes", type=int, default=8 << 20,
+                    help="peer exchange: one-pass form for the last bucket up to this many bytes over NVLink per rank (0: never)")
     ap.add_argument("--skip-packed", action="store_true")
     ap.add_argument("--skip-large", action="store_true", help="leave out the wide and deep configurations (`configs`)")
     ap.add_argument("--optimizer", default="flat", choices=["flat", "torch"],
@@ -970,7 +979,7 @@ def main():
                 packed["cpu_baseline"] = {
                     "value": b["compiled"]["value"], "unit": UNIT, "cores": b["compiled"]["cores"], "kind": "port",
                     "sample": "2^17 samples through the net compiled to straight-line C by CompiledLogicNet (gcc -O1, num_bits=64, "
-                              "compiled in %.1f s), 2^14-sample chunks in host threads" % b["compile_s"],
+                              "compiled in %.1f s), one chunk of the batch per host thread" % b["compile_s"],
                     "compiled_single_core": b["compiled_single_core"], "interpreter": b["interpreter"],
                     "interpreter_single_core": b["interpreter_single_core"]}
         if train["parity"] is not None and not train["parity"]["ok"]:

@@ -2,24 +2,23 @@
 //
 // Every rank (one process per GPU) keeps the flat gradient buffer and the flat parameter buffer of the network in
 // memory that its peers have mapped (CUDA IPC over NVLink).  The buffers are cut into buckets (one per layer, say);
-// as soon as a bucket's gradients are complete on a rank -- its backward_w kernel has finished, while the backward
-// pass of the layers below is still running -- that rank launches two small kernels for the bucket on a stream of
-// their own:
-//   reduce + Adam   announces "my gradients of this bucket are complete" to every peer (a flag store into the peer's
-//                   memory), waits until all peers have said so, reads ITS slice of the bucket from all ranks'
-//                   gradient buffers (16-byte loads over NVLink), averages, applies Adam with its slice of the moments
-//                   and stores the new parameters into its OWN parameter buffer; the last block to finish tells the
-//                   peers "my slice of this bucket is complete";
-//   gather          waits until all ranks have said that, and pulls the other ranks' slices of the new parameters
-//                   from their memory into its own parameter buffer.
-// Neither kernel waits for another block of its own grid, so nothing has to be resident together and the kernels
-// can share the GPU with the backward pass; what crosses NVLink is what a reduce-scatter plus an all-gather moves.
+// the last block of the backward_w kernel that completes a bucket's gradients tells every peer so (a flag store into
+// the peer's memory), and the rank launches ONE small kernel for the bucket, beside the backward pass of the layers
+// below:
+//   1. wait until all ranks have announced their gradients of the bucket;
+//   2. read ITS slice of the bucket from all ranks' gradient buffers (16-byte loads over NVLink), average, apply
+//      Adam with its slice of the moments and store the new parameters into its OWN parameter buffer; the last block
+//      to finish tells the peers "my slice of this bucket is complete";
+//   3. wait until all ranks have said that, and pull the other ranks' slices of the new parameters from their memory
+//      into its own parameter buffer.
+// The kernel waits only for OTHER GPUs (and, between its two phases, for the last block of its own small grid), never
+// for a kernel launched later on its own GPU.  What crosses NVLink is what a reduce-scatter plus an all-gather moves.
 // Only the bucket of the layer whose gradients come last is not hidden behind the backward pass.
 // Pulling instead of pushing the new parameters matters: after stores INTO peer memory a rank has to wait for their
 // system-wide visibility before it may raise its flag, and that fence measured 8 us.
 //
 // The peers are other GPUs of this machine mapped by plain peer-to-peer access; every access to their memory is an
-// ordinary ld/st instruction (no bulk copy, no TMA, no multicast).  Every wait is bounded (poll_limit polls); a kernel
+// ordinary ld/st instruction (no bulk copy, no TMA, no multicast).  Every wait is bounded (wait_limit_us microseconds); a kernel
 // whose wait runs out sets the error word of the bucket's state, changes NOTHING else (parameters, moments and step
 // count stay as they were) and returns, so a missing rank cannot hang the others and cannot corrupt the weights.
 #include <string.h>
@@ -31,7 +30,7 @@ namespace dl {
 
 constexpr int kMaxRanks = 16;
 constexpr int kMaxBuckets = 32;
-constexpr unsigned kExchangePollLimit = 1u << 22;  // default poll limit: a second or so
+constexpr unsigned kExchangeWaitUs = 20u * 1000u * 1000u;  // default limit of a wait for the peers: 20 seconds
 constexpr int kFlagBytes = kMaxBuckets * kMaxRanks * 2 * 4;
 
 struct ExchangePeers {
@@ -63,17 +62,29 @@ __device__ __forceinline__ float4 ld_peer(const float4 *p) {
 }
 
 // Called by ALL threads of a block: waits until every rank's flag (bucket, rank, which) in this rank's flag words has
-// reached `epoch`; false when a poll limit ran out.  Thread p polls rank p's flag with relaxed loads and reads it once
-// more with acquire when it has seen it; the block barrier passes the ordering on to the other threads.
-__device__ __forceinline__ bool wait_peers(const int *my_flags, int world, int bucket, int which, int epoch, unsigned limit) {
+// reached `epoch`; false when the wait took longer than `limit_us` microseconds (read off %globaltimer every 32
+// polls).  Thread p polls rank p's flag with relaxed loads and reads it once more with acquire when it has seen it;
+// the block barrier passes the ordering on to the other threads.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ bool wait_peers(const int *my_flags, int world, int bucket, int which, int epoch, unsigned limit_us) {
     bool ok = true;
     if ((int)threadIdx.x < world) {
         const int *f = my_flags + flag_index(bucket, threadIdx.x, which);
         unsigned spin = 0;
+        unsigned long long t0 = 0;
         while (ld_relaxed_sys(f) < epoch) {
-            if (++spin > limit) {
-                ok = false;
-                break;
+            if ((++spin & 31u) == 0u) {
+                const unsigned long long now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > (unsigned long long)limit_us * 1000ull) {
+                    ok = false;
+                    break;
+                }
             }
         }
         (void)ld_acquire_sys(f);
@@ -81,16 +92,22 @@ __device__ __forceinline__ bool wait_peers(const int *my_flags, int world, int b
     return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-// state of a bucket, 16 ints: [0] steps done, [1] ticket of the reduce kernel, [2] error (a wait ran out), [3] ticket
-// of the gather kernel, [4..15] six 64-bit time stamps of the latest step in nanoseconds: reduce kernel entered,
-// all ranks' gradients seen (block 0), slice complete (last block), gather kernel entered, all ranks' slices seen
-// (block 0), gather done (last block).
+// state of a bucket, 16 ints: [0] steps done, [1] ticket of the slice phase, [2] error (a wait ran out), [3] ticket
+// of the gather phase, [4..15] six 64-bit time stamps of the latest step in nanoseconds: kernel entered (after the
+// grid dependency), all ranks' gradients seen (block 0), slice complete (last block), [unused], all ranks' slices
+// seen (block 0), done (last block).
+//
+// One kernel per bucket and step, in one of two forms.
+//   Two passes (whole_bucket == 0): wait for all ranks' gradients -> reduce + Adam on this rank's slice -> tell the
+//   peers -> wait for all ranks' slices -> pull them.  Blocks wait for the LAST block of their own grid between the two
+//   phases; the grid is small (at most 64 blocks), and the only kernels that can hold it up are backward kernels,
+//   which wait for nothing.  NVLink carries 2 (N-1)/N of the bucket per rank.
+//   One pass (whole_bucket == 1): wait for all ranks' gradients -> every rank reduces the WHOLE bucket and applies Adam
+//   to all of it (the same additions in the same order on every rank: bit-identical replicas) -> the last block waits
+//   until every rank has finished reading.  NVLink carries (N-1) times the bucket per rank, but there is one flag
+//   round trip less and no second pass: the form for a small bucket that nothing else can hide (the one whose
+//   gradients come last in the backward pass).  A bucket must keep its form from step to step (one-pass buckets keep
+//   full moments on every rank, two-pass buckets only their slices).
 //
 // WORLD = number of ranks when it is 2, 4 or 8 (all loads of an iteration are then issued before the first one is
 // used: 8 peer loads of 16 bytes in flight per thread, i.e. 8 / WORLD elements per iteration), 0 = any number of ranks
@@ -98,35 +115,39 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // every variant, so all of them give the same bits.
 template <int WORLD>
 __global__ void __launch_bounds__(kThreads)
-exchange_reduce_adam_kernel(ExchangePeers peers, int rank, int world, float *__restrict__ m, float *__restrict__ v, int64_t off4,
-                            int64_t n4, int bucket, float lr, float beta1, float beta2, float eps, int *__restrict__ state,
-                            unsigned poll_limit) {
+exchange_bucket_kernel(ExchangePeers peers, int rank, int world, float *__restrict__ m, float *__restrict__ v, int64_t off4,
+                       int64_t n4, int bucket, float lr, float beta1, float beta2, float eps, int *__restrict__ state,
+                       int announce_here, int whole_bucket, unsigned wait_us) {
     __shared__ float s_step_size, s_bc2_sqrt;
     unsigned long long *stamps = reinterpret_cast<unsigned long long *>(state + 4);
-    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[0] = global_timer_ns();
+    // the step count of this bucket was last written by this kernel one step ago: safe before the dependency wait
     const int epoch = state[0] + 1;
-    // announce (once per rank): this rank's gradients of the bucket were written by kernels that completed before this
-    // one started; the fence orders them before the flag for observers on other GPUs
-    if (blockIdx.x == 0 && (int)threadIdx.x < world) {
-        __threadfence_system();
-        st_release_sys(peers.flags[threadIdx.x] + flag_index(bucket, rank, 0), epoch);
-    }
     if (threadIdx.x == kThreads - 1) {  // a thread that polls no flag
         const float t = (float)epoch;
         s_step_size = lr / (1.f - powf(beta1, t));
         s_bc2_sqrt = sqrtf(1.f - powf(beta2, t));
     }
-    const bool ok = wait_peers(peers.flags[rank], world, bucket, 0, epoch, poll_limit);  // ends with a block barrier
+    grid_dependency_wait();  // this rank's gradients come from the kernel just before (when launched right behind it)
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[0] = global_timer_ns();
+    // announce, unless the kernel that wrote the gradients has done it (dl_backward_w_announce_f32): this rank's
+    // gradients of the bucket were written by kernels that completed before this point; the fence orders them before
+    // the flag for observers on other GPUs
+    if (announce_here && blockIdx.x == 0 && (int)threadIdx.x < world) {
+        __threadfence_system();
+        st_release_sys(peers.flags[threadIdx.x] + flag_index(bucket, rank, 0), epoch);
+    }
+    const bool ok_a = wait_peers(peers.flags[rank], world, bucket, 0, epoch, wait_us);  // ends with a block barrier
     if (blockIdx.x == 0 && threadIdx.x == 0) stamps[1] = global_timer_ns();
 
-    if (ok) {
+    const int64_t per = (n4 + world - 1) / world;  // float4 per slice
+    float4 *own_param = reinterpret_cast<float4 *>(peers.param[rank]);
+    if (ok_a) {
         const AdamConsts consts = {1.f - beta1, beta2, 1.f - beta2, s_step_size, s_bc2_sqrt, eps};
         const float inv_world = 1.f / (float)world;
-        // this rank's slice of the bucket, in float4 units of the flat buffers
-        const int64_t per = (n4 + world - 1) / world;
-        const int64_t lo = off4 + min((int64_t)rank * per, n4), hi = min(lo + per, off4 + n4);
+        // this rank's slice of the bucket (the whole bucket in the one-pass form), in float4 units of the flat buffers
+        const int64_t lo = whole_bucket ? off4 : off4 + min((int64_t)rank * per, n4);
+        const int64_t hi = whole_bucket ? off4 + n4 : min(lo + per, off4 + n4);
         float4 *m4 = reinterpret_cast<float4 *>(m), *v4 = reinterpret_cast<float4 *>(v);
-        float4 *own_param = reinterpret_cast<float4 *>(peers.param[rank]);
         constexpr int W = WORLD > 0 ? WORLD : 1;
         constexpr int U = WORLD > 0 ? 8 / W : 1;  // elements per thread and iteration
         const int64_t stride = (int64_t)gridDim.x * kThreads;
@@ -179,49 +200,64 @@ exchange_reduce_adam_kernel(ExchangePeers peers, int rank, int world, float *__r
     }
 
     // The last block of this rank to finish its part of the slice tells the peers -- unless a wait ran out in any block
-    // of this launch: then the flag stays down and the peers' gather kernels run out too, instead of fetching
-    // a slice that is only partly updated.  Every thread orders its stores at GPU scope (they are stores to this
-    // GPU's own memory: once they are visible on this GPU, a peer's load over NVLink sees them too); only the one
-    // thread that raises the flags pays for a system-scope fence.
-    __threadfence();
+    // of this launch: then the flag stays down and the gather phase runs out everywhere, instead of fetching a slice
+    // that is only partly updated.  The block barrier orders every thread's stores before thread 0's fence (they are
+    // stores to this GPU's own memory: once they are visible on this GPU, a peer's load over NVLink sees them too);
+    // only the one thread that raises the flags pays for a system-scope fence.
+    __shared__ int s_last_and_sound;
     __syncthreads();
     if (threadIdx.x == 0) {
-        if (!ok) atomicExch(state + 2, 1);
+        if (!ok_a) atomicExch(state + 2, 1);
         __threadfence();
-        const int add = ok ? 1 : 0x10001;  // low half: blocks that are through; high half: those whose wait ran out
+        const int add = ok_a ? 1 : 0x10001;  // low half: blocks that are through; high half: those whose wait ran out
         const int all = atomicAdd(state + 1, add) + add;
+        s_last_and_sound = 0;
         if ((all & 0xffff) == (int)gridDim.x) {
             state[1] = 0;
             if ((all >> 16) == 0) {
                 __threadfence_system();
                 stamps[2] = global_timer_ns();
                 for (int p = 0; p < world; ++p) st_release_sys(peers.flags[p] + flag_index(bucket, rank, 1), epoch);
+                s_last_and_sound = 1;
             }
         }
     }
-}
 
-// Pulls the other ranks' slices of the bucket's new parameters, 8 peer loads of 16 bytes in flight per thread.
-__global__ void __launch_bounds__(kThreads)
-exchange_gather_kernel(ExchangePeers peers, int rank, int world, int64_t off4, int64_t n4, int bucket, int *__restrict__ state,
-                       unsigned poll_limit) {
-    constexpr int U = 8;
-    unsigned long long *stamps = reinterpret_cast<unsigned long long *>(state + 4);
-    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[3] = global_timer_ns();
-    const int epoch = state[0] + 1;
-    const bool ok = wait_peers(peers.flags[rank], world, bucket, 1, epoch, poll_limit);
+    if (whole_bucket) {
+        // One-pass form: every rank has averaged and updated the WHOLE bucket, so there is nothing to fetch.  The flag
+        // just raised says "this rank has finished reading the others' gradients"; the kernel must not end before all
+        // ranks have said so, because the next step's backward_w overwrites the gradients.  Only the block that
+        // finished last waits (the ranks work in lockstep after the first wait, so this is one flag latency).
+        __syncthreads();
+        if (!s_last_and_sound) return;
+        const bool ok_d = wait_peers(peers.flags[rank], world, bucket, 1, epoch, wait_us);
+        if (threadIdx.x == 0) {
+            const unsigned long long now = global_timer_ns();
+            stamps[4] = now;
+            stamps[5] = now;
+            if (ok_d)
+                state[0] = epoch;
+            else
+                atomicExch(state + 2, 1);
+        }
+        return;
+    }
+
+    // gather: wait until every rank's slice is complete (this rank's own flag included: it comes from this grid's last
+    // block), then pull the other ranks' slices, 8 peer loads of 16 bytes in flight per thread.  After a wait that
+    // ran out in the first phase there is nothing to wait for (this rank will never raise its flag).
+    const bool ok_b = ok_a && wait_peers(peers.flags[rank], world, bucket, 1, epoch, wait_us);
     if (blockIdx.x == 0 && threadIdx.x == 0) stamps[4] = global_timer_ns();
-    if (ok && world > 1) {
-        const int64_t per = (n4 + world - 1) / world;
+    if (ok_b && world > 1) {
+        constexpr int UG = 8;
         const int64_t total = (int64_t)(world - 1) * per;  // positions in the other ranks' slices (the tail may be short)
         const int64_t end4 = off4 + n4;
-        float4 *own_param = reinterpret_cast<float4 *>(peers.param[rank]);
         const int64_t stride = (int64_t)gridDim.x * kThreads;
-        for (int64_t base = (int64_t)blockIdx.x * kThreads + threadIdx.x; base < total; base += stride * U) {
-            float4 val[U];
-            int64_t at[U];
+        for (int64_t base = (int64_t)blockIdx.x * kThreads + threadIdx.x; base < total; base += stride * UG) {
+            float4 val[UG];
+            int64_t at[UG];
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
+            for (int u = 0; u < UG; ++u) {
                 const int64_t idx = base + u * stride;
                 at[u] = -1;
                 if (idx < total) {
@@ -236,16 +272,16 @@ exchange_gather_kernel(ExchangePeers peers, int rank, int world, int64_t off4, i
                 }
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u)
+            for (int u = 0; u < UG; ++u)
                 if (at[u] >= 0) own_param[at[u]] = val[u];
         }
     }
     // the last block to finish advances the bucket's step count -- only when no block's wait ran out
     __syncthreads();
     if (threadIdx.x == 0) {
-        if (!ok) atomicExch(state + 2, 1);
+        if (!ok_b) atomicExch(state + 2, 1);
         __threadfence();
-        const int add = ok ? 1 : 0x10001;
+        const int add = ok_b ? 1 : 0x10001;
         const int all = atomicAdd(state + 3, add) + add;
         if ((all & 0xffff) == (int)gridDim.x) {
             state[3] = 0;
@@ -254,6 +290,15 @@ exchange_gather_kernel(ExchangePeers peers, int rank, int world, int64_t off4, i
                 state[0] = epoch;
             }
         }
+    }
+}
+
+// Announces this rank's gradients of a bucket when no backward_w kernel did it (dl_backward_w_announce_f32 does it from
+// its last block): one thread per rank stores the bucket's next epoch into that rank's flag words.
+__global__ void exchange_announce_kernel(ExchangePeers peers, int rank, int world, int bucket, const int *__restrict__ state) {
+    if ((int)threadIdx.x < world) {
+        __threadfence_system();
+        st_release_sys(peers.flags[threadIdx.x] + flag_index(bucket, rank, 0), state[0] + 1);
     }
 }
 
@@ -332,45 +377,55 @@ static int exchange_peers(const char *who, ExchangePeers &peers, void *const *pa
 }
 
 // param_ptrs / grad_ptrs / flag_ptrs: HOST arrays of `world` device pointers, index = rank (own entry: own buffers).
-extern "C" DL_API int dl_exchange_reduce_adam_f32(void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs, int rank, int world,
-                                                  float *exp_avg, float *exp_avg_sq, int64_t offset, int64_t count, int bucket, float lr,
-                                                  float beta1, float beta2, float eps, int32_t *state, uint32_t poll_limit, void *stream) {
+extern "C" DL_API int dl_exchange_bucket_f32(void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs, int rank, int world,
+                                             float *exp_avg, float *exp_avg_sq, int64_t offset, int64_t count, int bucket, float lr,
+                                             float beta1, float beta2, float eps, int32_t *state, int announce_here,
+                                             int whole_bucket, uint32_t wait_limit_us, int flags, void *stream) {
     ExchangePeers peers;
-    DL_REQUIRE(grad_ptrs != nullptr, DL_ERR_INVALID_ARG, "dl_exchange_reduce_adam_f32: null pointer");
-    if (int s = exchange_peers("dl_exchange_reduce_adam_f32", peers, param_ptrs, grad_ptrs, flag_ptrs, rank, world, offset, count, bucket, state))
+    DL_REQUIRE(grad_ptrs != nullptr, DL_ERR_INVALID_ARG, "dl_exchange_bucket_f32: null pointer");
+    if (int s = exchange_peers("dl_exchange_bucket_f32", peers, param_ptrs, grad_ptrs, flag_ptrs, rank, world, offset, count, bucket, state))
         return s;
     DL_REQUIRE(exp_avg && exp_avg_sq && aligned_to(exp_avg, 16) && aligned_to(exp_avg_sq, 16), DL_ERR_INVALID_ARG,
-               "dl_exchange_reduce_adam_f32: moments must be non-null and 16-byte aligned");
-    const int64_t n4 = count / 4, per = ceil_div(n4, world);
+               "dl_exchange_bucket_f32: moments must be non-null and 16-byte aligned");
+    const int64_t n4 = count / 4, per = whole_bucket ? n4 : ceil_div(n4, world);
     const int per_thread = (world == 2 || world == 4 || world == 8) ? 8 / world : 1;
+    // enough blocks for one pass over the slice and for one pass of the gather (8 elements per thread); two passes: never
+    // more than 64, the blocks wait for their grid's last block between the phases and a small grid is resident as a
+    // whole; one pass: no block waits for another, up to two blocks per SM
     int64_t blocks = ceil_div(per > 0 ? per : 1, (int64_t)kThreads * per_thread);
-    if (blocks > 4 * 148) blocks = 4 * 148;  // beyond that the grid-stride loop takes over; the ticket holds 16 bits
-    const unsigned limit = poll_limit ? poll_limit : kExchangePollLimit;
+    const int64_t for_gather = whole_bucket ? 0 : ceil_div((int64_t)(world - 1) * per, (int64_t)kThreads * 8);
+    if (blocks < for_gather) blocks = for_gather;
+    const int64_t most = whole_bucket ? 2 * 148 : 64;
+    if (blocks > most) blocks = most;
+    const unsigned limit = wait_limit_us ? wait_limit_us : kExchangeWaitUs;
     int *st = reinterpret_cast<int *>(state);
     cudaStream_t cs = as_stream(stream);
-#define DL_EXCHANGE_REDUCE(WW)                                                                                                     \
-    exchange_reduce_adam_kernel<WW><<<(unsigned)blocks, kThreads, 0, cs>>>(peers, rank, world, exp_avg, exp_avg_sq, offset / 4, n4, \
-                                                                          bucket, lr, beta1, beta2, eps, st, limit)
+    const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
+#define DL_EXCHANGE_BUCKET(WW)                                                                                                          \
+    launch_dependent(overlap, exchange_bucket_kernel<WW>, dim3((unsigned)blocks), dim3(kThreads), 0, cs, peers, rank, world, exp_avg,   \
+                     exp_avg_sq, offset / 4, n4, bucket, lr, beta1, beta2, eps, st, announce_here, whole_bucket ? 1 : 0, limit)
     switch (world) {
-        case 2: DL_EXCHANGE_REDUCE(2); break;
-        case 4: DL_EXCHANGE_REDUCE(4); break;
-        case 8: DL_EXCHANGE_REDUCE(8); break;
-        default: DL_EXCHANGE_REDUCE(0); break;
+        case 2: DL_EXCHANGE_BUCKET(2); break;
+        case 4: DL_EXCHANGE_BUCKET(4); break;
+        case 8: DL_EXCHANGE_BUCKET(8); break;
+        default: DL_EXCHANGE_BUCKET(0); break;
     }
-#undef DL_EXCHANGE_REDUCE
-    return launch_status("dl_exchange_reduce_adam_f32");
+#undef DL_EXCHANGE_BUCKET
+    return launch_status("dl_exchange_bucket_f32");
 }
 
-extern "C" DL_API int dl_exchange_gather_f32(void *const *param_ptrs, void *const *flag_ptrs, int rank, int world, int64_t offset,
-                                             int64_t count, int bucket, int32_t *state, uint32_t poll_limit, void *stream) {
+extern "C" DL_API int dl_exchange_announce(void *const *flag_ptrs, int rank, int world, int bucket, const int32_t *state, void *stream) {
     ExchangePeers peers;
-    if (int s = exchange_peers("dl_exchange_gather_f32", peers, param_ptrs, nullptr, flag_ptrs, rank, world, offset, count, bucket, state))
-        return s;
-    const int64_t n4 = count / 4, per = ceil_div(n4, world);
-    int64_t blocks = ceil_div((int64_t)(world - 1) * per > 0 ? (int64_t)(world - 1) * per : 1, (int64_t)kThreads * 8);
-    if (blocks > 4 * 148) blocks = 4 * 148;
-    const unsigned limit = poll_limit ? poll_limit : kExchangePollLimit;
-    exchange_gather_kernel<<<(unsigned)blocks, kThreads, 0, as_stream(stream)>>>(peers, rank, world, offset / 4, n4, bucket,
-                                                                                 reinterpret_cast<int *>(state), limit);
-    return launch_status("dl_exchange_gather_f32");
+    DL_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world && bucket >= 0 && bucket < kMaxBuckets && flag_ptrs && state,
+               DL_ERR_INVALID_ARG, "dl_exchange_announce: bad argument");
+    for (int p = 0; p < world; ++p) {
+        DL_REQUIRE(flag_ptrs[p], DL_ERR_INVALID_ARG, "dl_exchange_announce: null peer pointer");
+        peers.flags[p] = reinterpret_cast<int *>(flag_ptrs[p]);
+    }
+    exchange_announce_kernel<<<1, 32, 0, as_stream(stream)>>>(peers, rank, world, bucket, reinterpret_cast<const int *>(state));
+    return launch_status("dl_exchange_announce");
 }
+
+// Word of a rank's flag array that rank `rank` raises for (bucket, which): for callers that announce from kernels of
+// their own (dl_backward_w_announce_f32 computes it itself).
+extern "C" DL_API int dl_exchange_flag_word(int bucket, int rank, int which) { return (bucket * kMaxRanks + rank) * 2 + which; }

@@ -132,6 +132,19 @@ struct AdamInBackward {
     float lr, beta1, beta2, eps, grad_scale;
 };
 
+// Optional announcement in the epilogue of backward_w (batch-sharded training over peer memory, exchange.cu): when the
+// last block of the last backward_w kernel of a gradient bucket is through, it stores the bucket's next epoch into
+// every rank's flag words, so the peers learn that this rank's gradients are complete without another launch.
+// block_ticket: one int per parameter (zero at rest); kernel_count: one int per bucket (zero at rest), counts the
+// backward_w kernels of the bucket that are through; world == 0: off.
+struct AnnounceGradients {
+    int *flags[16];        // flag words of every rank (index = rank), own entry included
+    int world, word;       // number of ranks; index of this rank's "gradients complete" word of the bucket
+    const int *epoch_src;  // steps the bucket has done so far: the epoch announced is that + 1
+    int *block_ticket, *kernel_count;
+    int kernels;           // backward_w kernels per step that write into the bucket
+};
+
 // Row of grad_y that holds the gradient of output row j.  gy_group == 1: its own row.  gy_group == g > 1: the layer's
 // outputs are summed in classes of g consecutive rows (GroupSum) and grad_y has one row per CLASS -- the gradient of
 // every row of a class is the same, so it is not expanded to [n_out][batch] in memory.
@@ -143,7 +156,7 @@ template <int G, bool VEC4>
 __global__ void __launch_bounds__(kThreads)
 backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
                   const float *__restrict__ gy, const float *w, int w_mode, float *__restrict__ grad_w,
-                  int64_t n_out, int64_t batch, int64_t ncols, int gy_group, AdamInBackward adam) {
+                  int64_t n_out, int64_t batch, int64_t ncols, int gy_group, AdamInBackward adam, AnnounceGradients ann) {
     using V = typename Vec<VEC4>::type;
     constexpr int R = kThreads / G;
     __shared__ float s_step_size, s_bc2_sqrt;
@@ -255,6 +268,20 @@ backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, co
         if (atomicAdd(adam.state + 1, 1) == (int)gridDim.x - 1) {
             adam.state[1] = 0;
             adam.state[0] = adam.state[0] + 1;
+        }
+    }
+    if (ann.world > 0) {
+        __syncthreads();  // every thread's gradient stores before thread 0's fence and its block's ticket
+        if (tid == 0) __threadfence();
+        if (tid == 0 && atomicAdd(ann.block_ticket, 1) == (int)gridDim.x - 1) {
+            *ann.block_ticket = 0;
+            if (atomicAdd(ann.kernel_count, 1) == ann.kernels - 1) {
+                *ann.kernel_count = 0;
+                __threadfence_system();  // the whole bucket's gradients before the flags, for observers on other GPUs
+                const int epoch = *ann.epoch_src + 1;
+                for (int p = 0; p < ann.world; ++p)
+                    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(ann.flags[p] + ann.word), "r"(epoch) : "memory");
+            }
         }
     }
 }
@@ -386,11 +413,11 @@ static int launch_forward(bool overlap, int G, const float *x, const int64_t *a,
 template <bool VEC4>
 static int launch_backward_w(bool overlap, int G, const float *x, const int64_t *a, const int64_t *b, const float *gy, const float *w,
                              int w_mode, float *grad_w, int64_t n_out, int64_t batch, int64_t ncols, int gy_group,
-                             const AdamInBackward &adam, cudaStream_t st) {
+                             const AdamInBackward &adam, const AnnounceGradients &ann, cudaStream_t st) {
     const unsigned grid = (unsigned)ceil_div(n_out, kThreads / G);
 #define DL_BW(GG)                                                                                          \
     case GG:                                                                                               \
-        launch_dependent(overlap, backward_w_kernel<GG, VEC4>, dim3(grid), dim3(kThreads), 0, st, x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols, gy_group, adam); \
+        launch_dependent(overlap, backward_w_kernel<GG, VEC4>, dim3(grid), dim3(kThreads), 0, st, x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols, gy_group, adam, ann); \
         break;
     switch (G) {
         DL_BW(1) DL_BW(2) DL_BW(4) DL_BW(8) DL_BW(16) DL_BW(32)
@@ -448,7 +475,8 @@ extern "C" DL_API int dl_forward_f32(const float *x, const int64_t *a, const int
 
 static int backward_w_entry(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w, int w_mode,
                             float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int64_t gy_group, int flags, void *stream,
-                            const AdamInBackward &adam = AdamInBackward{nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, 0.f, 0.f}) {
+                            const AdamInBackward &adam = AdamInBackward{nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, 0.f, 0.f},
+                            const AnnounceGradients &ann = AnnounceGradients{}) {
     DL_REQUIRE(gy_group >= 1 && gy_group <= INT32_MAX && n_out % gy_group == 0, DL_ERR_INVALID_ARG,
                "dl_backward_w_f32: n_out (%lld) is not a multiple of the rows per class (%lld)", (long long)n_out, (long long)gy_group);
     DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_backward_w_f32: negative size");
@@ -462,8 +490,8 @@ static int backward_w_entry(const float *x, const int64_t *a, const int64_t *b, 
     const int64_t ncols = vec ? batch / 4 : batch;
     const int G = pow2_at_least(ceil_div(ncols, 4), 32);
     const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
-    return vec ? launch_backward_w<true>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, adam, as_stream(stream))
-               : launch_backward_w<false>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, adam, as_stream(stream));
+    return vec ? launch_backward_w<true>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, adam, ann, as_stream(stream))
+               : launch_backward_w<false>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, adam, ann, as_stream(stream));
 }
 
 extern "C" DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
@@ -508,6 +536,35 @@ extern "C" DL_API int dl_backward_w_adam_f32(const float *x, const int64_t *a, c
     DL_REQUIRE(n_out == 0 || (w && exp_avg && exp_avg_sq && state), DL_ERR_INVALID_ARG, "dl_backward_w_adam_f32: null pointer");
     const AdamInBackward adam = {exp_avg, exp_avg_sq, reinterpret_cast<int *>(state), lr, beta1, beta2, eps, grad_scale};
     return backward_w_entry(x, a, b, grad_y, w, DL_W_LOGITS, grad_w, n_in, n_out, batch, rows_per_class, flags, stream, adam);
+}
+
+// backward_w (DL_W_LOGITS) whose last block announces the bucket's gradients to the peers of a peer-memory exchange.
+extern "C" DL_API int dl_backward_w_announce_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
+                                                 float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int64_t rows_per_class,
+                                                 void *const *flag_ptrs, int rank, int world, int bucket, const int32_t *bucket_state,
+                                                 int32_t *block_ticket, int32_t *kernel_count, int kernels_in_bucket, int flags,
+                                                 void *stream) {
+    DL_REQUIRE(world >= 1 && world <= 16 && rank >= 0 && rank < world && bucket >= 0 && bucket < 32, DL_ERR_INVALID_ARG,
+               "dl_backward_w_announce_f32: rank %d of %d, bucket %d", rank, world, bucket);
+    DL_REQUIRE(flag_ptrs && bucket_state && block_ticket && kernel_count && kernels_in_bucket >= 1 && grad_w, DL_ERR_INVALID_ARG,
+               "dl_backward_w_announce_f32: null pointer");
+    AnnounceGradients ann = {};
+    for (int p = 0; p < world; ++p) {
+        DL_REQUIRE(flag_ptrs[p] != nullptr, DL_ERR_INVALID_ARG, "dl_backward_w_announce_f32: null peer pointer");
+        ann.flags[p] = reinterpret_cast<int *>(flag_ptrs[p]);
+    }
+    ann.world = world;
+    ann.word = (bucket * 16 + rank) * 2;
+    ann.epoch_src = reinterpret_cast<const int *>(bucket_state);
+    ann.block_ticket = reinterpret_cast<int *>(block_ticket);
+    ann.kernel_count = reinterpret_cast<int *>(kernel_count);
+    ann.kernels = kernels_in_bucket;
+    if (n_out == 0) {
+        // nothing is launched for an empty layer, so nothing would announce: refuse instead of waiting forever
+        return fail(DL_ERR_INVALID_ARG, "dl_backward_w_announce_f32: empty layer");
+    }
+    return backward_w_entry(x, a, b, grad_y, w, DL_W_LOGITS, grad_w, n_in, n_out, batch, rows_per_class, flags, stream,
+                            AdamInBackward{nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, 0.f, 0.f}, ann);
 }
 
 extern "C" DL_API int dl_backward_x_f32(const float *x, const float *coef, const float *grad_y, const int64_t *start,

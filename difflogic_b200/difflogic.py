@@ -257,11 +257,11 @@ def _run_backward_w(x, a, b, grad, weights, grad_out, rows_per_class=1):
         ops.logic_backward_w_adam(x, a, b, grad, weights.data, overlap=True, rows_per_class=rows_per_class,
                                   **opt.backward_args(weights))
         return None
-    out = ops.logic_backward_w(x, a, b, grad, weights, ops.W_LOGITS, out=grad_out, overlap=True, rows_per_class=rows_per_class)
-    launched = getattr(weights, '_dl_after_backward_w', None)
-    if launched is not None:
-        launched(weights)   # e.g. FlatAdam's peer-memory exchange: the layer's gradient exchange can go out now
-    return out
+    exchange = getattr(weights, '_dl_exchange', None)
+    if exchange is not None:
+        # FlatAdam's peer-memory exchange: the kernel announces the gradient to the peers, the layer's exchange follows
+        return exchange.backward_w(weights, x, a, b, grad, grad_out, rows_per_class)
+    return ops.logic_backward_w(x, a, b, grad, weights, ops.W_LOGITS, out=grad_out, overlap=True, rows_per_class=rows_per_class)
 
 
 class LogicLayerFunction(torch.autograd.Function):

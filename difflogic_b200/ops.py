@@ -132,6 +132,32 @@ def logic_backward_w_adam(x, a, b, grad_y, w, exp_avg, exp_avg_sq, state, lr, be
     return grad_out
 
 
+def logic_backward_w_announce(x, a, b, grad_y, w, out, rows_per_class, flag_ptrs, rank, world, bucket, bucket_state, block_ticket,
+                              kernel_count, kernels_in_bucket):
+    """logic_backward_w (W_LOGITS) into `out` [n_out, 16] whose last block announces the gradients of exchange bucket
+    `bucket` to the peers (dl_backward_w_announce_f32).  flag_ptrs: ctypes array of the ranks' flag words;
+    bucket_state / block_ticket / kernel_count: int32 device tensors (see the header)."""
+    _f32_matrix(x, "x")
+    _f32_matrix(grad_y, "grad_y")
+    _f32_matrix(w, "w")
+    _f32_matrix(out, "out")
+    n_in, batch = x.shape
+    rows_per_class = int(rows_per_class)
+    n_out = grad_y.shape[0] * rows_per_class
+    _need(grad_y.shape[1] == batch, "grad_y and x disagree on the batch size")
+    _need(tuple(w.shape) == (n_out, 16) and tuple(out.shape) == (n_out, 16), "w and out must be [n_out, 16]")
+    _index(a, "a", n_out)
+    _index(b, "b", n_out)
+    for t in (bucket_state, block_ticket, kernel_count):
+        _need(t.is_cuda and t.dtype == torch.int32 and t.numel() >= 1, "state words must be int32 CUDA tensors")
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_backward_w_announce_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), grad_y.data_ptr(), w.data_ptr(),
+                                                   out.data_ptr(), n_in, n_out, batch, rows_per_class, flag_ptrs, rank, world, bucket,
+                                                   bucket_state.data_ptr(), block_ticket.data_ptr(), kernel_count.data_ptr(),
+                                                   int(kernels_in_bucket), N.LAUNCH_OVERLAP_SETUP, N.stream_of(x)))
+    return out
+
+
 def inverse_index(a, b, n_in):
     """The reference's inverse connection index (difflogic/difflogic.py:56-69) built with device
     ops: for every input row the consumer neurons in increasing order, a neuron whose two inputs

@@ -51,15 +51,21 @@ class FlatAdam(torch.optim.Optimizer):
 
     # -- batch-sharded training: exchange and step over peer memory, bucket by bucket -------------------------------
 
-    def enable_exchange(self, group=None, buckets=None, poll_limit=0):
-        """Switches to the peer-memory exchange (dl_exchange_reduce_adam_f32 / dl_exchange_gather_f32): the flat
+    def enable_exchange(self, group=None, buckets=None, wait_limit_us=0, announce_in_backward=False, one_pass_bytes=8 << 20):
+        """Switches to the peer-memory exchange (dl_backward_w_announce_f32 / dl_exchange_bucket_f32): the flat
         parameter and gradient buffers move into memory that the other ranks of `group` (one process per GPU on this
         machine) map through CUDA IPC.  The buffers are cut into buckets -- one per parameter, or `buckets` groups of
-        consecutive parameters.  As soon as the backward_w kernels of a bucket's layers have been launched, the
-        bucket's two exchange kernels are launched on a stream of their own: the gradients are averaged over the
-        ranks, Adam is applied to this rank's slice, the new parameters are fetched from the other ranks, all beside
-        the rest of the backward pass.  `step()` launches whatever is still missing and makes the current stream wait
-        for the exchange.  No NCCL call is made per step.  Collective: every rank of the group calls it."""
+        consecutive parameters.  A layer's backward_w kernel tells the peers when the bucket's gradients are complete,
+        and the bucket's exchange kernel is launched right after it on a stream of its own: the gradients are averaged
+        over the ranks, Adam is applied to this rank's slice, the new parameters are fetched from the other ranks, all
+        beside the rest of the backward pass.  `step()` launches whatever is still missing and makes the current
+        stream wait for the exchange.  No NCCL call is made per step.  Collective: every rank of the group calls it.
+        wait_limit_us: how long a kernel waits for the other ranks before it gives up (0: 20 seconds).
+        announce_in_backward: the layer's backward_w kernel tells the peers that the gradients are complete (its last
+        block does), instead of the exchange kernel at its start.
+        one_pass_bytes: the bucket whose gradients come LAST in the backward pass -- the only one whose exchange
+        nothing hides -- is exchanged in one pass (every rank averages and updates all of it: one flag round trip
+        less) when (ranks - 1) x its size is at most this many bytes; 0: never."""
         import ctypes
         import torch.distributed as dist
         lib = N.lib()
@@ -121,13 +127,22 @@ class FlatAdam(torch.optim.Optimizer):
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
         self._plan_exchange_buckets(buckets)
         self.state_t = torch.zeros((len(self._buckets), 16), dtype=torch.int32, device=dev)
+        self._bw_tickets = torch.zeros(len(self._params), dtype=torch.int32, device=dev)     # per parameter
+        self._bucket_kernels = torch.zeros(len(self._buckets), dtype=torch.int32, device=dev)  # per bucket
+        self._param_index = {p: i for i, p in enumerate(self._params)}
         self._exchange = (rank, world)
-        self._poll_limit = int(poll_limit)
-        self._comm_stream = torch.cuda.Stream(device=dev)
+        self._wait_limit_us = int(wait_limit_us)   # 0: the library's default (20 s); ranks further apart than that fail the step
+        self._announce_in_backward = bool(announce_in_backward)
+        self._one_pass_bytes = int(one_pass_bytes)
+        self._one_pass = set()          # buckets exchanged in one pass; fixed by the first step
+        self._forms_fixed = False
+        # a few streams for the buckets' exchange kernels, so that a bucket does not queue behind the one before it
+        # (high priority: their few blocks are scheduled ahead of the backward kernels' many)
+        self._comm_streams = [torch.cuda.Stream(device=dev, priority=-1) for _ in range(min(4, len(self._buckets)))]
         self._group = group
         self.exchange_enabled = True
         for p in self._params:
-            p._dl_after_backward_w = self._gradient_launched
+            p._dl_exchange = self
         self._begin_exchange_step()
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
@@ -152,55 +167,91 @@ class FlatAdam(torch.optim.Optimizer):
     def _begin_exchange_step(self):
         self._bucket_pending = [len(b[2]) for b in self._buckets]
         self._bucket_launched = [False] * len(self._buckets)
+        self._bucket_done = []          # events: the buckets' exchange kernels of this step
 
-    def _gradient_launched(self, p):
-        """Called by LogicLayer's backward right after the backward_w kernel of parameter `p` has been launched (on the
-        current stream): when that completes a bucket, the bucket's exchange goes out."""
-        bi = self._bucket_of.get(p)
-        if bi is None or self._bucket_launched[bi]:
-            return
-        self._bucket_pending[bi] -= 1
-        if self._bucket_pending[bi] <= 0:
-            self._launch_bucket(bi)
+    def backward_w(self, p, x, a, b, grad_y, grad_out, rows_per_class=1):
+        """backward_w of the layer whose weights are `p`, called by LogicLayer's backward in place of the plain kernel:
+        the kernel's last block tells the peers that this rank's gradients of p's bucket are complete, and once every
+        backward_w of the bucket is in the queue the bucket's exchange kernel follows -- on a stream of its own,
+        beside the rest of the backward pass; the bucket that comes last right behind its backward_w kernel."""
+        from . import ops
+        rank, world = self._exchange
+        bi = self._bucket_of[p]
+        if self._announce_in_backward:
+            out = ops.logic_backward_w_announce(x, a, b, grad_y, p, grad_out, rows_per_class, self._peer_ptrs["flags"], rank, world,
+                                                bi, self.state_t[bi], self._bw_tickets[self._param_index[p]:],
+                                                self._bucket_kernels[bi:], len(self._buckets[bi][2]))
+        else:
+            out = ops.logic_backward_w(x, a, b, grad_y, p, ops.W_LOGITS, out=grad_out, overlap=True, rows_per_class=rows_per_class)
+        if not self._bucket_launched[bi]:
+            self._bucket_pending[bi] -= 1
+            if self._bucket_pending[bi] <= 0:
+                last = sum(self._bucket_launched) == len(self._buckets) - 1
+                if last and not self._forms_fixed:
+                    if world > 1 and (world - 1) * self._buckets[bi][1] * 4 <= self._one_pass_bytes:
+                        self._one_pass.add(bi)
+                    self._forms_fixed = True
+                self._launch_bucket(bi, behind_backward_w=last, announce_here=not self._announce_in_backward)
+        return out
 
-    def _launch_bucket(self, bi):
+    def _launch_bucket(self, bi, behind_backward_w, announce_here):
         rank, world = self._exchange
         off, cnt, _ = self._buckets[bi]
         g = self.param_groups[0]
         beta1, beta2 = g['betas']
-        lib = N.lib()
         dev = self.flat_param.device
-        ready = torch.cuda.Event()
-        ready.record(torch.cuda.current_stream(dev))
-        self._comm_stream.wait_event(ready)
-        state = self.state_t[bi].data_ptr()
+        current = torch.cuda.current_stream(dev)
+        if behind_backward_w:
+            stream = current     # the kernel's set-up overlaps the end of the backward_w kernel just before it
+        else:
+            stream = self._comm_streams[bi % len(self._comm_streams)]
+            ready = torch.cuda.Event()
+            ready.record(current)
+            stream.wait_event(ready)
         with torch.cuda.device(dev):
-            st = self._comm_stream.cuda_stream
-            N.check(lib.dl_exchange_reduce_adam_f32(self._peer_ptrs["param"], self._peer_ptrs["grad"], self._peer_ptrs["flags"], rank,
-                                                    world, self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(), off, cnt, bi,
-                                                    float(g['lr']), float(beta1), float(beta2), float(g['eps']), state,
-                                                    self._poll_limit, st))
-            N.check(lib.dl_exchange_gather_f32(self._peer_ptrs["param"], self._peer_ptrs["flags"], rank, world, off, cnt, bi, state,
-                                               self._poll_limit, st))
+            N.check(N.lib().dl_exchange_bucket_f32(
+                self._peer_ptrs["param"], self._peer_ptrs["grad"], self._peer_ptrs["flags"], rank, world, self.exp_avg.data_ptr(),
+                self.exp_avg_sq.data_ptr(), off, cnt, bi, float(g['lr']), float(beta1), float(beta2), float(g['eps']),
+                self.state_t[bi].data_ptr(), int(announce_here), int(bi in self._one_pass), self._wait_limit_us,
+                N.LAUNCH_OVERLAP_SETUP if behind_backward_w else N.LAUNCH_PLAIN, stream.cuda_stream))
+        done = torch.cuda.Event()
+        done.record(stream)
+        self._bucket_done.append(done)
         self._bucket_launched[bi] = True
 
+    def full_exp_avg(self):
+        """Adam's first moments of ALL parameters in the flat layout.  Under the peer-memory exchange a rank holds the
+        moments of its own slices only (of the whole bucket for one-pass buckets): they are put together with one
+        all-reduce (collective; a diagnostic, not part of a step)."""
+        if not getattr(self, "exchange_enabled", False):
+            return self.exp_avg.detach().clone()
+        import torch.distributed as dist
+        rank, world = self._exchange
+        m = self.exp_avg.detach().clone()
+        if world > 1:
+            for bi, (off, cnt, _) in enumerate(self._buckets):
+                if bi in self._one_pass and rank != 0:
+                    m[off:off + cnt] = 0        # every rank holds these in full: count them once
+            dist.all_reduce(m, group=self._group)
+        return m
+
     def exchange_error(self):
-        """True when a wait for a peer ever ran out of its poll limit (synchronises).  The step in which that happened
+        """True when a wait for a peer ever ran out of its time limit (synchronises).  The step in which that happened
         left parameters, moments and step count as they were; training cannot go on from there."""
         return bool(int(self.state_t[:, 2].max().item())) if getattr(self, "exchange_enabled", False) else False
 
     def exchange_timing(self):
         """Per bucket, nanoseconds inside the latest exchange on this rank (synchronises): waiting for all ranks'
-        gradients, reduce + Adam on this rank's slice, from there to the gather kernel's start, waiting for all ranks'
-        slices, fetching the other slices; `total_ns` from the reduce kernel's entry to the gather kernel's end."""
+        gradients, reduce + Adam on this rank's slice, waiting for all ranks' slices, fetching the other slices;
+        `total_ns` from the kernel's entry to its end."""
         if not getattr(self, "exchange_enabled", False):
             return None
         out = []
         for row in self.state_t[:, 4:16].cpu().contiguous().view(torch.int64).tolist():
             t = row
-            out.append({"wait_gradients_ns": t[1] - t[0], "slice_ns": t[2] - t[1], "to_gather_ns": t[3] - t[2],
-                        "wait_slices_ns": t[4] - t[3], "gather_ns": t[5] - t[4], "total_ns": t[5] - t[0], "entered_ns": t[0],
-                        "done_ns": t[5]})
+            out.append({"wait_gradients_ns": t[1] - t[0], "slice_ns": t[2] - t[1], "wait_slices_ns": t[4] - t[2],
+                        "gather_ns": t[5] - t[4], "total_ns": t[5] - t[0], "entered_ns": t[0], "done_ns": t[5],
+                        "stamps_ns": [t[0], t[1], t[2], t[4], t[5]]})
         return out
 
     def close(self):
@@ -220,7 +271,7 @@ class FlatAdam(torch.optim.Optimizer):
                 off, cnt = self._slices[p]
                 p.data = keep_param[off:off + cnt].view_as(p)
                 p._dl_grad_out = keep_grad[off:off + cnt].view_as(p)
-                p._dl_after_backward_w = None
+                p._dl_exchange = None
                 p.grad = None
         self.flat_param, self.flat_grad = keep_param, keep_grad
         self.exchange_enabled = False
@@ -281,15 +332,7 @@ class FlatAdam(torch.optim.Optimizer):
         with torch.cuda.device(self.flat_param.device):
             st = N.stream_of(self.flat_param)
             if getattr(self, "exchange_enabled", False):
-                rank, world = self._exchange          # only this rank's slice of every bucket is touched
-                for off, cnt, _ in self._buckets:
-                    per = -(-(cnt // 4) // world) * 4
-                    lo = off + min(rank * per, cnt)
-                    nbytes = (min(lo + per, off + cnt) - lo) * 4
-                    for t in (self.exp_avg, self.exp_avg_sq):
-                        if nbytes > 0:
-                            N.check(N.lib().dl_prefetch_l2(t.data_ptr() + lo * 4, nbytes, st))
-                return
+                return   # a rank touches only its slices, and the exchange kernels read them beside their peer loads
             for t in (self.exp_avg, self.exp_avg_sq):
                 N.check(N.lib().dl_prefetch_l2(t.data_ptr(), t.numel() * 4, st))
 
@@ -315,12 +358,16 @@ class FlatAdam(torch.optim.Optimizer):
         g = self.param_groups[0]
         beta1, beta2 = g['betas']
         if getattr(self, "exchange_enabled", False):
-            # buckets whose gradients were not announced by a backward_w launch (none in a normal step) go out now;
-            # then the current stream waits for the exchange
+            # buckets whose exchange did not go out from a backward_w launch (gradients that came from elsewhere; none in
+            # a normal step) go out now and announce themselves; then the current stream waits for every bucket
             for bi in range(len(self._buckets)):
                 if not self._bucket_launched[bi]:
-                    self._launch_bucket(bi)
-            torch.cuda.current_stream(self.flat_param.device).wait_stream(self._comm_stream)
+                    self._bucket_kernels[bi:bi + 1].zero_()
+                    self._launch_bucket(bi, behind_backward_w=False, announce_here=True)
+            self._forms_fixed = True
+            current = torch.cuda.current_stream(self.flat_param.device)
+            for done in self._bucket_done:
+                current.wait_event(done)
             self._begin_exchange_step()
             return loss
         with torch.cuda.device(self.flat_param.device):

@@ -325,7 +325,7 @@ DL_API int dl_prefetch_l2(const void *ptr, size_t bytes, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Batch-sharded training: gradient exchange and Adam over peer memory, bucket by bucket.
- * No counterpart in the reference (it has no multi-GPU code); the two kernels take the place of an
+ * No counterpart in the reference (it has no multi-GPU code); these kernels take the place of an
  * NCCL all-reduce of the [out_dim,16] gradients followed by dl_adam_step_f32 on every rank.
  *
  * Set-up (these DO allocate, once): every rank allocates its flat parameter buffer, flat gradient
@@ -334,24 +334,37 @@ DL_API int dl_prefetch_l2(const void *ptr, size_t bytes, void *stream);
  * any means) and maps its peers' with dl_comm_import; dl_comm_close / dl_comm_free undo that.
  *
  * Per step and bucket -- a bucket is the range [offset, offset + count) of the flat buffers (floats,
- * multiples of 4), e.g. one layer's weights, numbered 0 .. 31 -- two launches, typically on a stream of
- * their own as soon as the bucket's gradients are complete, beside the rest of the backward pass:
- *   dl_exchange_reduce_adam_f32: tells every peer that this rank's gradients of the bucket are
- *     complete, waits until all peers have said so, averages slice `rank` of the bucket over all ranks'
- *     gradient buffers (peer loads), applies Adam to that slice (exp_avg / exp_avg_sq: buffers of the
- *     flat layout, of which every rank touches only its slices) and writes the new parameters into its
- *     own parameter buffer; then tells the peers that its slice is complete;
- *   dl_exchange_gather_f32: waits until all ranks' slices are complete and fetches the other ranks'
- *     slices (peer loads) into this rank's parameter buffer; advances the bucket's step count.
+ * multiples of 4), e.g. one layer's weights, numbered 0 .. 31:
+ *   1. the rank's gradients of the bucket are announced to every peer (its "gradients complete" flag
+ *      word in every rank's flag array is set to the bucket's step number): by the last block of
+ *      dl_backward_w_announce_f32, i.e. by the kernel that writes them, or by dl_exchange_announce, or by
+ *      dl_exchange_bucket_f32 itself (announce_here = 1);
+ *   2. dl_exchange_bucket_f32, typically on a stream of its own as soon as the bucket's backward_w is in
+ *      the queue, beside the rest of the backward pass: waits until all ranks have announced, averages
+ *      slice `rank` of the bucket over all ranks' gradient buffers (peer loads), applies Adam to that
+ *      slice (exp_avg / exp_avg_sq: buffers of the flat layout, of which every rank touches only its
+ *      slices), writes the new parameters into its own parameter buffer and tells the peers; waits until
+ *      all ranks' slices are complete, fetches the other ranks' slices (peer loads) into this rank's
+ *      parameter buffer and advances the bucket's step count.  With whole_bucket = 1 every rank averages
+ *      and updates the WHOLE bucket instead (identical arithmetic on every rank, full moments on every
+ *      rank), nothing is fetched, and the kernel ends when all ranks have finished reading: one flag round
+ *      trip less at (N-1) times the bucket over NVLink per rank -- for a small bucket that nothing else can
+ *      hide.  A bucket keeps its form from step to step.
  * The pointer arguments are HOST arrays of `world` device pointers (index = rank, own entry = own
  * buffers).  state: sixteen int32 on the device PER BUCKET, zero at first: {steps done, ticket, error,
- * ticket} and six 64-bit nanosecond time stamps of the latest step (%globaltimer: reduce kernel
- * entered, all ranks' gradients seen, own slice complete, gather kernel entered, all ranks' slices
- * seen, gather done).  Waits on peers poll at most poll_limit times (0: the default of 2^22, about a
- * second); when a wait runs out the kernel sets `error` to 1, leaves parameters, moments and step
- * count untouched and returns -- the run cannot continue, but nothing hangs and nothing is corrupted.
- * All ranks must launch the same buckets in the same order, one rank per GPU (the kernels of one
- * step must be able to run at the same time on their GPUs).
+ * ticket} and six 64-bit nanosecond time stamps of the latest step (%globaltimer: kernel entered, all
+ * ranks' gradients seen, own slice complete, unused, all ranks' slices seen, done).  A wait for the
+ * peers takes at most wait_limit_us microseconds (0: the default of 20 seconds); when a wait runs out
+ * the kernel sets `error` to 1, leaves parameters, moments and step count untouched and returns -- the
+ * run cannot continue, but nothing hangs and nothing is corrupted.  flags: DL_LAUNCH_OVERLAP_SETUP when the
+ * kernel is launched right behind the kernel that wrote this rank's gradients of the bucket, in the
+ * same stream.  All ranks must launch the same buckets, one rank per GPU (the kernels of one step
+ * must be able to run at the same time on their GPUs).  The kernel waits for other GPUs only.
+ *
+ * dl_backward_w_announce_f32: dl_backward_w_classes_f32 with DL_W_LOGITS whose last block does step 1.
+ * bucket_state: the bucket's sixteen int32 (the step number announced is steps done + 1);
+ * block_ticket: one zeroed int32 per parameter; kernel_count: one zeroed int32 per bucket, shared by the
+ * kernels_in_bucket backward_w kernels per step that write into the bucket (the last one announces).
  * ---------------------------------------------------------------------------------------- */
 DL_API int dl_comm_alloc(size_t bytes, void **ptr);
 DL_API int dl_comm_free(void *ptr);
@@ -359,12 +372,17 @@ DL_API int dl_comm_export(void *ptr, unsigned char *handle);
 DL_API int dl_comm_import(const unsigned char *handle, void **ptr);
 DL_API int dl_comm_close(void *ptr);
 DL_API size_t dl_exchange_flag_bytes(void);
-DL_API int dl_exchange_reduce_adam_f32(void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs, int rank,
-                                       int world, float *exp_avg, float *exp_avg_sq, int64_t offset, int64_t count, int bucket,
-                                       float lr, float beta1, float beta2, float eps, int32_t *state, uint32_t poll_limit,
-                                       void *stream);
-DL_API int dl_exchange_gather_f32(void *const *param_ptrs, void *const *flag_ptrs, int rank, int world, int64_t offset,
-                                  int64_t count, int bucket, int32_t *state, uint32_t poll_limit, void *stream);
+DL_API int dl_exchange_flag_word(int bucket, int rank, int which);
+DL_API int dl_exchange_announce(void *const *flag_ptrs, int rank, int world, int bucket, const int32_t *state, void *stream);
+DL_API int dl_exchange_bucket_f32(void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs, int rank, int world,
+                                  float *exp_avg, float *exp_avg_sq, int64_t offset, int64_t count, int bucket, float lr,
+                                  float beta1, float beta2, float eps, int32_t *state, int announce_here, int whole_bucket,
+                                  uint32_t wait_limit_us, int flags, void *stream);
+DL_API int dl_backward_w_announce_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
+                                      float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int64_t rows_per_class,
+                                      void *const *flag_ptrs, int rank, int world, int bucket, const int32_t *bucket_state,
+                                      int32_t *block_ticket, int32_t *kernel_count, int kernels_in_bucket, int flags,
+                                      void *stream);
 
 #ifdef __cplusplus
 }

@@ -2,7 +2,7 @@
 
 Rank 0 of a world of two is driven through the C ABI; its "peer" is a second set of buffers in the same process
 (same GPU, ordinary memory) that no kernel ever drives, so the flags rank 0 waits for are never raised.  With a
-small poll limit the kernels must give up, report through the error word of the bucket's state, and leave
+short time limit the kernels must give up, report through the error word of the bucket's state, and leave
 parameters, moments and step count exactly as they were.  Then the test plays the peer by hand (raises its flags)
 and the next call must work.  Nothing here faults or waits without a limit.
 """
@@ -26,8 +26,8 @@ def _ptrs(*tensors):
     return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
 
 
-@pytest.mark.parametrize("bucket", [0, 3])
-def test_exchange_wait_runs_out_and_leaves_everything_untouched(bucket):
+@pytest.mark.parametrize("bucket,whole", [(0, 0), (3, 0), (1, 1)])
+def test_exchange_wait_runs_out_and_leaves_everything_untouched(bucket, whole):
     lib = N.lib()
     n, lr, beta1, beta2, eps = 4096, 0.01, 0.9, 0.999, 1e-8
     g = torch.Generator().manual_seed(17 + bucket)
@@ -42,13 +42,12 @@ def test_exchange_wait_runs_out_and_leaves_everything_untouched(bucket):
     stream = torch.cuda.current_stream().cuda_stream
     before = own_p.clone()
 
-    def one_step(limit):
-        N.check(lib.dl_exchange_reduce_adam_f32(params, grads, flags, 0, 2, m.data_ptr(), v.data_ptr(), 0, n, bucket, lr, beta1,
-                                                beta2, eps, state.data_ptr(), limit, stream))
-        N.check(lib.dl_exchange_gather_f32(params, flags, 0, 2, 0, n, bucket, state.data_ptr(), limit, stream))
+    def one_step(limit_us):
+        N.check(lib.dl_exchange_bucket_f32(params, grads, flags, 0, 2, m.data_ptr(), v.data_ptr(), 0, n, bucket, lr, beta1, beta2, eps,
+                                           state.data_ptr(), 1, whole, limit_us, N.LAUNCH_PLAIN, stream))
         torch.cuda.synchronize()
 
-    one_step(4096)   # nobody raises the peer's flags: both waits run out
+    one_step(2000)   # 2 ms: nobody raises the peer's flags, the wait for its gradients runs out
     s = state.tolist()
     assert s[2] == 1, "the error word must be set"
     assert s[0] == 0 and s[1] == 0 and s[3] == 0, "step count untouched, tickets re-armed"
@@ -64,13 +63,43 @@ def test_exchange_wait_runs_out_and_leaves_everything_untouched(bucket):
     one_step(0)      # default limit; every flag is there already
     s = state.tolist()
     assert s[2] == 0 and s[0] == 1 and s[1] == 0 and s[3] == 0
-    half = n // 2
+    half = n if whole else n // 2      # one pass: this rank updates the whole bucket itself
     ref = before[:half].cpu().clone().requires_grad_(True)
     ref.grad = ((own_g[:half] + peer_g[:half]) * 0.5).cpu()
     torch.optim.Adam([ref], lr=lr, betas=(beta1, beta2), eps=eps).step()
     assert torch.allclose(own_p[:half].cpu(), ref.detach(), rtol=1e-6, atol=1e-7)   # own slice: Adam on the mean gradient
-    assert torch.equal(own_p[half:], peer_p[half:])                                 # other slice: fetched from the peer
-    assert m[half:].abs().max().item() == 0.0                                       # moments of the peer's slice untouched
+    if not whole:
+        assert torch.equal(own_p[half:], peer_p[half:])                             # other slice: fetched from the peer
+        assert m[half:].abs().max().item() == 0.0                                   # moments of the peer's slice untouched
+
+
+def test_backward_w_announces_the_bucket_when_its_last_kernel_is_through():
+    """dl_backward_w_announce_f32 on one GPU, world of one: same gradient as the plain kernel; the flag word carries the
+    bucket's next step number only after BOTH kernels that share the bucket have run; the counters are back at zero."""
+    from difflogic_b200 import ops
+    from tests.helpers import random_layer
+    lib = N.lib()
+    a, b, w = random_layer(40, 96, seed=4)
+    a, b, w = a.cuda(), b.cuda(), w.cuda()
+    x = torch.rand(40, 52, device="cuda")
+    gy = torch.randn(96, 52, device="cuda")
+    ref = ops.logic_backward_w(x, a, b, gy, w, ops.W_LOGITS)
+    flags = torch.zeros(lib.dl_exchange_flag_bytes() // 4, dtype=torch.int32, device="cuda")
+    state = torch.zeros(16, dtype=torch.int32, device="cuda")
+    state[0] = 6                                   # six steps done: the seventh is announced
+    tickets = torch.zeros(2, dtype=torch.int32, device="cuda")
+    kernels = torch.zeros(1, dtype=torch.int32, device="cuda")
+    bucket, word = 2, lib.dl_exchange_flag_word(2, 0, 0)
+    assert word == _flag(2, 0, 0)
+    out1, out2 = torch.empty_like(ref), torch.empty_like(ref)
+    ops.logic_backward_w_announce(x, a, b, gy, w, out1, 1, _ptrs(flags), 0, 1, bucket, state, tickets[0:], kernels, 2)
+    torch.cuda.synchronize()
+    assert int(flags[word]) == 0 and int(kernels[0]) == 1 and int(tickets[0]) == 0
+    ops.logic_backward_w_announce(x, a, b, gy, w, out2, 1, _ptrs(flags), 0, 1, bucket, state, tickets[1:], kernels, 2)
+    torch.cuda.synchronize()
+    assert int(flags[word]) == 7 and int(kernels[0]) == 0 and not tickets.any()
+    assert torch.equal(out1, ref) and torch.equal(out2, ref)
+    assert int(flags.ne(0).sum()) == 1
 
 
 def test_exchange_entry_points_validate_their_arguments():
@@ -81,9 +110,9 @@ def test_exchange_entry_points_validate_their_arguments():
     one = _ptrs(t)
     flags = _ptrs(f)
     args = (t.data_ptr(), t.data_ptr())
-    assert lib.dl_exchange_reduce_adam_f32(one, one, flags, 1, 1, *args, 0, 64, 0, 0.01, 0.9, 0.999, 1e-8, st.data_ptr(), 0, None) \
-        == N.DL_ERR_INVALID_ARG                                   # rank outside the world
-    assert lib.dl_exchange_reduce_adam_f32(one, one, flags, 0, 1, *args, 0, 62, 0, 0.01, 0.9, 0.999, 1e-8, st.data_ptr(), 0, None) \
-        == N.DL_ERR_INVALID_ARG                                   # count not a multiple of 4
-    assert lib.dl_exchange_gather_f32(one, flags, 0, 1, 0, 64, 32, st.data_ptr(), 0, None) == N.DL_ERR_INVALID_ARG   # bucket
-    assert lib.dl_exchange_gather_f32(one, flags, 0, 17, 0, 64, 0, st.data_ptr(), 0, None) == N.DL_ERR_INVALID_ARG   # world
+    tail = (0.01, 0.9, 0.999, 1e-8, st.data_ptr(), 1, 0, 0, 0, None)
+    assert lib.dl_exchange_bucket_f32(one, one, flags, 1, 1, *args, 0, 64, 0, *tail) == N.DL_ERR_INVALID_ARG    # rank outside the world
+    assert lib.dl_exchange_bucket_f32(one, one, flags, 0, 1, *args, 0, 62, 0, *tail) == N.DL_ERR_INVALID_ARG    # count not a multiple of 4
+    assert lib.dl_exchange_bucket_f32(one, one, flags, 0, 1, *args, 0, 64, 32, *tail) == N.DL_ERR_INVALID_ARG   # bucket
+    assert lib.dl_exchange_bucket_f32(one, one, flags, 0, 17, *args, 0, 64, 0, *tail) == N.DL_ERR_INVALID_ARG   # world
+    assert lib.dl_exchange_announce(flags, 0, 1, 40, st.data_ptr(), None) == N.DL_ERR_INVALID_ARG
