@@ -55,6 +55,10 @@ SIGNATURES = {
     "dl_groupsum_cross_entropy_backward_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),
     "dl_groupsum_cross_entropy_applicable": (_int, [_i64, _i64, _i64]),
     "dl_groupsum_cross_entropy_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),
+    "dl_forward_class_sums_rows": (_i64, [_i64, _i64, _i64]),
+    "dl_forward_class_sums_run": (_i64, [_i64]),
+    "dl_forward_class_sums_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
+    "dl_class_sums_cross_entropy_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _f32, _ptr]),
     "dl_backward_w_classes_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _int, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
     "dl_backward_w_adam_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _f32, _f32, _f32, _f32,
                                       _f32, _ptr, _int, _ptr]),

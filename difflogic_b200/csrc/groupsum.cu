@@ -159,6 +159,70 @@ groupsum_cluster_kernel(const float *__restrict__ x, float *__restrict__ out, in
     cluster.sync();  // the other CTAs' shared memory must stay alive until the first one has read it
 }
 
+// Mean cross-entropy loss over ALL samples from the scores in global memory, and the gradient of the loss w.r.t. the
+// scores laid out as one row per class; run by the one CTA that holds the ticket.  THREADS: its size.
+template <int THREADS>
+__device__ __forceinline__ void cross_entropy_of_scores(const float *__restrict__ scores, const int64_t *__restrict__ target,
+                                                        float *__restrict__ loss, float *__restrict__ grad_classes,
+                                                        unsigned int *__restrict__ counter, int64_t batch, int k, float tau,
+                                                        float *s_red) {
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const float scale = 1.f / (float)batch;
+    float local = 0.f;
+    constexpr int kRowRegs = 16;  // classes held in registers (one read of the scores instead of three)
+    for (int64_t s = tid; s < batch; s += THREADS) {
+        const float *row = scores + s * k;
+        const int64_t t = target[s];
+        if (k <= kRowRegs) {
+            float r[kRowRegs];
+#pragma unroll
+            for (int cc = 0; cc < kRowRegs; ++cc) r[cc] = cc < k ? __ldcg(row + cc) : -INFINITY;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int cc = 0; cc < kRowRegs; ++cc) mx = fmaxf(mx, r[cc]);  // the padding never wins: max is order-free
+            float sum = 0.f;
+#pragma unroll
+            for (int cc = 0; cc < kRowRegs; ++cc)
+                if (cc < k) sum += expf(r[cc] - mx);
+            const float lse = mx + logf(sum);
+#pragma unroll
+            for (int cc = 0; cc < kRowRegs; ++cc) {
+                if (cc < k) {
+                    const float p = expf(r[cc] - lse);
+                    const float g = (p - (t == cc ? 1.f : 0.f)) * scale;
+                    grad_classes[(int64_t)cc * batch + s] = g / tau;
+                    if (t == cc) local += lse - r[cc];
+                }
+            }
+        } else {
+            float mx = -INFINITY;
+            for (int cc = 0; cc < k; ++cc) mx = fmaxf(mx, __ldcg(row + cc));
+            float sum = 0.f;
+            for (int cc = 0; cc < k; ++cc) sum += expf(__ldcg(row + cc) - mx);
+            const float lse = mx + logf(sum);
+            for (int cc = 0; cc < k; ++cc) {
+                const float p = expf(__ldcg(row + cc) - lse);
+                const float g = (p - (t == cc ? 1.f : 0.f)) * scale;
+                grad_classes[(int64_t)cc * batch + s] = g / tau;
+            }
+            if (t >= 0 && t < k) local += lse - __ldcg(row + t);
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
+    if (lane == 0) s_red[warp] = local;
+    __syncthreads();
+    if (warp == 0) {
+        float v = lane < THREADS / 32 ? s_red[lane] : 0.f;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) {
+            loss[0] = v / (float)batch;
+            *counter = 0u;  // ready for the next call
+        }
+    }
+}
+
 // GroupSum forward + cross-entropy loss (mean over the batch) + the gradient of the loss w.r.t. the class scores, in
 // ONE launch: the head of a training step.  Same cluster scheme as above with one barrier less (every CTA pushes its
 // piece into the first CTA's shared memory, then one cluster barrier), and the first CTA of the cluster that finishes
@@ -232,60 +296,151 @@ groupsum_ce_kernel(const float *__restrict__ x, const int64_t *__restrict__ targ
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    const float scale = 1.f / (float)batch;
-    float local = 0.f;
-    constexpr int kRowRegs = 16;  // classes held in registers (one read of the scores instead of three)
-    for (int64_t s = tid; s < batch; s += kGcThreads) {
-        const float *row = scores + s * k;
-        const int64_t t = target[s];
-        if (k <= kRowRegs) {
-            float r[kRowRegs];
-#pragma unroll
-            for (int cc = 0; cc < kRowRegs; ++cc) r[cc] = cc < k ? __ldcg(row + cc) : -INFINITY;
-            float mx = -INFINITY;
-#pragma unroll
-            for (int cc = 0; cc < kRowRegs; ++cc) mx = fmaxf(mx, r[cc]);  // the padding never wins: max is order-free
-            float sum = 0.f;
-#pragma unroll
-            for (int cc = 0; cc < kRowRegs; ++cc)
-                if (cc < k) sum += expf(r[cc] - mx);
-            const float lse = mx + logf(sum);
-#pragma unroll
-            for (int cc = 0; cc < kRowRegs; ++cc) {
-                if (cc < k) {
-                    const float p = expf(r[cc] - lse);
-                    const float g = (p - (t == cc ? 1.f : 0.f)) * scale;
-                    grad_classes[(int64_t)cc * batch + s] = g / tau;
-                    if (t == cc) local += lse - r[cc];
-                }
-            }
-        } else {
-            float mx = -INFINITY;
-            for (int cc = 0; cc < k; ++cc) mx = fmaxf(mx, __ldcg(row + cc));
-            float sum = 0.f;
-            for (int cc = 0; cc < k; ++cc) sum += expf(__ldcg(row + cc) - mx);
-            const float lse = mx + logf(sum);
-            for (int cc = 0; cc < k; ++cc) {
-                const float p = expf(__ldcg(row + cc) - lse);
-                const float g = (p - (t == cc ? 1.f : 0.f)) * scale;
-                grad_classes[(int64_t)cc * batch + s] = g / tau;
-            }
-            if (t >= 0 && t < k) local += lse - __ldcg(row + t);
+    cross_entropy_of_scores<kGcThreads>(scores, target, loss, grad_classes, counter, batch, k, tau, s_red);
+}
+
+// Head of a training step when the last layer's forward kernel has already added up its rows per class and CTA
+// (dl_forward_class_sums_f32): `sums` is [2 * runs][batch], rows 2*i and 2*i+1 holding the sums of the i-th run of `nb`
+// rows for the class of its first row and for the next class.  A CTA takes (128 batch columns, class): its eight
+// groups of 128 threads add the class's pieces in a fixed order (piece p goes to group p % 8, the groups are added in
+// order) and write the scores; the CTA that holds the ticket computes the loss and the class-row gradients as in
+// groupsum_ce_kernel.  Reads pieces * batch floats per class that the forward kernel has just written (L2).
+constexpr int kCsThreads = 1024;
+constexpr int kCsGroups = kCsThreads / kGsCols;  // 8
+
+__global__ void __launch_bounds__(kCsThreads)
+class_sums_ce_kernel(const float *__restrict__ sums, const int64_t *__restrict__ target, float *__restrict__ scores,
+                     float *__restrict__ loss, float *__restrict__ grad_classes, unsigned int *__restrict__ counter, int64_t batch, int k,
+                     int m, int nb, float tau) {
+    __shared__ float s_part[kCsGroups][kGsCols];
+    __shared__ float s_red[kCsThreads / 32];
+    __shared__ bool s_last;
+    const int tid = threadIdx.x, g = tid / kGsCols, col = tid % kGsCols;
+    const int c = blockIdx.y;
+    const int64_t gcol = (int64_t)blockIdx.x * kGsCols + col;
+    const unsigned row0 = (unsigned)c * (unsigned)m;  // n < 2^31
+    const unsigned first = row0 / (unsigned)nb, last = (row0 + (unsigned)m - 1u) / (unsigned)nb;  // runs that hold rows of class c
+    grid_dependency_wait();  // sums is the output of the kernel just before
+    float acc = 0.f;
+    if (gcol < batch) {
+#pragma unroll 8
+        for (unsigned i = first + (unsigned)g; i <= last; i += kCsGroups) {
+            const unsigned e = i * (unsigned)nb >= row0 ? 0u : 1u;  // the run's first row is of class c, or of the class before it
+            acc += __ldcg(sums + (int64_t)(2u * i + e) * batch + gcol);
         }
     }
+    s_part[g][col] = acc;
+    __syncthreads();
+    if (g == 0 && gcol < batch) {
+        float total = 0.f;
+#pragma unroll
+        for (int gg = 0; gg < kCsGroups; ++gg) total += s_part[gg][col];
+        scores[gcol * k + c] = total / tau;
+    }
+    // ---- ticket: the CTA that gets here last computes the loss over all samples
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(counter, 1u) == gridDim.x * gridDim.y - 1u;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    cross_entropy_of_scores<kCsThreads>(scores, target, loss, grad_classes, counter, batch, k, tau, s_red);
+}
+
+// The same head for a batch of at most 128 samples in ONE thread-block cluster of eight CTAs, with nothing but the final
+// results going through global memory (at most KC classes of at most IT * 64 pieces each).  Piece p of a class goes
+// to CTA p % 8, thread group (p / 8) % 8: every thread has at most IT loads per class, all classes' loads in flight
+// together.  The groups meet in shared memory, the CTAs in the first CTA's view of the others' shared memory
+// (distributed shared memory), always added in a fixed order; the first CTA's first 128 threads go on to the softmax,
+// the loss and the class-row gradients of their sample.  One round of loads, two barriers, no fence, no ticket.
+constexpr int kCsCluster = 8;
+
+template <int KC, int IT>
+__global__ void __launch_bounds__(kCsThreads, 1)
+class_sums_ce_cluster_kernel(const float *__restrict__ sums, const int64_t *__restrict__ target, float *__restrict__ scores,
+                             float *__restrict__ loss, float *__restrict__ grad_classes, int64_t batch, int k, int m, int nb, float tau) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ float s_dyn[];  // [k][kCsGroups][kGsCols] partial sums of the groups
+    __shared__ float s_cta[KC][kGsCols];  // this CTA's sum per class and column
+    __shared__ unsigned s_first[KC], s_last[KC];
+    __shared__ float s_red[kGsCols / 32];
+    const int tid = threadIdx.x, g = tid / kGsCols, col = tid % kGsCols;
+    const unsigned q = cluster.block_rank();
+    if (tid < KC && tid < k) {  // runs that hold rows of class tid (32-bit arithmetic: n < 2^31)
+        const unsigned row0 = (unsigned)tid * (unsigned)m;
+        s_first[tid] = row0 / (unsigned)nb;
+        s_last[tid] = (row0 + (unsigned)m - 1u) / (unsigned)nb;
+    }
+    __syncthreads();
+    grid_dependency_wait();  // sums is the output of the kernel just before
+    float acc[KC];
+#pragma unroll
+    for (int c = 0; c < KC; ++c) {
+        acc[c] = 0.f;
+        if (c < k) {  // uniform: no divergence, the loads of all classes are issued back to back
+            const unsigned first = s_first[c], last = s_last[c], row0 = (unsigned)c * (unsigned)m;
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                // a piece beyond the class's last run, or a column beyond the batch, reads a valid address and adds zero
+                const unsigned want = first + q + (unsigned)(kCsCluster * g) + (unsigned)(it * kCsCluster * kCsGroups);
+                const bool live = want <= last && col < batch;
+                const unsigned i = live ? want : first;
+                // a run whose first row lies before the class's first row began in the class before it
+                const unsigned e = i * (unsigned)nb >= row0 ? 0u : 1u;
+                const float v = __ldcg(sums + (int64_t)(2u * i + e) * batch + (live ? col : 0));
+                acc[c] += live ? v : 0.f;
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < KC; ++c)
+        if (c < k) s_dyn[(c * kCsGroups + g) * kGsCols + col] = acc[c];
+    __syncthreads();
+    for (int idx = tid; idx < k * kGsCols; idx += kCsThreads) {
+        const int c = idx / kGsCols, cl = idx % kGsCols;
+        float total = 0.f;
+#pragma unroll
+        for (int gg = 0; gg < kCsGroups; ++gg) total += s_dyn[(c * kCsGroups + gg) * kGsCols + cl];
+        s_cta[c][cl] = total;
+    }
+    cluster.sync();
+    if (q == 0) {
+        for (int idx = tid; idx < k * kGsCols; idx += kCsThreads) {
+            const int c = idx / kGsCols, cl = idx % kGsCols;
+            float total = 0.f;
+#pragma unroll
+            for (int r = 0; r < kCsCluster; ++r) total += *cluster.map_shared_rank(&s_cta[c][cl], r);
+            const float sc = total / tau;
+            s_dyn[c * kGsCols + cl] = sc;  // the groups' sums are spent: the scores take their place, [class][column]
+            if (cl < batch) scores[(int64_t)cl * k + c] = sc;
+        }
+    }
+    cluster.sync();  // the other CTAs' shared memory stays alive until the first one has read it
+    if (q != 0 || tid >= kGsCols) return;  // the first CTA's first four warps go on, one sample each
+    float local = 0.f;
+    if (col < batch) {
+        const int64_t t = target[col];
+        const float scale = 1.f / (float)batch;
+        float mx = -INFINITY;
+        for (int c = 0; c < k; ++c) mx = fmaxf(mx, s_dyn[c * kGsCols + col]);
+        float sum = 0.f;
+        for (int c = 0; c < k; ++c) sum += expf(s_dyn[c * kGsCols + col] - mx);
+        const float lse = mx + logf(sum);
+        for (int c = 0; c < k; ++c) {
+            const float sc = s_dyn[c * kGsCols + col];
+            const float p = expf(sc - lse);
+            const float gr = (p - (t == c ? 1.f : 0.f)) * scale;
+            grad_classes[(int64_t)c * batch + col] = gr / tau;
+            if (t == c) local += lse - sc;
+        }
+    }
+    // sum of the samples' losses: shuffle within the warps, then over the four warps in order
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
-    if (lane == 0) s_red[warp] = local;
-    __syncthreads();
-    if (warp == 0) {
-        float v = lane < kGcThreads / 32 ? s_red[lane] : 0.f;
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-        if (lane == 0) {
-            loss[0] = v / (float)batch;
-            *counter = 0u;  // ready for the next call
-        }
-    }
+    if (tid % 32 == 0) s_red[tid / 32] = local;
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // only these 128 threads are left
+    if (tid == 0) loss[0] = (((s_red[0] + s_red[1]) + s_red[2]) + s_red[3]) / (float)batch;
 }
 
 // Backward: grad_x[i][:] = grad_out[:, class(i)] / tau.  A CTA takes a run of rows of one class and a block of
@@ -442,6 +597,51 @@ extern "C" DL_API int dl_groupsum_cross_entropy_f32(const float *x, const int64_
     cudaLaunchKernelEx(&cfg, groupsum_ce_kernel, x, target, scores, loss, grad_classes, reinterpret_cast<unsigned int *>(counter), batch,
                        (int)k, (int)(n / k), tau);
     return launch_status("dl_groupsum_cross_entropy_f32");
+}
+
+// Head of a training step from per-CTA class sums (dl_forward_class_sums_f32): scores, loss, grad_classes as
+// dl_groupsum_cross_entropy_f32 gives them.  rows_per_run: rows per CTA of the forward kernel, i.e.
+// 2 * ceil(n / rows_per_run) == dl_forward_class_sums_rows(n, batch, k).  counter: one zeroed uint32, left zero.
+extern "C" DL_API int dl_class_sums_cross_entropy_f32(const float *class_sums, const int64_t *target, float *scores, float *loss,
+                                                      float *grad_classes, void *counter, int64_t n, int64_t batch, int64_t k,
+                                                      int64_t rows_per_run, float tau, void *stream) {
+    if (int s = groupsum_check("dl_class_sums_cross_entropy_f32", n, batch, k)) return s;
+    DL_REQUIRE(n <= INT32_MAX, DL_ERR_TOO_LARGE, "dl_class_sums_cross_entropy_f32: more than 2^31 rows");
+    DL_REQUIRE(n > 0 && batch > 0 && rows_per_run > 0 && n / k >= rows_per_run && rows_per_run <= INT32_MAX, DL_ERR_INVALID_ARG,
+               "dl_class_sums_cross_entropy_f32: classes must be at least as long as a run of rows");
+    DL_REQUIRE(class_sums && target && scores && loss && grad_classes && counter, DL_ERR_INVALID_ARG,
+               "dl_class_sums_cross_entropy_f32: null pointer");
+    const int64_t colblocks = ceil_div(batch, kGsCols);
+    DL_REQUIRE(colblocks <= INT32_MAX && k <= 65535, DL_ERR_TOO_LARGE, "dl_class_sums_cross_entropy_f32: batch or k too large");
+    constexpr int kSmallClasses = 16, kSmallPieces = 2;
+    const size_t small_smem = (size_t)k * kCsGroups * kGsCols * sizeof(float);
+    const int64_t pieces = ceil_div(n / k, rows_per_run) + 1;  // runs that can hold rows of one class
+    if (colblocks == 1 && k <= kSmallClasses && pieces <= kSmallPieces * kCsGroups * kCsCluster) {
+        // one cluster does it all, nothing but the results touches global memory
+        auto kernel = class_sums_ce_cluster_kernel<kSmallClasses, kSmallPieces>;
+        if (small_smem > 32 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)small_smem) != cudaSuccess)
+            return launch_status("dl_class_sums_cross_entropy_f32 (shared memory opt-in)");
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kCsCluster);
+        cfg.blockDim = dim3(kCsThreads);
+        cfg.dynamicSmemBytes = small_smem;
+        cfg.stream = as_stream(stream);
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = kCsCluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        cudaLaunchKernelEx(&cfg, kernel, class_sums, target, scores, loss, grad_classes, batch, (int)k, (int)(n / k), (int)rows_per_run, tau);
+        return launch_status("dl_class_sums_cross_entropy_f32");
+    }
+    launch_dependent(true, class_sums_ce_kernel, dim3((unsigned)colblocks, (unsigned)k), dim3(kCsThreads), 0, as_stream(stream), class_sums, target,
+                     scores, loss, grad_classes, reinterpret_cast<unsigned int *>(counter), batch, (int)k, (int)(n / k), (int)rows_per_run,
+                     tau);
+    return launch_status("dl_class_sums_cross_entropy_f32");
 }
 
 // Backward of cross_entropy(GroupSum(x)) in one launch: dl_cross_entropy_backward_f32 followed by

@@ -38,15 +38,26 @@ __device__ __forceinline__ float ldv(const float *p) { return __ldg(p); }
 // row loads are issued and, while they are in flight, the four coefficients of each of the CTA's
 // neurons are computed into shared memory.
 // ---------------------------------------------------------------------------------------------
-template <int G, int U, bool VEC4>
+__device__ __forceinline__ void zero(float4 &v);
+__device__ __forceinline__ void zero(float &v);
+__device__ __forceinline__ void addv(float4 &acc, const float4 v) { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+__device__ __forceinline__ void addv(float &acc, const float v) { acc += v; }
+
+// CLASSSUM: the layer's output feeds a GroupSum over classes of `class_rows` consecutive rows (the last layer of a
+// network in training).  The rows are then not stored at all: every CTA adds up its NB rows per class -- at most two
+// classes, class_rows >= NB -- in a fixed order and stores the sums as two rows of `y`, which then is
+// [2 * gridDim.x][batch]: row 2*blockIdx.x for the class of the CTA's first neuron, row 2*blockIdx.x + 1 for the
+// next class (zeros when the CTA does not reach it).  class_sums_ce_kernel (groupsum.cu) adds the pieces up.
+template <int G, int U, bool VEC4, bool CLASSSUM>
 __global__ void __launch_bounds__(kThreads, 4)
 forward_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
                const float *__restrict__ w, int w_mode, float *__restrict__ y, float4 *__restrict__ coef_out,
-               int64_t n_out, int64_t batch, int64_t ncols, int64_t nslabs) {
+               int64_t n_out, int64_t batch, int64_t ncols, int64_t nslabs, int64_t class_rows) {
     using V = typename Vec<VEC4>::type;
     constexpr int R = kThreads / G;  // neurons per pass
     constexpr int NB = R * U;        // neurons per CTA
     __shared__ float4 s_coef[NB];
+    __shared__ V s_acc[CLASSSUM ? 2 * kThreads : 1];  // [class 0 | class 1][row group][lane]
 
     const int tid = threadIdx.x;
     const int lane = tid % G;
@@ -96,11 +107,43 @@ forward_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const
             __syncthreads();
             first = false;
         }
+        if (!CLASSSUM) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int r = r0 + u * R;
-            if (incol && n0 + r < n_out)
-                *reinterpret_cast<V *>(y + (n0 + r) * batch + off) = mixv(s_coef[r], va[u], vb[u]);
+            for (int u = 0; u < U; ++u) {
+                const int r = r0 + u * R;
+                if (incol && n0 + r < n_out)
+                    *reinterpret_cast<V *>(y + (n0 + r) * batch + off) = mixv(s_coef[r], va[u], vb[u]);
+            }
+        } else {
+            // rows below `border` belong to the class of the CTA's first neuron, the others to the next class
+            const int64_t border = (n0 / class_rows + 1) * class_rows;
+            V acc0, acc1;
+            zero(acc0);
+            zero(acc1);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int r = r0 + u * R;
+                if (incol && n0 + r < n_out) {
+                    const V val = mixv(s_coef[r], va[u], vb[u]);
+                    if (n0 + r < border)
+                        addv(acc0, val);
+                    else
+                        addv(acc1, val);
+                }
+            }
+            s_acc[tid] = acc0;
+            s_acc[kThreads + tid] = acc1;
+            __syncthreads();
+            if (tid < 2 * G) {  // one thread per (class, lane): the R row groups in a fixed order
+                const int e = tid / G, l = tid % G;
+                V sum;
+                zero(sum);
+#pragma unroll
+                for (int rr = 0; rr < R; ++rr) addv(sum, s_acc[e * kThreads + rr * G + l]);
+                const int64_t c = slab * G + l;
+                if (c < ncols) *reinterpret_cast<V *>(y + (2 * (int64_t)blockIdx.x + e) * batch + c * Vec<VEC4>::width) = sum;
+            }
+            __syncthreads();  // the sums are read before the next slab overwrites them
         }
     }
 }
@@ -391,17 +434,20 @@ build_plan_kernel(const int64_t *__restrict__ a, const int64_t *__restrict__ b, 
 // ---------------------------------------------------------------------------------------------
 static inline unsigned slab_grid(int64_t nslabs) { return (unsigned)(nslabs < 65535 ? nslabs : 65535); }
 
-template <bool VEC4>
+constexpr int kForwardU = 4;  // passes of a CTA of the forward kernel over its row groups
+static inline int64_t forward_rows_per_cta(int G) { return (kThreads / G) * kForwardU; }
+
+template <bool VEC4, bool CLASSSUM = false>
 static int launch_forward(bool overlap, int G, const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode, float *y,
-                          float *coef, int64_t n_out, int64_t batch, int64_t ncols, cudaStream_t st) {
-    constexpr int U = 4;
+                          float *coef, int64_t n_out, int64_t batch, int64_t ncols, cudaStream_t st, int64_t class_rows = 0) {
+    constexpr int U = kForwardU;
     const int64_t nslabs = ceil_div(ncols, G);
-    const int64_t nb = (kThreads / G) * U;
+    const int64_t nb = forward_rows_per_cta(G);
     const dim3 grid((unsigned)ceil_div(n_out, nb), slab_grid(nslabs));
     float4 *c4 = reinterpret_cast<float4 *>(coef);
 #define DL_FWD(GG)                                                                                              \
     case GG:                                                                                                    \
-        launch_dependent(overlap, forward_kernel<GG, U, VEC4>, grid, dim3(kThreads), 0, st, x, a, b, w, w_mode, y, c4, n_out, batch, ncols, nslabs); \
+        launch_dependent(overlap, forward_kernel<GG, U, VEC4, CLASSSUM>, grid, dim3(kThreads), 0, st, x, a, b, w, w_mode, y, c4, n_out, batch, ncols, nslabs, class_rows); \
         break;
     switch (G) {
         DL_FWD(1) DL_FWD(2) DL_FWD(4) DL_FWD(8) DL_FWD(16) DL_FWD(32)
@@ -471,6 +517,62 @@ extern "C" DL_API int dl_forward_f32(const float *x, const int64_t *a, const int
         return launch_forward_tma(overlap, x, a, b, w, w_mode, y, coef, n_out, batch, as_stream(stream));
     return vec ? launch_forward<true>(overlap, G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream))
                : launch_forward<false>(overlap, G, x, a, b, w, w_mode, y, coef, n_out, batch, ncols, as_stream(stream));
+}
+
+// Geometry of the class-sum form of the forward kernel for a batch: the lane group G, rows per CTA and whether rows are
+// moved as float4 (decided from the batch alone; the pointers must then be 16-byte aligned).
+static void forward_class_geometry(int64_t batch, int *G, int64_t *rows_per_cta, bool *vec) {
+    *vec = batch % 4 == 0;
+    const int64_t ncols = *vec ? batch / 4 : batch;
+    *G = pow2_at_least(ncols, 32);
+    *rows_per_cta = forward_rows_per_cta(*G);
+}
+
+// Rows of the `class_sums` buffer that dl_forward_class_sums_f32 writes: two per CTA (0 when the sizes are outside the
+// kernel's range: classes must be at least as long as a CTA's run of rows).
+extern "C" DL_API int64_t dl_forward_class_sums_rows(int64_t n_out, int64_t batch, int64_t k) {
+    if (n_out <= 0 || batch <= 0 || k <= 0 || n_out % k != 0) return 0;
+    int G;
+    int64_t nb;
+    bool vec;
+    forward_class_geometry(batch, &G, &nb, &vec);
+    if (n_out / k < nb) return 0;
+    return 2 * ceil_div(n_out, nb);
+}
+
+// Rows per run (= per CTA of the forward kernel) at this batch size.
+extern "C" DL_API int64_t dl_forward_class_sums_run(int64_t batch) {
+    if (batch <= 0) return 0;
+    int G;
+    int64_t nb;
+    bool vec;
+    forward_class_geometry(batch, &G, &nb, &vec);
+    return nb;
+}
+
+// Forward of a layer whose output goes into GroupSum(k): instead of y [n_out][batch], per-CTA class sums
+// class_sums [dl_forward_class_sums_rows()][batch] are written (see forward_kernel).
+extern "C" DL_API int dl_forward_class_sums_f32(const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode,
+                                                float *class_sums, float *coef, int64_t n_in, int64_t n_out, int64_t batch, int64_t k,
+                                                int flags, void *stream) {
+    DL_REQUIRE(n_in > 0 && n_out > 0 && batch > 0 && k > 0, DL_ERR_INVALID_ARG, "dl_forward_class_sums_f32: sizes must be positive");
+    DL_REQUIRE(n_out % k == 0, DL_ERR_NOT_DIVISIBLE, "dl_forward_class_sums_f32: n_out (%lld) has to be divisible by k (%lld)",
+               (long long)n_out, (long long)k);
+    DL_REQUIRE(w_mode >= DL_W_LOGITS && w_mode <= DL_W_ARGMAX, DL_ERR_INVALID_ARG, "dl_forward_class_sums_f32: unknown w_mode %d", w_mode);
+    DL_REQUIRE(x && a && b && w && class_sums, DL_ERR_INVALID_ARG, "dl_forward_class_sums_f32: null pointer");
+    DL_REQUIRE(dl_forward_class_sums_rows(n_out, batch, k) > 0, DL_ERR_INVALID_ARG,
+               "dl_forward_class_sums_f32: classes of %lld rows are shorter than a CTA's run of rows", (long long)(n_out / k));
+    DL_REQUIRE(coef == nullptr || aligned_to(coef, 16), DL_ERR_INVALID_ARG, "dl_forward_class_sums_f32: coef must be 16-byte aligned");
+    int G;
+    int64_t nb;
+    bool vec;
+    forward_class_geometry(batch, &G, &nb, &vec);
+    DL_REQUIRE(!vec || (aligned_to(x, 16) && aligned_to(class_sums, 16)), DL_ERR_INVALID_ARG,
+               "dl_forward_class_sums_f32: x and class_sums must be 16-byte aligned");
+    const int64_t ncols = vec ? batch / 4 : batch;
+    const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
+    return vec ? launch_forward<true, true>(overlap, G, x, a, b, w, w_mode, class_sums, coef, n_out, batch, ncols, as_stream(stream), n_out / k)
+               : launch_forward<false, true>(overlap, G, x, a, b, w, w_mode, class_sums, coef, n_out, batch, ncols, as_stream(stream), n_out / k);
 }
 
 static int backward_w_entry(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w, int w_mode,

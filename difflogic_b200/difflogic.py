@@ -308,8 +308,9 @@ class LogicLayerFunction(torch.autograd.Function):
 class LogicLayerHeadFunction(torch.autograd.Function):
     """The LAST logic layer, GroupSum and the mean cross-entropy loss as one autograd node (training).
 
-    forward : layer forward, then ONE kernel for the class sums, the loss and the gradient of the loss w.r.t. the
-              class scores (ops.groupsum_cross_entropy);
+    forward : the layer's forward kernel adds up its rows per class and CTA (the output itself is never stored), then one
+              small kernel finishes the class sums and computes the loss and the gradient of the loss w.r.t. the class
+              scores (ops.logic_forward_head); sizes outside that path: layer forward, then ops.groupsum_cross_entropy;
     backward: the layer's backward_w / backward_x read that gradient as "one row per class" -- the `[n, batch]`
               gradient of the layer's output, whose rows are equal within a class, is never formed.
     Replaces LogicLayerFunction -> GroupSumFunction -> CrossEntropyLoss for the tail of
@@ -317,10 +318,15 @@ class LogicLayerHeadFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weights, a, b, start, plan, grad_factor, grad_out, target, k, tau):
-        y, coef = ops.logic_forward(x, a, b, weights, ops.W_LOGITS, want_coef=True, overlap=True)
-        loss, scores, grad_classes = ops.groupsum_cross_entropy(y, target, k, tau)
+        n_out = weights.shape[0]
+        if ops.forward_head_applicable(n_out, x.shape[1], k):
+            # the layer's rows are added up per class inside the forward kernel; its output is never stored
+            loss, scores, grad_classes, coef = ops.logic_forward_head(x, a, b, weights, target, k, tau)
+        else:
+            y, coef = ops.logic_forward(x, a, b, weights, ops.W_LOGITS, want_coef=True, overlap=True)
+            loss, scores, grad_classes = ops.groupsum_cross_entropy(y, target, k, tau)
         ctx.save_for_backward(x, weights, a, b, start, plan, coef, grad_classes)
-        ctx.grad_factor, ctx.grad_out, ctx.rows_per_class = grad_factor, grad_out, y.shape[0] // k
+        ctx.grad_factor, ctx.grad_out, ctx.rows_per_class = grad_factor, grad_out, n_out // k
         ctx.mark_non_differentiable(scores)
         ctx.set_materialize_grads(False)
         return loss, scores
@@ -359,7 +365,8 @@ def logic_layer_head(layer, x, target, k, tau):
     three modules)."""
     if not (layer.training and layer._plan is not None and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2
             and target.dtype == torch.int64 and target.dim() == 1 and layer.out_dim % k == 0
-            and ops.groupsum_cross_entropy_applicable(layer.out_dim, x.shape[0], k)):
+            and (ops.groupsum_cross_entropy_applicable(layer.out_dim, x.shape[0], k)
+                 or ops.forward_head_applicable(layer.out_dim, x.shape[0], k))):
         return None
     xt = x.transpose(0, 1).contiguous()
     a, b = layer.indices

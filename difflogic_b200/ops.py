@@ -475,6 +475,47 @@ def groupsum_cross_entropy(x, target, k, tau):
     return loss, scores, grad_classes
 
 
+def forward_head_applicable(n_out, batch, k):
+    """True when logic_forward_head takes these sizes: classes at least as long as a forward CTA's run of rows."""
+    return N.lib().dl_forward_class_sums_rows(int(n_out), int(batch), int(k)) > 0
+
+
+def logic_forward_head(x, a, b, w, target, k, tau, w_mode=W_LOGITS):
+    """Last layer + GroupSum(k, tau) + mean cross-entropy in two kernels that never store the layer's output:
+    (loss scalar, scores [batch, k], grad_classes [k, batch], coef [n_out, 4]).  The forward kernel's CTAs add up
+    their rows per class; a small second kernel adds those pieces in a fixed order and does the loss.  grad_classes
+    is for logic_backward_w / logic_backward_x with rows_per_class = n_out / k."""
+    _f32_matrix(x, "x")
+    _f32_matrix(w, "w")
+    n_in, batch = x.shape
+    n_out, k = w.shape[0], int(k)
+    _need(w.shape[1] == 16, "w must be [n_out, 16]")
+    _index(a, "a", n_out)
+    _index(b, "b", n_out)
+    _need(k > 0 and n_out % k == 0, "n_out (%d) must be divisible by k (%d)" % (n_out, k))
+    _need(target.is_cuda and target.dtype == torch.int64 and target.dim() == 1 and target.is_contiguous()
+          and target.shape[0] == batch and target.device == x.device, "target must be a contiguous int64 [batch] CUDA tensor")
+    lib = N.lib()
+    rows = lib.dl_forward_class_sums_rows(n_out, batch, k)
+    _need(rows > 0, "classes of %d rows are shorter than a forward CTA's run of rows" % (n_out // k))
+    sums = torch.empty((rows, batch), dtype=torch.float32, device=x.device)
+    coef = torch.empty((n_out, 4), dtype=torch.float32, device=x.device)
+    scores = torch.empty((batch, k), dtype=torch.float32, device=x.device)
+    loss = torch.empty((), dtype=torch.float32, device=x.device)
+    grad_classes = torch.empty((k, batch), dtype=torch.float32, device=x.device)
+    counter = _HEAD_COUNTERS.get(x.device)
+    if counter is None:
+        counter = _HEAD_COUNTERS[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = N.stream_of(x)
+        N.check(lib.dl_forward_class_sums_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), w.data_ptr(), w_mode, sums.data_ptr(),
+                                              coef.data_ptr(), n_in, n_out, batch, k, N.LAUNCH_OVERLAP_SETUP, st))
+        N.check(lib.dl_class_sums_cross_entropy_f32(sums.data_ptr(), target.data_ptr(), scores.data_ptr(), loss.data_ptr(),
+                                                    grad_classes.data_ptr(), counter.data_ptr(), n_out, batch, k,
+                                                    lib.dl_forward_class_sums_run(batch), float(tau), st))
+    return loss, scores, grad_classes, coef
+
+
 def groupsum_backward(grad_out, n, tau):
     """[batch, k] -> feature-major [n, batch] with grad_x[i,:] = grad_out[:, i // (n/k)] / tau."""
     _f32_matrix(grad_out, "grad_out")

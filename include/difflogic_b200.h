@@ -282,6 +282,24 @@ DL_API int dl_cross_entropy_backward_f32(const float *probs, const int64_t *targ
 DL_API int dl_groupsum_cross_entropy_applicable(int64_t n, int64_t batch, int64_t k);
 DL_API int dl_groupsum_cross_entropy_f32(const float *x, const int64_t *target, float *scores, float *loss, float *grad_classes,
                                          void *counter, int64_t n, int64_t batch, int64_t k, float tau, void *stream);
+/* The same head in two launches that never form the last layer's output.  dl_forward_class_sums_f32 is the layer's
+ * forward (as dl_forward_f32), but its CTAs add up their rows per class and store only those sums: class_sums
+ * [dl_forward_class_sums_rows(n_out, batch, k)][batch] holds two rows per run of dl_forward_class_sums_run(batch)
+ * consecutive neurons -- the sum over the run's rows that belong to the class of its first row, and the sum over those of
+ * the next class (zero when the run does not reach it).  dl_class_sums_cross_entropy_f32 adds the runs of each class in
+ * a fixed order and gives scores, loss and grad_classes as above.  Replaces logic_layer_cuda_forward
+ * (difflogic_kernel.cu:259-297) of the last layer + GroupSum (difflogic/difflogic.py:195-196) + CrossEntropyLoss
+ * (experiments/main.py:167,175) in training, where the layer's output itself is never needed (its backward reads the
+ * layer's INPUT and grad_classes).  dl_forward_class_sums_rows returns 0 when a class is shorter than a run (use the
+ * separate entry points then). */
+DL_API int64_t dl_forward_class_sums_rows(int64_t n_out, int64_t batch, int64_t k);
+DL_API int64_t dl_forward_class_sums_run(int64_t batch);
+DL_API int dl_forward_class_sums_f32(const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode,
+                                     float *class_sums, float *coef, int64_t n_in, int64_t n_out, int64_t batch, int64_t k,
+                                     int flags, void *stream);
+DL_API int dl_class_sums_cross_entropy_f32(const float *class_sums, const int64_t *target, float *scores, float *loss,
+                                           float *grad_classes, void *counter, int64_t n, int64_t batch, int64_t k,
+                                           int64_t rows_per_run, float tau, void *stream);
 /* backward_w with the Adam step (update rule of dl_adam_step_f32) of the layer's weights in its epilogue: the 16
  * gradients of a neuron go from the registers straight into the update of w [n_out][16], exp_avg and exp_avg_sq (the
  * layer's slices, same layout as w); grad_w may be null, the gradient is then not stored.  state: two int32 on the
