@@ -803,6 +803,9 @@ def reference_arm(args):
 def run_case(argv):
     """python bench.py --case eval|gbs|tail [words [neurons]]        packed eval / group bit-sum (k = 10) / last layer +
                                                                       group bit-sum in one kernel; default 4096 x 8000
+       python bench.py --case packbits|thrpack [samples [features]]  bool -> words from the batch-major matrix (default
+                                                                      2^18 x 784) / uint8 pixels -> 3 thermometer
+                                                                      thresholds -> words (default 2^16 x 3072)
        python bench.py --case fwd|bw|bx|bwadam|head [batch [neurons]] training kernels; default 128 x 16000
     Each case builds a square layer with 'random' connections and launches the kernel three times.  The sizes are
     chosen so that a full-metric capture of one launch finishes in seconds (a few hundred MB on the device)."""
@@ -830,6 +833,18 @@ def run_case(argv):
                 ops.eval_groupbitsum(x, a, b, gate, 0, 10)
             else:
                 ops.groupbitsum(x, 0, 10)
+    elif which in ("packbits", "thrpack"):
+        samples = int(argv[1]) if len(argv) > 1 else (1 << 18 if which == "packbits" else 1 << 16)
+        n = int(argv[2]) if len(argv) > 2 else (784 if which == "packbits" else 3072)
+        if which == "packbits":
+            t = torch.rand(samples, n, device=dev) < 0.19
+        else:
+            t = torch.randint(0, 256, (samples, n), dtype=torch.uint8, device=dev)
+        for _ in range(3):
+            if which == "packbits":
+                ops.packbits_batch_major(t, 64)
+            else:
+                ops.threshold_packbits_batch_major(t, (63, 127, 191), 64)
     elif which in ("fwd", "bw", "bx", "bwadam", "head", "fwdhead"):
         batch = int(argv[1]) if len(argv) > 1 else 128
         n = int(argv[2]) if len(argv) > 2 else 16000
@@ -850,6 +865,8 @@ def run_case(argv):
                 ops.logic_backward_w_adam(x, a, b, gy, w, m1, m2, state, lr=0.01, beta1=0.9, beta2=0.999, eps=1e-8)
             elif which == "head":
                 ops.groupsum_cross_entropy(x, target, 10, 30.0)
+            elif which == "fwdhead":
+                ops.logic_forward_head(x, a, b, w, target, 10, 30.0)
             elif which == "fwd":
                 ops.logic_forward(x, a, b, w, ops.W_LOGITS, True)
             elif which == "bw":

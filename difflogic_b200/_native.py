@@ -33,8 +33,10 @@ SIGNATURES = {
     "dl_coefs_f32": (_int, [_ptr, _int, _ptr, _i64, _ptr]),
     "dl_backward_w_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _int, _ptr, _i64, _i64, _i64, _int, _ptr]),
     "dl_backward_x_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, _i64, _i64, _i64, _int, _ptr]),
+    "dl_check_connections": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr, _ptr]),
     "dl_build_backward_plan": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr]),
     "dl_eval_packed": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr]),
+    "dl_eval_packed_pitched": (_int, [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr]),
     "dl_argmax_gate_u8": (_int, [_ptr, _ptr, _i64, _ptr]),
     "dl_packbits": (_int, [_ptr, _ptr, _i64, _i64, _int, _ptr]),
     "dl_packbits_batch_major": (_int, [_ptr, _ptr, _i64, _i64, _int, _ptr]),

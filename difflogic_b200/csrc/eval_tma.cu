@@ -47,7 +47,7 @@ template <int kTileRows, int kStages>
 __global__ void __launch_bounds__(kTmaThreads)
 eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
                 const uint8_t *__restrict__ gate, uint8_t *__restrict__ y, uint32_t n_out, int64_t row_bytes, int chunk,
-                uint32_t row_blocks, uint32_t ntiles) {
+                uint32_t row_blocks, uint32_t ntiles, int64_t x_pitch, int64_t y_pitch) {
     extern __shared__ __align__(128) uint8_t smem[];
     const size_t stage_bytes = (size_t)2 * kTileRows * chunk;
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + kStages * stage_bytes);
@@ -113,7 +113,7 @@ eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, co
             if (lane == 0) mbar_arrive_expect_tx(full + s, copies * bytes);
             __syncwarp();
             if (needed)
-                bulk_load(smem + s * stage_bytes + (size_t)(which * kTileRows + r) * chunk, x + idx * row_bytes + col0, bytes,
+                bulk_load(smem + s * stage_bytes + (size_t)(which * kTileRows + r) * chunk, x + idx * x_pitch + col0, bytes,
                           full + s);
             ++issued;
             idx = idx_next;
@@ -154,7 +154,7 @@ eval_tma_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict__ a, co
             const int pitch = chunk / 16;
             for (int r = cw; r < nvalid; r += kConsumerWarps) {
                 const GateMasks gm = gate_masks(meta[s * kTileRows + r]);
-                uint4 *dst = reinterpret_cast<uint4 *>(y + ((int64_t)nb * kTileRows + r) * row_bytes + col0);
+                uint4 *dst = reinterpret_cast<uint4 *>(y + ((int64_t)nb * kTileRows + r) * y_pitch + col0);
 #pragma unroll 4
                 for (int c = lane; c < vecs; c += 32) {
                     const uint4 va = sa[r * pitch + c], vb = sb[r * pitch + c];
@@ -195,7 +195,7 @@ bool eval_tma_applicable(const void *x, const void *y, int64_t row_bytes, int64_
 
 template <int ROWS, int STAGES>
 static int launch_eval_tma_shape(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_out,
-                                 int64_t row_bytes, int ctas_per_sm, cudaStream_t st) {
+                                 int64_t row_bytes, int ctas_per_sm, cudaStream_t st, int64_t x_pitch, int64_t y_pitch) {
     const int chunk = (int)(row_bytes < kMaxChunk ? row_bytes : kMaxChunk);
     const int64_t col_chunks = ceil_div(row_bytes, chunk);
     const int64_t row_blocks = ceil_div(n_out, ROWS);
@@ -207,19 +207,21 @@ static int launch_eval_tma_shape(const void *x, const int64_t *a, const int64_t 
     const unsigned grid = (unsigned)(ntiles < slots ? ntiles : slots);
     eval_tma_kernel<ROWS, STAGES><<<grid, kTmaThreads, smem, st>>>(reinterpret_cast<const uint8_t *>(x), a, b, gate,
                                                                   reinterpret_cast<uint8_t *>(y), (uint32_t)n_out, row_bytes, chunk,
-                                                                  (uint32_t)row_blocks, (uint32_t)ntiles);
+                                                                  (uint32_t)row_blocks, (uint32_t)ntiles, x_pitch, y_pitch);
     return launch_status("dl_eval_packed");
 }
 
+// x_pitch / y_pitch: bytes from one row of x / y to the next (row_bytes for contiguous matrices; larger when the rows
+// are a column slice of wider rows).  Multiples of 16.
 int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_in, int64_t n_out,
-                    int64_t row_bytes, cudaStream_t st) {
+                    int64_t row_bytes, cudaStream_t st, int64_t x_pitch, int64_t y_pitch) {
     // fan-out of an input row: 2 * n_out / n_in.  DL_TUNE_EVAL_SHAPE = 1 (wide) | 2 (square) overrides the choice.
     const int force = tuning(DL_TUNE_EVAL_SHAPE);
     const int64_t chunk = row_bytes < kMaxChunk ? row_bytes : kMaxChunk;
     const bool few_tiles = ceil_div(row_bytes, chunk) * ceil_div(n_out, 16) < (int64_t)64 * sm_count();
     const bool wide = force == 1 ? true : force == 2 ? false : (n_out >= 2 * n_in || few_tiles);
-    if (wide) return launch_eval_tma_shape<8, 3>(x, a, b, gate, y, n_out, row_bytes, 2, st);
-    return launch_eval_tma_shape<16, 2>(x, a, b, gate, y, n_out, row_bytes, 1, st);
+    if (wide) return launch_eval_tma_shape<8, 3>(x, a, b, gate, y, n_out, row_bytes, 2, st, x_pitch, y_pitch);
+    return launch_eval_tma_shape<16, 2>(x, a, b, gate, y, n_out, row_bytes, 1, st, x_pitch, y_pitch);
 }
 
 }  // namespace dl

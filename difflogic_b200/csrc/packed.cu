@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "gates.cuh"
+#include "pack_tile.cuh"
 #include "bitcount.cuh"
 
 namespace dl {
@@ -17,7 +18,7 @@ namespace dl {
 // packed_tma.cu: the same eval with the gathered rows staged in shared memory by bulk copies
 bool eval_tma_applicable(const void *x, const void *y, int64_t row_bytes, int64_t n_out);
 int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y, int64_t n_in, int64_t n_out,
-                    int64_t row_bytes, cudaStream_t st);
+                    int64_t row_bytes, cudaStream_t st, int64_t x_pitch, int64_t y_pitch);
 // groupbitsum_tma.cu: the group bit-sum with rows staged the same way
 bool groupbitsum_tma_applicable(const void *x, int64_t n, int64_t row_bytes, int64_t k);
 int launch_groupbitsum_tma(const void *x, int32_t *out, int64_t n, int64_t row_bytes, int64_t batch, int64_t k, cudaStream_t st);
@@ -131,7 +132,23 @@ packbits_kernel(const uint8_t *__restrict__ t, uint8_t *__restrict__ out, int64_
     }
 }
 
-// packbits from the batch-major matrix t[batch][n]: transpose and pack in one pass.
+// packbits from the batch-major matrix t[batch][n], n % 8 == 0: transpose and pack in one pass, 8-byte loads, bits moved
+// eight by eight (pack_tile.cuh).
+struct MaskNonZero {
+    __device__ __forceinline__ uint32_t operator()(uint32_t lo, uint32_t hi, int) const {
+        return squeeze8_ones(nonzero_bytes(lo), nonzero_bytes(hi));
+    }
+};
+
+__global__ void __launch_bounds__(kThreads)
+packbits_bm8_kernel(const uint8_t *__restrict__ t, uint8_t *__restrict__ out, int64_t n, int64_t batch, int64_t row_bytes) {
+    __shared__ unsigned long long s_words[8 * kPackRow];
+    const int64_t f0 = (int64_t)blockIdx.x * kPackFeatures;
+    for (int64_t sblk = blockIdx.y; sblk * kPackSamples < row_bytes * 8; sblk += gridDim.y)
+        pack_tile<1>(t, out, 0, n, batch, row_bytes, f0, sblk, s_words, MaskNonZero());
+}
+
+// The same for any n (and any alignment): 4-byte or single-byte loads, one bit at a time.
 // A CTA takes 128 features x 512 samples.  Warp w owns 64 samples (one 64-bit word); its lanes
 // each own four adjacent features, read as one 32-bit load per sample (coalesced along the
 // features) and shifted into four words.  The 8 warps' words go through shared memory so that
@@ -340,12 +357,26 @@ extern "C" DL_API int dl_eval_packed(const void *x, const int64_t *a, const int6
     auto fits = [&](int64_t sz) { return row_bytes % sz == 0 && aligned_to(x, sz) && aligned_to(y, sz); };
     // DL_TUNE_EVAL_KERNEL = 1 forces the register-staged kernel (for A/B measurements)
     const bool plain_only = tuning(DL_TUNE_EVAL_KERNEL) == 1;
-    if (!plain_only && eval_tma_applicable(x, y, row_bytes, n_out)) return launch_eval_tma(x, a, b, gate, y, n_in, n_out, row_bytes, st);
+    if (!plain_only && eval_tma_applicable(x, y, row_bytes, n_out)) return launch_eval_tma(x, a, b, gate, y, n_in, n_out, row_bytes, st, row_bytes, row_bytes);
     if (fits(16)) return launch_eval<uint4>(x, a, b, gate, y, n_out, row_bytes, st);
     if (fits(8)) return launch_eval<unsigned long long>(x, a, b, gate, y, n_out, row_bytes, st);
     if (fits(4)) return launch_eval<uint32_t>(x, a, b, gate, y, n_out, row_bytes, st);
     if (fits(2)) return launch_eval<uint16_t>(x, a, b, gate, y, n_out, row_bytes, st);
     return launch_eval<uint8_t>(x, a, b, gate, y, n_out, row_bytes, st);
+}
+
+// dl_eval_packed on column slices: the rows of x and y are `row_bytes` long but lie x_pitch / y_pitch bytes apart (a column
+// range of wider matrices, or contiguous ones with pitch == row_bytes).  Staged kernel only: rows of at least 512 bytes,
+// row_bytes, both pitches and both pointers multiples of 16.
+extern "C" DL_API int dl_eval_packed_pitched(const void *x, int64_t x_pitch, const int64_t *a, const int64_t *b, const uint8_t *gate,
+                                             void *y, int64_t y_pitch, int64_t n_in, int64_t n_out, int64_t row_bytes, void *stream) {
+    DL_REQUIRE(n_in > 0 && n_out > 0 && row_bytes > 0, DL_ERR_INVALID_ARG, "dl_eval_packed_pitched: sizes must be positive");
+    DL_REQUIRE(x && a && b && gate && y, DL_ERR_INVALID_ARG, "dl_eval_packed_pitched: null pointer");
+    DL_REQUIRE(x_pitch >= row_bytes && y_pitch >= row_bytes && x_pitch % 16 == 0 && y_pitch % 16 == 0, DL_ERR_INVALID_ARG,
+               "dl_eval_packed_pitched: pitches must be multiples of 16 and at least row_bytes");
+    DL_REQUIRE(eval_tma_applicable(x, y, row_bytes, n_out), DL_ERR_INVALID_ARG,
+               "dl_eval_packed_pitched: rows must be at least 512 bytes, a multiple of 16 and 16-byte aligned");
+    return launch_eval_tma(x, a, b, gate, y, n_in, n_out, row_bytes, as_stream(stream), x_pitch, y_pitch);
 }
 
 extern "C" DL_API int dl_packbits(const uint8_t *t, void *out, int64_t n, int64_t batch, int bit_count, void *stream) {
@@ -372,7 +403,11 @@ extern "C" DL_API int dl_packbits_batch_major(const uint8_t *t, void *out, int64
     const int64_t sblocks = ceil_div(row_bytes, 64);  // 512 samples each; covers the pad bytes too
     const dim3 grid((unsigned)ceil_div(n, 128), (unsigned)(sblocks < 65535 ? sblocks : 65535));
     uint8_t *o = reinterpret_cast<uint8_t *>(out);
-    if (n % 4 == 0 && aligned_to(t, 4))
+    if (n % 8 == 0 && aligned_to(t, 8)) {
+        const int64_t sb = ceil_div(row_bytes, kPackSamples / 8);
+        const dim3 grid8((unsigned)ceil_div(n, kPackFeatures), (unsigned)(sb < 65535 ? sb : 65535));
+        packbits_bm8_kernel<<<grid8, kThreads, 0, as_stream(stream)>>>(t, o, n, batch, row_bytes);
+    } else if (n % 4 == 0 && aligned_to(t, 4))
         packbits_bm_kernel<true><<<grid, kThreads, 0, as_stream(stream)>>>(t, o, n, batch, row_bytes);
     else
         packbits_bm_kernel<false><<<grid, kThreads, 0, as_stream(stream)>>>(t, o, n, batch, row_bytes);

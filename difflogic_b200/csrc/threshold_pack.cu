@@ -3,13 +3,13 @@
 // The reference's image pipeline turns every pixel into T binary features (pixel / 255 > (i+1) / (T+1)),
 // concatenated threshold-major (experiments/main.py:56-59), then PackBitsTensor transposes and packs the float
 // or bool matrix (difflogic/packbitstensor.py:15-16).  For 2^20 samples that is gigabytes of intermediate bools.
-// Here the uint8 matrix t[batch][n] is read once per threshold (from L2 after the first) and the packed rows
+// Here the uint8 matrix t[batch][n] is read once (for up to four thresholds at a time) and the packed rows
 // out[i*n + f][word] come out directly: bit s of row i*n + f is  t[s][f] > thresholds[i].
 //
-// Same tiling as packbits_bm_kernel: a CTA takes 128 features x 512 samples for one threshold; a warp owns 64
-// samples, its lanes four adjacent features each (one 32-bit load per sample, compared bytewise), the eight
-// warps' words go through shared memory so that a feature's eight words leave as one 64-byte run.
+// n % 8 == 0: the tile packer of pack_tile.cuh (256 features x 512 samples per CTA, 8-byte loads, bits moved eight by
+// eight).  Any other n: the 128 x 512 tiling of packbits_bm_kernel, one threshold per pass, one bit at a time.
 #include "common.cuh"
+#include "pack_tile.cuh"
 
 namespace dl {
 
@@ -17,6 +17,32 @@ constexpr int kMaxThresholds = 16;
 struct Thresholds {
     unsigned char v[kMaxThresholds];
 };
+
+// n % 8 == 0: 8-byte loads, bits moved eight by eight (pack_tile.cuh); NT thresholds per pass over the source
+// (blockIdx.z walks groups of NT thresholds), so the pixels are read once for up to kThresholdsPerPass of them.
+constexpr int kThresholdsPerPass = 4;
+
+template <int NT>
+struct MaskAbove {
+    uint32_t th4[NT];  // the threshold in every byte
+    __device__ __forceinline__ uint32_t operator()(uint32_t lo, uint32_t hi, int i) const {
+        return squeeze8_ones(__vcmpgtu4(lo, th4[i]) & 0x01010101u, __vcmpgtu4(hi, th4[i]) & 0x01010101u);
+    }
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, 2)
+threshold_pack8_kernel(const uint8_t *__restrict__ t, Thresholds thr, int first, uint8_t *__restrict__ out, int64_t n, int64_t batch,
+                       int64_t row_bytes) {
+    __shared__ unsigned long long s_words[8 * kPackRow];
+    const int64_t f0 = (int64_t)blockIdx.x * kPackFeatures;
+    MaskAbove<NT> mask;
+#pragma unroll
+    for (int i = 0; i < NT; ++i) mask.th4[i] = (uint32_t)thr.v[first + i] * 0x01010101u;
+    uint8_t *dst = out + (int64_t)first * n * row_bytes;
+    for (int64_t sblk = blockIdx.y; sblk * kPackSamples < row_bytes * 8; sblk += gridDim.y)
+        pack_tile<NT>(t, dst, n * row_bytes, n, batch, row_bytes, f0, sblk, s_words, mask);
+}
 
 template <bool VEC4>
 __global__ void __launch_bounds__(kThreads)
@@ -87,7 +113,18 @@ extern "C" DL_API int dl_threshold_packbits_batch_major(const uint8_t *t, const 
     const int64_t sblocks = ceil_div(row_bytes, 64);
     const dim3 grid((unsigned)ceil_div(n, 128), (unsigned)(sblocks < 65535 ? sblocks : 65535), (unsigned)n_thresholds);
     uint8_t *o = reinterpret_cast<uint8_t *>(out);
-    if (n % 4 == 0 && aligned_to(t, 4))
+    if (n % 8 == 0 && aligned_to(t, 8)) {
+        const int64_t sb = ceil_div(row_bytes, kPackSamples / 8);
+        const dim3 grid8((unsigned)ceil_div(n, kPackFeatures), (unsigned)(sb < 65535 ? sb : 65535));
+        for (int first = 0; first < n_thresholds; first += kThresholdsPerPass) {
+            switch (n_thresholds - first < kThresholdsPerPass ? n_thresholds - first : kThresholdsPerPass) {
+                case 1: threshold_pack8_kernel<1><<<grid8, kThreads, 0, as_stream(stream)>>>(t, thr, first, o, n, batch, row_bytes); break;
+                case 2: threshold_pack8_kernel<2><<<grid8, kThreads, 0, as_stream(stream)>>>(t, thr, first, o, n, batch, row_bytes); break;
+                case 3: threshold_pack8_kernel<3><<<grid8, kThreads, 0, as_stream(stream)>>>(t, thr, first, o, n, batch, row_bytes); break;
+                default: threshold_pack8_kernel<4><<<grid8, kThreads, 0, as_stream(stream)>>>(t, thr, first, o, n, batch, row_bytes); break;
+            }
+        }
+    } else if (n % 4 == 0 && aligned_to(t, 4))
         threshold_pack_kernel<true><<<grid, kThreads, 0, as_stream(stream)>>>(t, thr, o, n, batch, row_bytes);
     else
         threshold_pack_kernel<false><<<grid, kThreads, 0, as_stream(stream)>>>(t, thr, o, n, batch, row_bytes);

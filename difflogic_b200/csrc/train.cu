@@ -429,6 +429,62 @@ build_plan_kernel(const int64_t *__restrict__ a, const int64_t *__restrict__ b, 
     }
 }
 
+// Every kernel of this library trusts a layer's index arrays: they are fixed when the layer is built, so they are checked
+// once, there, instead of on every access.  report: {code, where, value, limit}; the first violation found wins (atomicCAS
+// on the code), nothing is accessed through a bad index.  Codes: 1 a[j] or b[j] outside [0, n_in); 2 start[] not
+// 0 = start[0] <= ... <= start[n_in] = 2 n_out; 3 list entry outside [0, n_out); 4 plan entry outside its range;
+// 5 plan entry does not match the connections (the neuron's input in that slot is not the row that lists it, or the
+// partner row is not the neuron's other input).
+__device__ __forceinline__ void report_violation(int64_t *report, int64_t code, int64_t where, int64_t value, int64_t limit) {
+    if (atomicCAS(reinterpret_cast<unsigned long long *>(report), 0ull, (unsigned long long)code) == 0ull) {
+        report[1] = where;
+        report[2] = value;
+        report[3] = limit;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+check_connections_kernel(const int64_t *__restrict__ a, const int64_t *__restrict__ b, const int64_t *__restrict__ start,
+                         const int64_t *__restrict__ list, const int2 *__restrict__ plan, int64_t n_in, int64_t n_out,
+                         int64_t *__restrict__ report, int phase) {
+    // One launch per phase, in the order of the codes, each phase only when the ones before found nothing: what is
+    // reported is the violation with the lowest code, and a later phase may rely on what the earlier ones established.
+    if (*reinterpret_cast<volatile int64_t *>(report) != 0) return;
+    if (phase == 1) start = nullptr, list = nullptr, plan = nullptr;
+    if (phase == 2) list = nullptr, plan = nullptr;
+    if (phase == 3) start = nullptr, plan = nullptr;
+    if (phase == 4) list = nullptr;
+    const bool connections = phase == 1, offsets = phase == 2;
+    const int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (connections && t < n_out) {
+        if (a[t] < 0 || a[t] >= n_in) report_violation(report, 1, t, a[t], n_in);
+        if (b[t] < 0 || b[t] >= n_in) report_violation(report, 1, t, b[t], n_in);
+    }
+    if (offsets && start != nullptr && t <= n_in) {
+        const int64_t v = start[t];
+        if (v < 0 || v > 2 * n_out || (t == 0 && v != 0) || (t == n_in && v != 2 * n_out) || (t > 0 && start[t - 1] > v))
+            report_violation(report, 2, t, v, 2 * n_out);
+    }
+    if (list != nullptr && t < 2 * n_out && (list[t] < 0 || list[t] >= n_out)) report_violation(report, 3, t, list[t], n_out);
+    if (plan != nullptr && start != nullptr && t < n_in) {
+        // the entries of input row t, as far as start[] can be trusted
+        const int64_t e0 = start[t], e1 = start[t + 1];
+        if (e0 >= 0 && e0 <= e1 && e1 <= 2 * n_out) {
+            for (int64_t e = e0; e < e1; ++e) {
+                const int2 p = plan[e];
+                const int64_t j = p.x >> 1;
+                const int slot = p.x & 1;
+                if (p.x < 0 || j >= n_out || p.y < 0 || p.y >= n_in) {
+                    report_violation(report, 4, e, p.x < 0 || j >= n_out ? p.x : p.y, p.x < 0 || j >= n_out ? 2 * n_out : n_in);
+                } else {
+                    const int64_t mine = slot ? b[j] : a[j], other = slot ? a[j] : b[j];
+                    if (mine != t || other != p.y) report_violation(report, 5, e, j, t);
+                }
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -680,6 +736,22 @@ extern "C" DL_API int dl_backward_x_classes_f32(const float *x, const float *coe
                                                 const int32_t *plan, float grad_scale, float *grad_x, int64_t n_in, int64_t n_out,
                                                 int64_t batch, int64_t rows_per_class, int flags, void *stream) {
     return backward_x_entry(x, coef, grad_y_classes, start, plan, grad_scale, grad_x, n_in, n_out, batch, rows_per_class, flags, stream);
+}
+
+// Checks a layer's index arrays on the device (see check_connections_kernel).  start, list and plan may be null (only a
+// and b are checked then).  report: four int64 on the device, zeroed by the caller; stays zero when everything is sound.
+extern "C" DL_API int dl_check_connections(const int64_t *a, const int64_t *b, const int64_t *start, const int64_t *list,
+                                           const int32_t *plan, int64_t n_in, int64_t n_out, int64_t *report, void *stream) {
+    DL_REQUIRE(n_in >= 0 && n_out >= 0, DL_ERR_INVALID_ARG, "dl_check_connections: negative size");
+    DL_REQUIRE(report != nullptr && aligned_to(report, 8), DL_ERR_INVALID_ARG, "dl_check_connections: report must be 8-byte aligned");
+    if (n_out == 0 && n_in == 0) return DL_OK;
+    DL_REQUIRE(n_out == 0 || (a && b), DL_ERR_INVALID_ARG, "dl_check_connections: null pointer");
+    DL_REQUIRE(plan == nullptr || aligned_to(plan, 8), DL_ERR_INVALID_ARG, "dl_check_connections: plan must be 8-byte aligned");
+    int64_t most = 2 * n_out > n_in + 1 ? 2 * n_out : n_in + 1;
+    for (int phase = 1; phase <= 4; ++phase)
+        check_connections_kernel<<<(unsigned)ceil_div(most, kThreads), kThreads, 0, as_stream(stream)>>>(
+            a, b, start, list, reinterpret_cast<const int2 *>(plan), n_in, n_out, report, phase);
+    return launch_status("dl_check_connections");
 }
 
 extern "C" DL_API int dl_build_backward_plan(const int64_t *a, const int64_t *b, const int64_t *start, const int64_t *list,

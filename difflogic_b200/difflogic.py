@@ -26,6 +26,12 @@ from .packbitstensor import PackBitsTensor
 _backward_w_stream = None
 
 
+# DIFFLOGIC_DEBUG=1: every CUDA LogicLayer checks its index tensors on the device when they are set (the kernels trust
+# them afterwards); read once, at import.
+import os as _os
+_DEBUG_CHECKS = _os.environ.get("DIFFLOGIC_DEBUG", "0") == "1"
+
+
 def set_backward_w_stream(stream):
     """Sets (or, with None, clears) the CUDA stream on which LogicLayer's backward_w kernels are launched."""
     global _backward_w_stream
@@ -109,7 +115,11 @@ class LogicLayer(torch.nn.Module):
         a, b = self.indices
         self.given_x_indices_of_y_start, self.given_x_indices_of_y = ops.inverse_index(a, b, self.in_dim)
         if a.is_cuda:
+            if _DEBUG_CHECKS:
+                ops.check_connections(a, b, self.in_dim)      # before anything is computed from them
             self._plan = ops.build_backward_plan(a, b, self.given_x_indices_of_y_start, self.given_x_indices_of_y)
+            if _DEBUG_CHECKS:
+                ops.check_connections(a, b, self.in_dim, self.given_x_indices_of_y_start, self.given_x_indices_of_y, self._plan)
             # the layer's kernels may read these index tensors ahead of the kernel that precedes them in the
             # stream (DL_LAUNCH_OVERLAP_SETUP), so they must be final before any such launch is queued
             torch.cuda.current_stream(a.device).synchronize()

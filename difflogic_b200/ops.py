@@ -184,6 +184,34 @@ def build_backward_plan(a, b, start, lst):
     return plan
 
 
+_VIOLATIONS = {1: "connection index outside [0, in_dim)", 2: "inverse-index offsets are not 0 = start[0] <= ... <= start[in_dim] = 2 * out_dim",
+               3: "inverse-index entry outside [0, out_dim)", 4: "gather-plan entry out of range",
+               5: "gather-plan entry does not match the connections"}
+
+
+def check_connections(a, b, n_in, start=None, lst=None, plan=None):
+    """Checks a layer's index tensors on the device (dl_check_connections) and raises ValueError with the first violation
+    found.  Synchronises; meant for construction time and debugging, not for the hot path."""
+    n_out = a.numel()
+    _index(a, "a")
+    _index(b, "b", n_out)
+    if start is not None:
+        _index(start, "start", n_in + 1)
+    if lst is not None:
+        _index(lst, "list", 2 * n_out)
+    if plan is not None:
+        _need(plan.is_cuda and plan.dtype == torch.int32 and plan.is_contiguous() and tuple(plan.shape) == (2 * n_out, 2),
+              "plan must be a contiguous int32 [2*n_out, 2] tensor")
+    report = torch.zeros(4, dtype=torch.int64, device=a.device)
+    with torch.cuda.device(a.device):
+        N.check(N.lib().dl_check_connections(a.data_ptr(), b.data_ptr(), N.ptr(start), N.ptr(lst), N.ptr(plan), int(n_in), n_out,
+                                             report.data_ptr(), N.stream_of(a)))
+    code, where, value, limit = report.tolist()
+    if code != 0:
+        raise ValueError("difflogic_b200: %s (position %d, value %d, limit %d)" % (_VIOLATIONS.get(code, "violation %d" % code),
+                                                                                 where, value, limit))
+
+
 def logic_backward_x(x, coef, grad_y, start, plan, grad_scale=1.0, overlap=False, rows_per_class=1):
     """Gradient w.r.t. the layer's input.  rows_per_class > 1: grad_y holds one row per class (see logic_backward_w)."""
     _f32_matrix(x, "x")

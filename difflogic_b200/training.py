@@ -28,7 +28,10 @@ class TrainStep:
         :param loss_fn:       defaults to CrossEntropyLoss (mean over the local batch)
         :param process_group: torch.distributed group to average gradients over, or None
         :param fuse_head:     when the model ends in GroupSum and the loss is a default CrossEntropyLoss, run the two
-                              as one autograd node (same numbers, three kernels instead of five)
+                              as one autograd node (same numbers, three kernels instead of five).  The fused
+                              kernels take class-index targets in [0, k) only: they have no `ignore_index`
+                              (torch's default -100 included), and a target outside the range would count as
+                              "no class".  The targets of the first eager step are checked, once, on the host.
         :param step_in_backward: single GPU, FlatAdam, every parameter a CUDA LogicLayer's weights: the Adam update runs
                               in the epilogue of each layer's backward_w kernel instead of a kernel of its own after
                               the backward pass (same numbers; `.grad` is then not populated)
@@ -63,6 +66,7 @@ class TrainStep:
             last = self._body[-1] if len(self._body) > 0 else None
             if isinstance(last, LogicLayer) and getattr(last, "implementation", None) == "cuda":
                 self._pre, self._last = self._body[:-1], last   # everything before the last logic layer, and that layer
+        self._targets_checked = False
         self._in_backward = False
         if (step_in_backward and self._on_gpu and self.world_size == 1 and not self._exchange_in_optimizer
                 and hasattr(optimizer, "enable_step_in_backward") and self._all_logic_weights(model, optimizer)):
@@ -96,8 +100,20 @@ class TrainStep:
         return (type(loss_fn) is torch.nn.CrossEntropyLoss and loss_fn.weight is None and loss_fn.reduction == "mean"
                 and loss_fn.ignore_index == -100 and loss_fn.label_smoothing == 0.0)
 
+    def _check_targets_once(self, y):
+        """The fused head has no ignore_index: the first batch of targets that is seen outside a graph capture must
+        lie in [0, k) (one host synchronisation, once)."""
+        if self._targets_checked or not y.is_cuda or torch.cuda.is_current_stream_capturing():
+            return
+        self._targets_checked = True
+        k = int(self._head.k)
+        if y.numel() and (int(y.min()) < 0 or int(y.max()) >= k):
+            raise ValueError("TrainStep: targets must be class indices in [0, %d); the fused GroupSum + cross-entropy head "
+                             "implements no ignore_index (pass fuse_head=False to use the loss module as it is)" % k)
+
     def _loss(self, x, y):
         if self._head is not None:
+            self._check_targets_once(y)
             if self._last is not None:
                 # last layer + GroupSum + loss as one autograd node
                 from .difflogic import logic_layer_head

@@ -143,6 +143,16 @@ DL_API int dl_backward_x_f32(const float *x, const float *coef, const float *gra
 DL_API int dl_build_backward_plan(const int64_t *a, const int64_t *b, const int64_t *start, const int64_t *list,
                            int32_t *plan, int64_t n_in, int64_t n_out, void *stream);
 
+/* Debug aid: checks a layer's index arrays on the device, once, instead of bounds checks on every access (the arrays
+ * are fixed when a layer is built, and every kernel here trusts them).  Checked: a[j], b[j] in [0, n_in);
+ * 0 = start[0] <= ... <= start[n_in] = 2 n_out; list entries in [0, n_out); plan entries in range and consistent with
+ * a and b.  start, list, plan may be NULL.  report: four int64 on the device, zeroed by the caller:
+ * {code (0 = sound), position, offending value, limit}; nothing is read through an unchecked index and nothing traps.
+ * The reference checks only contiguity and device of its tensors (CHECK_INPUT, difflogic_kernel.cu:13-17); an index
+ * out of range there is an out-of-bounds access.  LogicLayer runs this check at construction when DIFFLOGIC_DEBUG=1. */
+DL_API int dl_check_connections(const int64_t *a, const int64_t *b, const int64_t *start, const int64_t *list,
+                                const int32_t *plan, int64_t n_in, int64_t n_out, int64_t *report, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Packed-bit eval.
  * Replaces logic_layer_cuda_eval, difflogic_kernel.cu:503-541 (kernel :474-501, gates
@@ -152,6 +162,13 @@ DL_API int dl_build_backward_plan(const int64_t *a, const int64_t *b, const int6
  * ---------------------------------------------------------------------------------------- */
 DL_API int dl_eval_packed(const void *x, const int64_t *a, const int64_t *b, const uint8_t *gate, void *y,
                    int64_t n_in, int64_t n_out, int64_t words, int bit_count, void *stream);
+
+/* dl_eval_packed on column slices: the rows of x and y are row_bytes long but lie x_pitch / y_pitch bytes apart (a
+ * column range of wider matrices; pitch == row_bytes for contiguous ones).  For running a network over a batch in
+ * slices whose activations stay in the L2 cache while the packed input and the counts stay whole.  Rows of at least
+ * 512 bytes; row_bytes, pitches and pointers multiples of 16 (else DL_ERR_INVALID_ARG).  Same kernel, same results. */
+DL_API int dl_eval_packed_pitched(const void *x, int64_t x_pitch, const int64_t *a, const int64_t *b, const uint8_t *gate,
+                                  void *y, int64_t y_pitch, int64_t n_in, int64_t n_out, int64_t row_bytes, void *stream);
 
 /* argmax over the 16 gate weights -> uint8 gate id, first maximum on ties
  * (weights.argmax(-1).to(uint8), difflogic/difflogic.py:146). */
@@ -334,6 +351,11 @@ DL_API int dl_groupsum_cross_entropy_backward_f32(const float *probs, const int6
  *   p = p - lr / (1 - beta1^t) * m / (sqrt(v) / sqrt(1 - beta2^t) + eps),     g = grad * grad_scale
  * state is two int32 on the device: {t (steps done so far), 0}; the kernel advances t, so the
  * launch can be replayed from a CUDA graph.  All buffers 16-byte aligned.
+ * The kernel is launched with programmatic stream serialisation and reads param, exp_avg, exp_avg_sq and
+ * state BEFORE it waits for the kernel in front of it in the stream; only grad is read after that wait.
+ * The caller promises that the kernel just before this one in the stream writes none of the four (in a
+ * training step it is a backward kernel, which writes gradients only).  dl_backward_w_adam_f32 makes the
+ * same assumption for exp_avg, exp_avg_sq and state (w itself is read after the wait).
  * ---------------------------------------------------------------------------------------- */
 DL_API int dl_adam_step_f32(float *param, const float *grad, float *exp_avg, float *exp_avg_sq, int64_t n, float lr,
                             float beta1, float beta2, float eps, float grad_scale, int32_t *state, void *stream);

@@ -286,3 +286,35 @@ def test_thermometer_packing_from_uint8_images(bits, shape):
     p = D.PackBitsTensor.from_uint8_thresholds(img.cuda(), (63, 127, 191), bit_count=bits)
     assert p.pad_len == ref_pad and p.bit_count == bits
     assert np.array_equal(p.t.cpu().numpy(), ref)
+
+
+# ------------------------------------------------------------------------------------------------
+# index checks (debug aid)
+# ------------------------------------------------------------------------------------------------
+def test_check_connections_accepts_a_sound_layer_and_names_the_first_violation():
+    a, b, _ = random_layer(30, 64, seed=9, force_same_input=True)
+    ad, bd = _dev(a), _dev(b)
+    start, lst = ops.inverse_index(ad, bd, 30)
+    plan = ops.build_backward_plan(ad, bd, start, lst)
+    ops.check_connections(ad, bd, 30)
+    ops.check_connections(ad, bd, 30, start, lst, plan)
+    bad = ad.clone()
+    bad[5] = 30                                               # one past the last input row
+    with pytest.raises(ValueError, match="outside"):
+        ops.check_connections(bad, bd, 30)
+    bad_start = start.clone()
+    bad_start[7] = bad_start[6] - 1                           # offsets must not decrease
+    with pytest.raises(ValueError, match="offsets"):
+        ops.check_connections(ad, bd, 30, bad_start, lst, plan)
+    bad_list = lst.clone()
+    bad_list[3] = 64
+    with pytest.raises(ValueError, match="entry outside"):
+        ops.check_connections(ad, bd, 30, start, bad_list, plan)
+    bad_plan = plan.clone()
+    bad_plan[10, 1] = (int(bad_plan[10, 1]) + 1) % 30         # a partner row that is not the neuron's other input
+    with pytest.raises(ValueError, match="does not match"):
+        ops.check_connections(ad, bd, 30, start, lst, bad_plan)
+    bad_plan = plan.clone()
+    bad_plan[0, 0] = 2 * 64 + 1                               # a neuron that does not exist: reported, not dereferenced
+    with pytest.raises(ValueError, match="out of range"):
+        ops.check_connections(ad, bd, 30, start, lst, bad_plan)
