@@ -44,9 +44,6 @@ SIGNATURES = {
     "dl_groupbitsum": (_int, [_ptr, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
     "dl_eval_groupbitsum_applicable": (_int, [_ptr, _i64, _i64, _i64, _int, _i64]),
     "dl_eval_groupbitsum": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _i64, _int, _ptr]),
-    "dl_pack_net_layer": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr]),
-    "dl_eval_net_shared_bytes": (ctypes.c_size_t, [_ptr, _int]),
-    "dl_eval_net_packed": (_int, [_ptr, _ptr, _ptr, _int, _ptr, _i64, _i64, _i64, _int, _ptr]),
     "dl_groupsum_workspace_bytes": (ctypes.c_size_t, [_i64, _i64, _i64]),
     "dl_groupsum_f32": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),
     "dl_groupsum_backward_f32": (_int, [_ptr, _ptr, _i64, _i64, _i64, _f32, _ptr]),

@@ -213,15 +213,6 @@ class LogicLayer(torch.nn.Module):
             self._gate_cache = cached
         return cached[1]
 
-    def _packed_descriptors(self, gate):
-        """uint32 {a:14 | b:14 | gate:4} per neuron for the whole-network eval kernel, cached per gate tensor."""
-        cached = getattr(self, '_desc_cache', None)
-        if cached is None or cached[0] is not gate:
-            a, b = self.indices
-            cached = (gate, ops.pack_net_layer(a, b, gate, self.in_dim))
-            self._desc_cache = cached
-        return cached[1]
-
     def extra_repr(self):
         return '{}, {}, {}'.format(self.in_dim, self.out_dim, 'train' if self.training else 'eval')
 

@@ -380,57 +380,6 @@ def eval_groupbitsum(x, a, b, gate, pad_len, k):
 
 
 # ------------------------------------------------------------------------------------------------
-# whole-network packed inference
-# ------------------------------------------------------------------------------------------------
-
-FUSED_NET_MAX_WIDTH = 16384
-FUSED_NET_MAX_SHARED = 220 * 1024
-
-
-def pack_net_layer(a, b, gate, n_in):
-    """uint32 descriptors {a:14 | b:14 | gate:4} of one layer, padded to a multiple of four."""
-    n_out = gate.numel()
-    _index(a, "a", n_out)
-    _index(b, "b", n_out)
-    _need(gate.dtype == torch.uint8 and gate.is_cuda and gate.is_contiguous(), "gate must be a contiguous CUDA uint8 vector")
-    meta = torch.empty(((n_out + 3) // 4 * 4,), dtype=torch.int32, device=a.device)
-    with torch.cuda.device(a.device):
-        N.check(N.lib().dl_pack_net_layer(a.data_ptr(), b.data_ptr(), gate.data_ptr(), meta.data_ptr(), n_in, n_out,
-                                          N.stream_of(a)))
-    return meta
-
-
-def fused_net_fits(widths, row_bytes):
-    """True when a net with these widths (input rows first) can run in the single fused kernel."""
-    import ctypes
-    if row_bytes % 8 != 0 or len(widths) < 2 or len(widths) > 33 or max(widths) > FUSED_NET_MAX_WIDTH:
-        return False
-    arr = (ctypes.c_int64 * len(widths))(*widths)
-    return N.lib().dl_eval_net_shared_bytes(ctypes.addressof(arr), len(widths) - 1) <= FUSED_NET_MAX_SHARED
-
-
-def eval_net_packed(x, metas, widths, pad_len, k):
-    """Packed input x [widths[0], words] through all layers (descriptor tensors `metas`, see pack_net_layer) and the
-    group bit-sum: int32 [batch, k], identical to running eval_packed per layer and groupbitsum."""
-    import ctypes
-    N.require_cuda(x)
-    _need(x.dim() == 2 and x.is_contiguous() and x.shape[0] == widths[0], "x must be a contiguous [widths[0], words] tensor")
-    bits = bits_of(x)
-    words = x.shape[1]
-    k = int(k)
-    if k <= 0 or widths[-1] % k != 0:
-        raise ValueError("in_dim (%d) has to be divisible by k (%d) but it is not" % (widths[-1], k))
-    meta = metas[0] if len(metas) == 1 else torch.cat(metas)
-    batch = words * bits - int(pad_len)
-    out = torch.empty((batch, k), dtype=torch.int32, device=x.device)
-    arr = (ctypes.c_int64 * len(widths))(*widths)
-    with torch.cuda.device(x.device):
-        N.check(N.lib().dl_eval_net_packed(x.data_ptr(), meta.data_ptr(), ctypes.addressof(arr), len(widths) - 1,
-                                           out.data_ptr(), words, int(pad_len), k, bits, N.stream_of(x)))
-    return out
-
-
-# ------------------------------------------------------------------------------------------------
 # float GroupSum
 # ------------------------------------------------------------------------------------------------
 

@@ -6,14 +6,11 @@ high bits in the last word, sample s being bit s % bit_count (LSB first) of word
 
 Evaluation is lazy.  A LogicLayer in eval mode does not compute at once; it appends itself to the
 tensor's list of pending layers.  Reading `.t` runs the pending layers one kernel per layer, exactly
-as the reference does.  `group_sum(k)` -- what GroupSum calls -- hands the packed input, all pending
-layers and the bit-sum to ONE kernel when the network fits it (ops.eval_net_packed: activations stay
-in shared memory), and otherwise falls back to layer by layer.  Both give identical counts; the
-in-place semantics of the reference (the layer returns the same object, `.t` then holds the layer's
-output) are kept.  The single-kernel path is opt-in (module switch FUSED_NET; DL_FUSED_EVAL=1 in the environment
-when the module is imported): on B200 it is bound by
-shared-memory bank conflicts of the random 8-byte gathers (measured 0.9 gates per clock and SM) and is slower
-than the layer-by-layer path, which already runs at 80-90 % of the HBM copy bandwidth.
+as the reference does.  `group_sum(k)` -- what GroupSum calls -- runs all pending layers but the last
+one kernel each and hands the last layer together with the bit-sum to ONE kernel that never stores the
+layer's output (ops.eval_groupbitsum) when the sizes are in that kernel's range.  The counts are
+identical either way; the in-place semantics of the reference (the layer returns the same object, `.t`
+then holds the layer's output) are kept.
 """
 import os
 
@@ -23,8 +20,7 @@ import torch
 from . import ops
 
 
-# Module switches, read from the environment once at import (set the attributes to change them afterwards).
-FUSED_NET = os.environ.get("DL_FUSED_EVAL", "0") == "1"                # all layers + bit-sum in ONE kernel (opt-in)
+# Module switch, read from the environment once at import (set the attribute to change it afterwards).
 FUSED_LAST_LAYER = os.environ.get("DL_FUSED_LAST_LAYER", "1") != "0"   # last layer + bit-sum in one kernel
 
 
@@ -92,12 +88,6 @@ class PackBitsTensor:
 
     def group_sum(self, k):
         assert torch.device(self.device).type == 'cuda', self.device
-        if self._pending and FUSED_NET:
-            widths = [self._t.shape[0]] + [layer.out_dim for layer, _ in self._pending]
-            row_bytes = self._t.shape[1] * self._t.element_size()
-            if ops.fused_net_fits(widths, row_bytes):
-                metas = [layer._packed_descriptors(gate) for layer, gate in self._pending]
-                return ops.eval_net_packed(self._t, metas, widths, self.pad_len, k)
         if self._pending and FUSED_LAST_LAYER:
             # all layers but the last run now; the last one is counted as it is computed, its output never stored
             (layer, gate) = self._pending.pop()

@@ -221,24 +221,6 @@ DL_API int dl_eval_groupbitsum(const void *x, const int64_t *a, const int64_t *b
                                void *stream);
 
 /* ------------------------------------------------------------------------------------------
- * Whole-network packed-bit inference in one launch: every logic layer and the group bit-sum, the
- * activations of a 64-sample block staying in shared memory.  Replaces the chain
- * model(PackBitsTensor) of experiments/main.py:198-210, i.e. one logic_layer_cuda_eval per layer
- * (difflogic_kernel.cu:503-541) followed by groupbitsum (:666-700); bit-identical results.
- *
- * dl_pack_net_layer packs one layer's connections and gate ids into descriptors
- * {a:14 | b:14 | gate:4} (uint32, padded to a multiple of 4 per layer); `meta` of dl_eval_net_packed
- * is the layers' descriptor arrays one after the other.  widths is a HOST array of n_layers+1
- * numbers: input rows, then the gates of each layer.  Limits: every width <= 16384;
- * dl_eval_net_shared_bytes(widths, n_layers) <= 220 KiB; rows a multiple of 8 bytes; widths[L] % k == 0.
- * ---------------------------------------------------------------------------------------- */
-DL_API int dl_pack_net_layer(const int64_t *a, const int64_t *b, const uint8_t *gate, uint32_t *meta, int64_t n_in,
-                             int64_t n_out, void *stream);
-DL_API size_t dl_eval_net_shared_bytes(const int64_t *widths, int n_layers);
-DL_API int dl_eval_net_packed(const void *x, const uint32_t *meta, const int64_t *widths, int n_layers, int32_t *out,
-                              int64_t words, int64_t pad_len, int64_t k, int bit_count, void *stream);
-
-/* ------------------------------------------------------------------------------------------
  * Float GroupSum, forward and backward, on the feature-major activation of the last layer.
  * Replaces the torch expression of GroupSum.forward, difflogic/difflogic.py:195-196
  * (reshape -> sum -> / tau) and its autograd.

@@ -321,34 +321,49 @@ def test_cross_entropy_matches_torch(shape):
 
 
 @pytest.mark.parametrize("case", [
-    # dims, k, batch, bit_count
-    ([100, 640, 640, 320], 10, 5000, 64),
-    ([784, 8000, 8000, 8000, 8000], 10, 1000, 64),
-    ([33, 50, 70, 36], 3, 777, 64),          # ragged widths (not multiples of 4), words not a multiple of 4
-    ([20, 48], 4, 130, 64),                  # a single layer
-    ([64, 128, 96], 2, 4096 + 64, 32),       # 32-bit words (rows a multiple of 8 bytes)
-    ([64, 128, 96], 96, 300, 64),            # more classes than warps per round
-    ([16, 13000, 13000, 9000], 1, 200, 64),   # close to the shared-memory limit, a single class
+    ([100, 640, 640, 320], 10, 64 * 64 * 3, 64),     # 192 words per row, slices of 64 words (512-byte rows)
+    ([784, 2000, 2000], 10, 64 * 128 * 3, 128),              # 384 words per row, slices of 128 words
 ])
-def test_whole_network_packed_kernel_equals_layer_by_layer(case, monkeypatch):
-    dims, k, batch, bits = case
+def test_network_over_column_slices_equals_the_whole_batch(case):
+    """dl_eval_packed_pitched: the first layer reads a column slice of the packed input in place and writes a small
+    buffer, the other layers run on small buffers, the counts of a slice land in their rows of the whole result.  This
+    is how a batch is processed in pieces without copying the input; the counts must equal the one-piece run."""
+    from difflogic_b200 import _native as N, ops
+    dims, k, batch, slice_words = case
     torch.manual_seed(sum(dims) + k)
     net = O.OracleNet.build(dims, k, 1.0)
     model = build_model(dims, k, 1.0, net.weights, net.idx_a, net.idx_b)
     model.eval()
     x = torch.rand(batch, dims[0]) < 0.4
-    from difflogic_b200 import ops
-    row_bytes = -(-batch // bits) * bits // 8
-    assert ops.fused_net_fits(dims, row_bytes) == (row_bytes % 8 == 0)
+    packed = D.PackBitsTensor(x.cuda(), bit_count=64)
+    words0, W = packed.t, packed.t.shape[1]
     with torch.no_grad():
-        monkeypatch.setattr(D.packbitstensor, "FUSED_NET", True)
-        fused = model(D.PackBitsTensor(x.cuda(), bit_count=bits))
-        monkeypatch.setattr(D.packbitstensor, "FUSED_NET", False)
-        layerwise = model(D.PackBitsTensor(x.cuda(), bit_count=bits))
-    assert torch.equal(fused, layerwise)
-    if batch <= 1000:
-        ref = O.c_packed_net_counts(x.numpy(), net.idx_a, net.idx_b, net.gate_ids(), k)
-        assert np.array_equal(fused.cpu().numpy(), ref)
+        whole = model(D.PackBitsTensor(x.cuda(), bit_count=64))
+    layers = logic_layers(model)
+    gates = [l._gate_ids() for l in layers]
+    lib, st = N.lib(), torch.cuda.current_stream().cuda_stream
+    counts = torch.full((batch, k), -1, dtype=torch.int32, device="cuda")
+    width = max(dims[1:])
+    bufs = [torch.empty(width * slice_words, dtype=torch.int64, device="cuda") for _ in range(2)]
+    assert W % slice_words == 0
+    for si in range(W // slice_words):
+        l = layers[0]
+        N.check(lib.dl_eval_packed_pitched(words0.data_ptr() + si * slice_words * 8, W * 8, l.indices[0].data_ptr(),
+                                           l.indices[1].data_ptr(), gates[0].data_ptr(), bufs[0].data_ptr(), slice_words * 8,
+                                           l.in_dim, l.out_dim, slice_words * 8, st))
+        cur = bufs[0][:layers[0].out_dim * slice_words].view(layers[0].out_dim, slice_words)
+        for i, l in enumerate(layers[1:], start=1):
+            nxt = bufs[i % 2][:l.out_dim * slice_words].view(l.out_dim, slice_words)
+            cur = ops.eval_packed(cur, l.indices[0], l.indices[1], gates[i], out=nxt)
+        counts[si * slice_words * 64:(si + 1) * slice_words * 64] = ops.groupbitsum(cur, 0, k)
+    assert torch.equal(counts, whole)
+    # a pitch below the row length, or not a multiple of 16, is refused before anything is launched
+    l = layers[0]
+    args = (l.indices[0].data_ptr(), l.indices[1].data_ptr(), gates[0].data_ptr(), bufs[0].data_ptr())
+    assert lib.dl_eval_packed_pitched(words0.data_ptr(), slice_words * 8 - 16, *args, slice_words * 8, l.in_dim, l.out_dim,
+                                      slice_words * 8, st) == N.DL_ERR_INVALID_ARG
+    assert lib.dl_eval_packed_pitched(words0.data_ptr(), W * 8 + 8, *args, slice_words * 8, l.in_dim, l.out_dim,
+                                      slice_words * 8, st) == N.DL_ERR_INVALID_ARG
 
 
 def test_packbitstensor_is_lazy_but_keeps_the_in_place_contract():
