@@ -130,12 +130,11 @@ exchange_bucket_kernel(ExchangePeers peers, int rank, int world, float *__restri
     grid_dependency_wait();  // this rank's gradients come from the kernel just before (when launched right behind it)
     if (blockIdx.x == 0 && threadIdx.x == 0) stamps[0] = global_timer_ns();
     // announce, unless the kernel that wrote the gradients has done it (dl_backward_w_announce_f32): this rank's
-    // gradients of the bucket were written by kernels that completed before this point; the fence orders them before
-    // the flag for observers on other GPUs
-    if (announce_here && blockIdx.x == 0 && (int)threadIdx.x < world) {
-        __threadfence_system();
+    // gradients of the bucket were written by kernels that completed before this point; the release store (system scope)
+    // orders them before the flag for observers on other GPUs.  (A separate system-scope fence in front of it was
+    // redundant and cost microseconds on the only path nothing hides.)
+    if (announce_here && blockIdx.x == 0 && (int)threadIdx.x < world)
         st_release_sys(peers.flags[threadIdx.x] + flag_index(bucket, rank, 0), epoch);
-    }
     const bool ok_a = wait_peers(peers.flags[rank], world, bucket, 0, epoch, wait_us);  // ends with a block barrier
     if (blockIdx.x == 0 && threadIdx.x == 0) stamps[1] = global_timer_ns();
 
@@ -215,7 +214,8 @@ exchange_bucket_kernel(ExchangePeers peers, int rank, int world, float *__restri
         if ((all & 0xffff) == (int)gridDim.x) {
             state[1] = 0;
             if ((all >> 16) == 0) {
-                __threadfence_system();
+                // the ticket (atomic + GPU-scope fences) has ordered every block's stores before this thread; its release
+                // stores at system scope pass that on to the peers
                 stamps[2] = global_timer_ns();
                 for (int p = 0; p < world; ++p) st_release_sys(peers.flags[p] + flag_index(bucket, rank, 1), epoch);
                 s_last_and_sound = 1;
@@ -296,10 +296,7 @@ exchange_bucket_kernel(ExchangePeers peers, int rank, int world, float *__restri
 // Announces this rank's gradients of a bucket when no backward_w kernel did it (dl_backward_w_announce_f32 does it from
 // its last block): one thread per rank stores the bucket's next epoch into that rank's flag words.
 __global__ void exchange_announce_kernel(ExchangePeers peers, int rank, int world, int bucket, const int *__restrict__ state) {
-    if ((int)threadIdx.x < world) {
-        __threadfence_system();
-        st_release_sys(peers.flags[threadIdx.x] + flag_index(bucket, rank, 0), state[0] + 1);
-    }
+    if ((int)threadIdx.x < world) st_release_sys(peers.flags[threadIdx.x] + flag_index(bucket, rank, 0), state[0] + 1);
 }
 
 }  // namespace dl

@@ -63,9 +63,10 @@ class FlatAdam(torch.optim.Optimizer):
         wait_limit_us: how long a kernel waits for the other ranks before it gives up (0: 20 seconds).
         announce_in_backward: the layer's backward_w kernel tells the peers that the gradients are complete (its last
         block does), instead of the exchange kernel at its start.
-        one_pass_bytes: the bucket whose gradients come LAST in the backward pass -- the only one whose exchange
-        nothing hides -- is exchanged in one pass (every rank averages and updates all of it: one flag round trip
-        less) when (ranks - 1) x its size is at most this many bytes; 0: never."""
+        one_pass_bytes: the buckets whose gradients come LAST in the backward pass -- the ones whose exchange little or
+        nothing hides -- are exchanged in one pass (every rank averages and updates all of the bucket: one flag round
+        trip less): as many buckets from the end as keep (ranks - 1) x their total size within this many bytes;
+        0: never."""
         import ctypes
         import torch.distributed as dist
         lib = N.lib()
@@ -187,10 +188,14 @@ class FlatAdam(torch.optim.Optimizer):
             self._bucket_pending[bi] -= 1
             if self._bucket_pending[bi] <= 0:
                 last = sum(self._bucket_launched) == len(self._buckets) - 1
-                if last and not self._forms_fixed:
-                    if world > 1 and (world - 1) * self._buckets[bi][1] * 4 <= self._one_pass_bytes:
+                if not self._forms_fixed:
+                    # One pass for the buckets at the END of the backward pass, as many as fit the byte limit: this bucket
+                    # and everything that is still to come.  (With two ranks that is every bucket: one pass then moves no
+                    # more bytes than two.)
+                    still = sum(b[1] for i, b in enumerate(self._buckets) if not self._bucket_launched[i])
+                    if world > 1 and (world - 1) * still * 4 <= self._one_pass_bytes:
                         self._one_pass.add(bi)
-                    self._forms_fixed = True
+                    self._forms_fixed = last
                 self._launch_bucket(bi, behind_backward_w=last, announce_here=not self._announce_in_backward)
         return out
 

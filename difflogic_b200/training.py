@@ -47,6 +47,7 @@ class TrainStep:
             dist.get_world_size(process_group) if process_group is not None else 1)
         self.params = [p for p in model.parameters() if p.requires_grad]
         self._graph = None
+        self._resident = []
         self._static_x = self._static_y = self._static_loss = None
         self._comm_stream = None
         self._bw_stream = torch.cuda.Stream() if all(p.is_cuda for p in self.params) else None
@@ -242,6 +243,27 @@ class TrainStep:
         self._graph = graph
         return self
 
+    def capture_resident(self, xs, ys):
+        """After capture(): one more graph per batch (xs[i], ys[i]) that reads its inputs where they ARE -- device tensors
+        that stay alive and in place -- instead of the static buffers, for batches that are already resident in device
+        memory (no copy into the static buffers in front of a step).  The graphs share the first graph's memory pool.
+        Returns the number of graphs; replay_resident(i) runs the step on batch i."""
+        if self._graph is None:
+            raise RuntimeError("TrainStep.capture_resident: call capture() first")
+        self._resident = []
+        for x, y in zip(xs, ys):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph.pool()):
+                loss = self._step(x, y)
+            self._resident.append((graph, loss, x, y))
+        return len(self._resident)
+
+    def replay_resident(self, i):
+        """Replays the step captured on resident batch i (whatever that batch's tensors hold now)."""
+        graph, loss = self._resident[i][0], self._resident[i][1]
+        graph.replay()
+        return loss
+
     @property
     def static_inputs(self):
         return self._static_x, self._static_y
@@ -264,6 +286,7 @@ class TrainStep:
             torch.cuda.synchronize()
         self._graph = None
         self._static_loss = None
+        self._resident = []
         if self._exchange_in_optimizer and hasattr(self.optimizer, "close"):
             self.optimizer.close()   # unmaps the peers' buffers; the parameters move back to ordinary memory
             self._exchange_in_optimizer = False

@@ -280,3 +280,29 @@ def test_train_step_with_adam_inside_backward(captured):
     assert all(torch.equal(p, q) for p, q in zip(la, lb))
     assert all(torch.equal(p, q) for p, q in zip(wa, wb))
     assert torch.equal(ma, mb) and torch.equal(va, vb)
+
+
+def test_resident_batches_replay_without_copies():
+    """capture_resident: one graph per batch that reads the batch where it lies; the same steps as eager ones."""
+    torch.manual_seed(8)
+    dims = [40, 96, 128, 640]
+    net = O.OracleNet.build(dims, 10, 4.0)
+    g = torch.Generator().manual_seed(4)
+    xs = [(torch.rand(48, 40, generator=g) < 0.4).float().cuda() for _ in range(3)]
+    ys = [torch.randint(0, 10, (48,), generator=g).cuda() for _ in range(3)]
+    results = []
+    for resident in (False, True):
+        model = build_model(dims, 10, 4.0, net.weights, net.idx_a, net.idx_b)
+        step = TrainStep(model, FlatAdam(model.parameters(), lr=0.01), CrossEntropyLoss())
+        if resident:
+            step.capture(xs[0], ys[0], warmup=0)
+            assert step.capture_resident(xs, ys) == 3
+            losses = [step.replay_resident(i).clone() for i in (0, 1, 2, 1)]
+        else:
+            losses = [step(xs[i], ys[i]).clone() for i in (0, 1, 2, 1)]
+        torch.cuda.synchronize()
+        results.append((losses, [l.weights.detach().clone() for l in logic_layers(model)]))
+        step.close()
+    (la, wa), (lb, wb) = results
+    assert all(torch.equal(p, q) for p, q in zip(la, lb))
+    assert all(torch.equal(p, q) for p, q in zip(wa, wb))
