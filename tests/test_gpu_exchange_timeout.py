@@ -116,3 +116,58 @@ def test_exchange_entry_points_validate_their_arguments():
     assert lib.dl_exchange_bucket_f32(one, one, flags, 0, 1, *args, 0, 64, 32, *tail) == N.DL_ERR_INVALID_ARG   # bucket
     assert lib.dl_exchange_bucket_f32(one, one, flags, 0, 17, *args, 0, 64, 0, *tail) == N.DL_ERR_INVALID_ARG   # world
     assert lib.dl_exchange_announce(flags, 0, 1, 40, st.data_ptr(), None) == N.DL_ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize("world,rank,whole", [(8, 3, 0), (8, 7, 1), (4, 0, 0), (4, 2, 1), (3, 1, 0), (2, 1, 0)])
+def test_exchange_kernel_for_every_world_size_with_the_peers_played_by_hand(world, rank, whole):
+    """One rank of a world of 2, 3, 4 or 8 on ONE GPU: the other ranks are buffers in the same process whose flags are
+    raised beforehand, so no wait has anything to wait for.  Checks the arithmetic of every variant of the kernel: the
+    mean over all ranks' gradients in this rank's slice (the whole bucket in the one-pass form), Adam on it, and the
+    other ranks' slices fetched from their parameter buffers.  The bucket is not a multiple of the slice size."""
+    lib = N.lib()
+    n, off, lr, beta1, beta2, eps, bucket = 4 * 1237, 64, 0.01, 0.9, 0.999, 1e-8, 5
+    total = off + n + 32
+    g = torch.Generator().manual_seed(100 * world + rank)
+    params = [torch.randn(total, generator=g).cuda() for _ in range(world)]
+    grads = [torch.randn(total, generator=g).cuda() for _ in range(world)]
+    words = lib.dl_exchange_flag_bytes() // 4
+    flags = [torch.zeros(words, dtype=torch.int32, device="cuda") for _ in range(world)]
+    for p in range(world):
+        if p != rank:
+            flags[rank][_flag(bucket, p, 0)] = 1
+            flags[rank][_flag(bucket, p, 1)] = 1
+    m, v = torch.zeros(total, device="cuda"), torch.zeros(total, device="cuda")
+    state = torch.zeros(16, dtype=torch.int32, device="cuda")
+    before = params[rank].clone()
+    N.check(lib.dl_exchange_bucket_f32(_ptrs(*params), _ptrs(*grads), _ptrs(*flags), rank, world, m.data_ptr(), v.data_ptr(), off, n,
+                                       bucket, lr, beta1, beta2, eps, state.data_ptr(), 1, whole, 0, N.LAUNCH_PLAIN,
+                                       torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    s = state.tolist()
+    assert s[0] == 1 and s[1] == 0 and s[2] == 0 and s[3] == 0
+    per = -(-(n // 4) // world) * 4                       # floats per slice
+    lo = off + min(rank * per, n)
+    hi = min(lo + per, off + n)
+    if whole:
+        lo, hi = off, off + n
+    mean = grads[0].clone()
+    for p in range(1, world):
+        mean += grads[p]                                  # rank order, as the kernel adds them
+    mean *= 1.0 / world
+    ref = before[lo:hi].cpu().clone().requires_grad_(True)
+    ref.grad = mean[lo:hi].cpu()
+    torch.optim.Adam([ref], lr=lr, betas=(beta1, beta2), eps=eps).step()
+    got = params[rank]
+    assert torch.allclose(got[lo:hi].cpu(), ref.detach(), rtol=1e-6, atol=1e-7)
+    assert torch.equal(got[:off], before[:off]) and torch.equal(got[off + n:], before[off + n:])   # outside the bucket
+    if not whole:
+        for p in range(world):
+            if p == rank:
+                continue
+            plo = off + min(p * per, n)
+            phi = min(plo + per, off + n)
+            assert torch.equal(got[plo:phi], params[p][plo:phi])
+        assert not m[off:lo].any() and not m[hi:off + n].any()
+    # every rank was told about this rank's gradients and its finished slice
+    for p in range(world):
+        assert int(flags[p][_flag(bucket, rank, 0)]) == 1 and int(flags[p][_flag(bucket, rank, 1)]) == 1
