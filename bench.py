@@ -288,6 +288,44 @@ def replica_checksum(opt, world):
     return lo == hi
 
 
+_PEER_EXCHANGE = {}
+
+
+def peer_exchange_usable(args, world):
+    """Whether this box lets every rank map every other rank's buffers and two trial steps of the headline network get
+    through the peer-memory exchange with no wait running out (a short limit, so a box without working peer access
+    costs seconds).  Decided once, by all ranks together; when it fails the bench runs on NCCL's all-reduce and says so
+    in `implementation.exchange`.  Returns (usable, reason)."""
+    if "usable" in _PEER_EXCHANGE:
+        return _PEER_EXCHANGE["usable"], _PEER_EXCHANGE["why"]
+    from difflogic_b200.losses import CrossEntropyLoss
+    from difflogic_b200.optim import ExchangeUnavailable, FlatAdam
+    from difflogic_b200.training import TrainStep
+    cfg = CONFIGS["c2"]
+    why = None
+    model = build_gpu_model(cfg["dims"], cfg["k"], cfg["tau"], seed=0, grad_factor=cfg["grad_factor"])
+    model.train()
+    opt = FlatAdam(model.parameters(), lr=TRAIN_LR)
+    try:
+        opt.enable_exchange(dist.group.WORLD, buckets=args.exchange_buckets, announce_in_backward=args.announce_in_backward,
+                            one_pass_bytes=args.one_pass_bytes, wait_limit_us=3_000_000)
+    except ExchangeUnavailable as e:      # raised on every rank
+        why = str(e)
+    if why is None:
+        step = TrainStep(model, opt, CrossEntropyLoss(), process_group=dist.group.WORLD, world_size=world)
+        g = torch.Generator().manual_seed(77)
+        for _ in range(2):
+            step(synthetic_features("c2", cfg["batch"], g).cuda(), torch.randint(0, cfg["k"], (cfg["batch"],), generator=g).cuda())
+        torch.cuda.synchronize()
+        failed = all_max(1.0 if opt.exchange_error() else 0.0, world) > 0
+        same = replica_checksum(opt, world)
+        if failed or not same:
+            why = "trial steps failed (a wait for a peer ran out: %s, replicas identical: %s)" % (failed, same)
+        step.close()
+    _PEER_EXCHANGE["usable"], _PEER_EXCHANGE["why"] = why is None, why
+    return why is None, why
+
+
 def bench_train(name, args, rank, world, headline):
     from difflogic_b200 import _native
     from difflogic_b200.losses import CrossEntropyLoss
@@ -304,7 +342,7 @@ def bench_train(name, args, rank, world, headline):
     else:
         opt = FlatAdam(model.parameters(), lr=TRAIN_LR)
     group = dist.group.WORLD if world > 1 else None
-    peer = world > 1 and args.exchange == "peer" and args.optimizer == "flat"
+    peer = world > 1 and args.exchange == "peer" and args.optimizer == "flat" and peer_exchange_usable(args, world)[0]
     if peer:
         opt.enable_exchange(group, buckets=args.exchange_buckets, announce_in_backward=args.announce_in_backward,
                             one_pass_bytes=args.one_pass_bytes)
@@ -957,14 +995,19 @@ def main():
 
     if rank == 0:
         peer = world > 1 and args.exchange == "peer" and args.optimizer == "flat"
+        if peer and not _PEER_EXCHANGE.get("usable", True):
+            peer, fell_back = False, " (the peer-memory exchange was not usable here: %s)" % _PEER_EXCHANGE["why"]
+        else:
+            fell_back = ""
         line = {
             "metric": METRIC, "value": train["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": train["ms_per_step"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": train_config(world),
             "implementation": {
-                "exchange": "none" if world == 1 else ("reduce-scatter + Adam and all-gather kernels over peer memory, one pair "
-                                                       "per layer, launched beside the backward pass" if peer else "NCCL all-reduce"),
+                "exchange": "none" if world == 1 else ("one kernel per layer over peer memory (CUDA IPC, plain loads and stores): "
+                                                       "average, Adam and the new weights, launched beside the backward pass"
+                                                       if peer else "NCCL all-reduce" + fell_back),
                 "execution": "whole step replayed as one CUDA graph",
                 "loss": "CrossEntropy (%s)" % ("difflogic_b200.losses.CrossEntropyLoss" if args.loss == "fused"
                                                else "torch.nn.CrossEntropyLoss"),

@@ -475,7 +475,9 @@ static int launch_fg(const void *x, const int64_t *a, const int64_t *b, const ui
         return fail(DL_ERR_CUDA, "dl_eval_groupbitsum: no cluster of %d CTAs can be resident", S);
     }
     // Column block: 2 KB.  Narrower blocks that would fill the last round of the static round-robin better were
-    // measured slower throughout: the kernel's time goes with the number of stages, not with their width.
+    // measured slower throughout: the kernel's time goes with the number of stages, not with their width.  So was
+    // sharing the last round's units among all clusters stage by stage, with the parts' counts added to a zeroed out
+    // by atomics: 300 against 288 us for 8000 gates x 2^20 samples, 70 against 64 us for 2^17 samples.
     const int block_bytes = (int)(row_bytes < kFgChunk ? row_bytes : kFgChunk);
     const int64_t nunits = ceil_div(row_bytes, block_bytes) * k;
     const int64_t nclusters = nunits < resident ? nunits : resident;

@@ -16,6 +16,10 @@ import torch
 from . import _native as N
 
 
+class ExchangeUnavailable(RuntimeError):
+    """enable_exchange could not map a peer's buffers; raised on EVERY rank of the group, with the optimizer untouched."""
+
+
 class FlatAdam(torch.optim.Optimizer):
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8):
         defaults = dict(lr=lr, betas=betas, eps=eps)
@@ -60,6 +64,7 @@ class FlatAdam(torch.optim.Optimizer):
         over the ranks, Adam is applied to this rank's slice, the new parameters are fetched from the other ranks, all
         beside the rest of the backward pass.  `step()` launches whatever is still missing and makes the current
         stream wait for the exchange.  No NCCL call is made per step.  Collective: every rank of the group calls it.
+        Raises ExchangeUnavailable on every rank, with nothing changed, when a rank cannot map a peer's buffers.
         wait_limit_us: how long a kernel waits for the other ranks before it gives up (0: 20 seconds).
         announce_in_backward: the layer's backward_w kernel tells the peers that the gradients are complete (its last
         block does), instead of the exchange kernel at its start.
@@ -90,6 +95,41 @@ class FlatAdam(torch.optim.Optimizer):
             return t
 
         ptrs = {"param": alloc(n * 4), "grad": alloc(n * 4), "flags": alloc(int(lib.dl_exchange_flag_bytes()))}
+        handles = {}
+        for name, ptr in ptrs.items():
+            buf = (ctypes.c_ubyte * 64)()
+            N.check(lib.dl_comm_export(ptr, buf))
+            handles[name] = bytes(buf)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, handles, group=group)
+        # map the peers' buffers; a rank that cannot (no peer access between two of the GPUs) must not leave the others
+        # waiting in the next collective, so the outcome is agreed on before anything of the optimizer has changed
+        imported, peer_ptrs, failure = [], {}, None
+        for name in ptrs:
+            arr = (ctypes.c_void_p * world)()
+            for r in range(world):
+                if r == rank:
+                    arr[r] = ptrs[name]
+                    continue
+                out = ctypes.c_void_p()
+                with torch.cuda.device(dev):
+                    rc = lib.dl_comm_import(gathered[r][name], ctypes.byref(out))
+                if rc != 0:
+                    failure = failure or "rank %d could not map the %s buffer of rank %d (%s)" % (rank, name, r, "status %d: %s" % (rc, N.last_error()))
+                    continue
+                arr[r] = out.value
+                imported.append(out.value)
+            peer_ptrs[name] = arr
+        failures = [None] * world
+        dist.all_gather_object(failures, failure, group=group)
+        if any(failures):
+            with torch.cuda.device(dev):
+                for ptr in imported:
+                    lib.dl_comm_close(ptr)
+                for ptr in ptrs.values():
+                    lib.dl_comm_free(ptr)
+            raise ExchangeUnavailable("; ".join(f for f in failures if f))
+
         new_param = as_tensor(ptrs["param"], n, "<f4", torch.float32)
         new_grad = as_tensor(ptrs["grad"], n, "<f4", torch.float32)
         with torch.no_grad():
@@ -100,29 +140,7 @@ class FlatAdam(torch.optim.Optimizer):
                 p.data = new_param[off:off + cnt].view_as(p)
                 p._dl_grad_out = new_grad[off:off + cnt].view_as(p)
         self.flat_param, self.flat_grad = new_param, new_grad
-
-        handles = {}
-        for name, ptr in ptrs.items():
-            buf = (ctypes.c_ubyte * 64)()
-            N.check(lib.dl_comm_export(ptr, buf))
-            handles[name] = bytes(buf)
-        gathered = [None] * world
-        dist.all_gather_object(gathered, handles, group=group)
-        self._own_ptrs = ptrs
-        self._imported = []
-        self._peer_ptrs = {}
-        for name in ptrs:
-            arr = (ctypes.c_void_p * world)()
-            for r in range(world):
-                if r == rank:
-                    arr[r] = ptrs[name]
-                else:
-                    out = ctypes.c_void_p()
-                    with torch.cuda.device(dev):
-                        N.check(lib.dl_comm_import(gathered[r][name], ctypes.byref(out)))
-                    arr[r] = out.value
-                    self._imported.append(out.value)
-            self._peer_ptrs[name] = arr
+        self._own_ptrs, self._imported, self._peer_ptrs = ptrs, imported, peer_ptrs
         # moments in the flat layout; a rank only ever touches its slices of them
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)

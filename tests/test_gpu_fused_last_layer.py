@@ -26,10 +26,11 @@ def _case(n_in, n_out, words, bits, seed):
 
 
 # (n_in, n_out, words, bits, k, pad_len): rows of 560 B .. 10 KB (one ragged and several column blocks), classes of
-# 32 .. 2040 gates (clusters of 2, 4 and 8 CTAs; shares that are not multiples of the 8-gate stage), one class, padding
+# 32 .. 2040 gates (clusters of 2, 4 and 8 CTAs; shares that are not multiples of the 8-gate stage), one class, padding;
+# the last two have more units than clusters fit on the GPU: several rounds of the persistent clusters, the last one partial
 CASES = [(300, 640, 70, 64, 10, 0), (100, 2000, 300, 64, 10, 13), (64, 1500, 256, 64, 1, 63), (50, 640, 128, 64, 20, 1),
          (40, 1010, 512, 8, 10, 7), (77, 999, 200, 32, 3, 31), (500, 8000, 1282, 64, 10, 5), (30, 4080, 66, 64, 2, 0),
-         (90, 330, 96, 64, 10, 2), (64, 1640, 1040, 16, 8, 15)]
+         (90, 330, 96, 64, 10, 2), (64, 1640, 1040, 16, 8, 15), (64, 640, 2304, 64, 10, 3), (40, 660, 4100, 64, 11, 9)]
 
 
 @pytest.mark.parametrize("case", CASES)
