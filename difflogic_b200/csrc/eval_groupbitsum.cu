@@ -311,12 +311,14 @@ eval_groupbitsum_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict
                     continue;  // keep the iteration counts; nothing is waited for any more
                 }
                 const int nr = min(kFgRows, g.rows - r);
+                // the gates' results first, then the slot goes back to the producers, then the counting: the slot is
+                // not held while the adder tree runs
+                unsigned long long v[kFgRows];
                 if (mine) {
                     const uint2 *col_a = reinterpret_cast<const uint2 *>(smem + s * kFgStageBytes) + ct;
                     const uint2 *col_b = col_a + kFgRows * kFgWords;
                     const uint4 *mk = meta + s * kFgRows;
                     // rows past the end of the share count as zero words
-                    unsigned long long v[kFgRows];
 #pragma unroll
                     for (int i = 0; i < kFgRows; ++i) {
                         v[i] = 0ull;
@@ -326,10 +328,10 @@ eval_groupbitsum_kernel(const uint8_t *__restrict__ x, const int64_t *__restrict
                             v[i] = ((unsigned long long)gate_from_masks(va.y, vb.y, mm) << 32) | gate_from_masks(va.x, vb.x, mm);
                         }
                     }
-                    cn.add8(v);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty + s);
+                if (mine) cn.add8(v);
             }
 
             // ---- publish this CTA's planes of unit n ----
