@@ -61,6 +61,7 @@ SIGNATURES = {
     "dl_backward_w_classes_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _int, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
     "dl_backward_w_adam_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _f32, _f32, _f32, _f32,
                                       _f32, _ptr, _int, _ptr]),
+    "dl_transpose_f32": (_int, [_ptr, _ptr, _i64, _i64, _ptr]),
     "dl_backward_x_classes_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _f32, _ptr, _i64, _i64, _i64, _i64, _int, _ptr]),
     "dl_comm_alloc": (_int, [ctypes.c_size_t, _ptr]),
     "dl_comm_free": (_int, [_ptr]),

@@ -412,6 +412,28 @@ backward_x_kernel(const float *__restrict__ x, const float4 *__restrict__ coef, 
     }
 }
 
+// y[c][r] = x[r][c]: the batch-major input of a network -> the feature-major layout of the layer kernels, 32 x 32 tiles
+// through shared memory.  The kernel that follows may begin its set-up at once (it reads y only after its own dependency
+// wait, i.e. after this grid has finished).
+__global__ void __launch_bounds__(kThreads)
+transpose_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows, int64_t cols) {
+    __shared__ float tile[32][33];
+    grid_dependents_launch();
+    const int tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+    const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
+#pragma unroll
+    for (int i = 0; i < 32; i += kThreads / 32) {
+        const int64_t r = r0 + ty + i, c = c0 + tx;
+        if (r < rows && c < cols) tile[ty + i][tx] = x[r * cols + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 32; i += kThreads / 32) {
+        const int64_t c = c0 + ty + i, r = r0 + tx;
+        if (r < rows && c < cols) y[c * rows + r] = tile[tx][ty + i];
+    }
+}
+
 __global__ void __launch_bounds__(kThreads)
 build_plan_kernel(const int64_t *__restrict__ a, const int64_t *__restrict__ b, const int64_t *__restrict__ start,
                   const int64_t *__restrict__ list, int2 *__restrict__ plan, int64_t n_in) {
@@ -736,6 +758,17 @@ extern "C" DL_API int dl_backward_x_classes_f32(const float *x, const float *coe
                                                 const int32_t *plan, float grad_scale, float *grad_x, int64_t n_in, int64_t n_out,
                                                 int64_t batch, int64_t rows_per_class, int flags, void *stream) {
     return backward_x_entry(x, coef, grad_y_classes, start, plan, grad_scale, grad_x, n_in, n_out, batch, rows_per_class, flags, stream);
+}
+
+// y [cols][rows] = transpose of x [rows][cols] (a network's input batch -> feature-major).
+extern "C" DL_API int dl_transpose_f32(const float *x, float *y, int64_t rows, int64_t cols, void *stream) {
+    DL_REQUIRE(rows >= 0 && cols >= 0, DL_ERR_INVALID_ARG, "dl_transpose_f32: negative size");
+    if (rows == 0 || cols == 0) return DL_OK;
+    DL_REQUIRE(x && y && x != y, DL_ERR_INVALID_ARG, "dl_transpose_f32: null pointer, or in place");
+    DL_REQUIRE(ceil_div(rows, 32) <= 65535, DL_ERR_TOO_LARGE, "dl_transpose_f32: more than 2^21 rows");
+    const dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)ceil_div(rows, 32));
+    transpose_kernel<<<grid, kThreads, 0, as_stream(stream)>>>(x, y, rows, cols);
+    return launch_status("dl_transpose_f32");
 }
 
 // Checks a layer's index arrays on the device (see check_connections_kernel).  start, list and plan may be null (only a

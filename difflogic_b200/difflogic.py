@@ -179,7 +179,13 @@ class LogicLayer(torch.nn.Module):
             assert x.device.type == 'cuda', x.device
         assert x.ndim == 2, x.ndim
 
-        x = x.transpose(0, 1).contiguous()  # feature-major; a no-op after another LogicLayer
+        # feature-major: a no-op after another LogicLayer; the network's input goes through the library's transpose
+        xt = x.transpose(0, 1)
+        if (not xt.is_contiguous() and x.is_contiguous() and x.is_cuda and x.dtype == torch.float32
+                and not (x.requires_grad and torch.is_grad_enabled())):
+            x = ops.transpose(x)
+        else:
+            x = xt.contiguous()
         assert x.shape[0] == self.in_dim, (x.shape, self.in_dim)
         if self._plan is None:
             raise RuntimeError('LogicLayer(implementation="cuda") needs its weights on a CUDA device')

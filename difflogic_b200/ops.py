@@ -68,6 +68,15 @@ def logic_coefs(w, w_mode=W_LOGITS):
     return coef
 
 
+def transpose(x):
+    """[rows, cols] float32 -> its transpose as a new contiguous tensor (dl_transpose_f32)."""
+    _f32_matrix(x, "x")
+    y = torch.empty((x.shape[1], x.shape[0]), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_transpose_f32(x.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1], N.stream_of(x)))
+    return y
+
+
 def logic_backward_w(x, a, b, grad_y, w=None, w_mode=W_PROBS, out=None, overlap=False, rows_per_class=1):
     """[n_out,16] gradient: w_mode=W_PROBS w.r.t. the mixing weights, W_LOGITS w.r.t. the raw
     parameters `w` (softmax backward applied in the kernel).  rows_per_class > 1: grad_y holds one row per class of

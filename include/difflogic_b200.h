@@ -99,6 +99,11 @@ DL_API int dl_async_error(void);
 DL_API int dl_forward_f32(const float *x, const int64_t *a, const int64_t *b, const float *w, int w_mode,
                    float *y, float *coef, int64_t n_in, int64_t n_out, int64_t batch, int flags, void *stream);
 
+/* y [cols][rows] = transpose of x [rows][cols]: a network's batch-major input -> the feature-major layout above, in
+ * front of the first layer (the reference transposes with ATen, difflogic/difflogic.py:115-116).  The kernel lets a
+ * DL_LAUNCH_OVERLAP_SETUP kernel launched behind it begin its set-up at once. */
+DL_API int dl_transpose_f32(const float *x, float *y, int64_t rows, int64_t cols, void *stream);
+
 /* The coefficient table alone (w [n_out][16] -> coef [n_out][4]); used when a caller hands
  * dl_backward_x_f32 weights that did not pass through dl_forward_f32.  No counterpart in the
  * reference, which re-reads 12 of the 16 weights per consumer (difflogic_kernel.cu:215-251). */

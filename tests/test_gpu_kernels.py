@@ -318,3 +318,15 @@ def test_check_connections_accepts_a_sound_layer_and_names_the_first_violation()
     bad_plan[0, 0] = 2 * 64 + 1                               # a neuron that does not exist: reported, not dereferenced
     with pytest.raises(ValueError, match="out of range"):
         ops.check_connections(ad, bd, 30, start, lst, bad_plan)
+
+
+@pytest.mark.parametrize("shape", [(128, 784), (1, 7), (33, 65), (100, 32), (3, 4000)])
+def test_transpose_equals_torch(shape):
+    x = torch.randn(*shape, device="cuda")
+    y = ops.transpose(x)
+    assert y.is_contiguous() and torch.equal(y, x.t().contiguous())
+    # the first layer of a network takes its batch-major input through it: same output as with a pre-transposed input
+    import difflogic_b200 as D
+    layer = D.LogicLayer(shape[1], max(64, shape[1]), device="cuda", implementation="cuda")
+    layer.eval()
+    assert torch.equal(layer(x), layer(x.t().contiguous().t()))
