@@ -423,26 +423,18 @@ def bench_train(name, args, rank, world, headline):
             "timeline_ns": [[t - first["entered_ns"] for t in b_["stamps_ns"]] for b_ in exchange_timing]}
 
     if headline:
-        # ---- end to end: pinned host batch -> H2D -> step -> loss read back on the host, every step.  The public call for
-        # this is TrainStep.step_from_host(): the two copies from the pinned input buffers, the step and the copy of the
-        # loss into a pinned host word are one graph launch, followed by one synchronisation.  The batch is put into the
-        # pinned buffers before the clock starts (where a data loader would have written it).
-        stage_x, stage_y = step.capture_host_io()
+        # ---- end to end: pinned host batch -> H2D -> step -> loss read back on the host, every step
         for i in range(W):
-            stage_x.copy_(hx[i % pool])
-            stage_y.copy_(hy[i % pool])
-            step.step_from_host()
+            step(hx[i % pool], hy[i % pool]).item()
         barrier(world)
         e2e_times = []
         for _ in range(max(3, reps // 2)):
             t_rep = 0.0
             for i in range(K):
-                stage_x.copy_(hx[i % pool])
-                stage_y.copy_(hy[i % pool])
                 flush.zero_()
                 torch.cuda.synchronize()
                 t0 = time.perf_counter()
-                step.step_from_host()
+                step(hx[i % pool], hy[i % pool]).item()
                 t_rep += time.perf_counter() - t0
             barrier(world)
             e2e_times.append(t_rep)
@@ -450,7 +442,7 @@ def bench_train(name, args, rank, world, headline):
         t_e2e = median(e2e_times)
         out["e2e"] = {"value": world * batch * K / t_e2e, "unit": UNIT, "ms_per_step": t_e2e / K * 1e3,
                       "h2d_bytes_per_step": hx[0].numel() * 4 + hy[0].numel() * 8, "d2h_bytes_per_step": 4,
-                      "repetitions": len(e2e_times), "call": "TrainStep.step_from_host()"}
+                      "repetitions": len(e2e_times), "call": "TrainStep.__call__(x_pinned, y_pinned).item()"}
     sampler.__exit__(None, None, None)
     out["clocks"] = sampler.summary()
 

@@ -386,7 +386,9 @@ extern "C" DL_API int dl_exchange_bucket_f32(void *const *param_ptrs, void *cons
                "dl_exchange_bucket_f32: moments must be non-null and 16-byte aligned");
     const int64_t n4 = count / 4, per = whole_bucket ? n4 : ceil_div(n4, world);
     const int per_thread = (world == 2 || world == 4 || world == 8) ? 8 / world : 1;
-    // enough blocks for one pass over the slice and for one pass of the gather (8 elements per thread); two passes: never
+    // enough blocks for one pass over the slice and for one pass of the gather (8 elements per thread; grids of 2 and 4 times
+    // as many blocks with fewer elements per thread made the step of 2 ranks 10 and 30 us slower: the blocks compete with
+    // the backward kernels); two passes: never
     // more than 64, the blocks wait for their grid's last block between the phases and a small grid is resident as a
     // whole; one pass: no block waits for another, up to two blocks per SM
     int64_t blocks = ceil_div(per > 0 ? per : 1, (int64_t)kThreads * per_thread);

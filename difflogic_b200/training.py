@@ -47,7 +47,6 @@ class TrainStep:
             dist.get_world_size(process_group) if process_group is not None else 1)
         self.params = [p for p in model.parameters() if p.requires_grad]
         self._graph = None
-        self._host_graph = None
         self._resident = []
         self._static_x = self._static_y = self._static_loss = None
         self._comm_stream = None
@@ -265,38 +264,6 @@ class TrainStep:
         graph.replay()
         return loss
 
-    def capture_host_io(self):
-        """After capture(): one more graph of the step that begins with the copies of the batch from two pinned host
-        buffers (`host_inputs`) and ends with the copy of the loss into a pinned host word -- a step from host memory to
-        host memory is then ONE launch and one synchronisation (`step_from_host()`), instead of two copies, a launch and
-        a blocking read.  Returns the pinned (x, y) buffers: fill them, then call step_from_host()."""
-        if self._graph is None:
-            raise RuntimeError("TrainStep.capture_host_io: call capture() first")
-        x, y = self._static_x, self._static_y
-        self._host_x = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
-        self._host_y = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
-        self._host_loss = torch.zeros((), dtype=torch.float32, pin_memory=True)
-        self._host_x.copy_(x)
-        self._host_y.copy_(y)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, pool=self._graph.pool()):
-            x.copy_(self._host_x, non_blocking=True)
-            y.copy_(self._host_y, non_blocking=True)
-            loss = self._step(x, y)
-            self._host_loss.copy_(loss.to(torch.float32), non_blocking=True)
-        self._host_graph = graph
-        return self._host_x, self._host_y
-
-    @property
-    def host_inputs(self):
-        return self._host_x, self._host_y
-
-    def step_from_host(self):
-        """One step on the batch that `host_inputs` hold; returns the loss as a python float (synchronises)."""
-        self._host_graph.replay()
-        torch.cuda.current_stream().synchronize()
-        return float(self._host_loss)
-
     @property
     def static_inputs(self):
         return self._static_x, self._static_y
@@ -318,7 +285,6 @@ class TrainStep:
         if self._on_gpu and torch.cuda.is_available():
             torch.cuda.synchronize()
         self._graph = None
-        self._host_graph = None
         self._static_loss = None
         self._resident = []
         if self._exchange_in_optimizer and hasattr(self.optimizer, "close"):

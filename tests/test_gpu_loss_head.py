@@ -307,33 +307,3 @@ def test_resident_batches_replay_without_copies():
     assert all(torch.equal(p, q) for p, q in zip(la, lb))
     assert all(torch.equal(p, q) for p, q in zip(wa, wb))
 
-
-def test_step_from_host_equals_eager_steps():
-    """capture_host_io: copies in, step and loss out as one graph; the same steps as eager ones on the same batches."""
-    torch.manual_seed(9)
-    dims = [40, 96, 128, 640]
-    net = O.OracleNet.build(dims, 10, 4.0)
-    g = torch.Generator().manual_seed(6)
-    xs = [(torch.rand(48, 40, generator=g) < 0.4).float() for _ in range(3)]
-    ys = [torch.randint(0, 10, (48,), generator=g) for _ in range(3)]
-    results = []
-    for from_host in (False, True):
-        model = build_model(dims, 10, 4.0, net.weights, net.idx_a, net.idx_b)
-        step = TrainStep(model, FlatAdam(model.parameters(), lr=0.01), CrossEntropyLoss())
-        if from_host:
-            step.capture(xs[0].cuda(), ys[0].cuda(), warmup=0)
-            hx, hy = step.capture_host_io()
-            assert hx.is_pinned() and hy.is_pinned() and step.host_inputs[0] is hx
-            losses = []
-            for i in (0, 1, 2, 1):
-                hx.copy_(xs[i])
-                hy.copy_(ys[i])
-                losses.append(step.step_from_host())
-        else:
-            losses = [float(step(xs[i].cuda(), ys[i].cuda()).item()) for i in (0, 1, 2, 1)]
-        torch.cuda.synchronize()
-        results.append((losses, [l.weights.detach().clone() for l in logic_layers(model)]))
-        step.close()
-    (la, wa), (lb, wb) = results
-    assert la == lb
-    assert all(torch.equal(p, q) for p, q in zip(wa, wb))
