@@ -308,7 +308,7 @@ def peer_exchange_usable(args, world):
     opt = FlatAdam(model.parameters(), lr=TRAIN_LR)
     try:
         opt.enable_exchange(dist.group.WORLD, buckets=args.exchange_buckets, announce_in_backward=args.announce_in_backward,
-                            one_pass_bytes=args.one_pass_bytes, wait_limit_us=3_000_000)
+                            one_pass_bytes=args.one_pass_bytes, packet_bytes=args.packet_bytes, wait_limit_us=3_000_000)
     except ExchangeUnavailable as e:      # raised on every rank
         why = str(e)
     if why is None:
@@ -345,7 +345,7 @@ def bench_train(name, args, rank, world, headline):
     peer = world > 1 and args.exchange == "peer" and args.optimizer == "flat" and peer_exchange_usable(args, world)[0]
     if peer:
         opt.enable_exchange(group, buckets=args.exchange_buckets, announce_in_backward=args.announce_in_backward,
-                            one_pass_bytes=args.one_pass_bytes)
+                            one_pass_bytes=args.one_pass_bytes, packet_bytes=args.packet_bytes)
     loss_fn = torch.nn.CrossEntropyLoss() if args.loss == "torch" else CrossEntropyLoss()
     step = TrainStep(model, opt, loss_fn, process_group=group, world_size=world, buckets=args.buckets)
 
@@ -385,6 +385,8 @@ def bench_train(name, args, rank, world, headline):
                 flush.zero_()
             else:
                 flush[:1 << 20].zero_()  # diagnostic: keeps the launch queue ahead without evicting L2
+            if peer:
+                opt.rank_barrier()       # the flush does not take equally long on every rank: the timed step starts together
             s, e = event_pair()
             s.record()
             loss = step.replay_resident(i % pool)
@@ -416,7 +418,7 @@ def bench_train(name, args, rank, world, headline):
         last = max(exchange_timing, key=lambda b: b["done_ns"])
         first = min(exchange_timing, key=lambda b: b["entered_ns"])
         out["exchange_last_step"] = {
-            "buckets": len(exchange_timing), "first_bucket_entered_to_last_done_ns": last["done_ns"] - first["entered_ns"],
+            "buckets": len(exchange_timing), "forms": [b_["form"] for b_ in exchange_timing], "first_bucket_entered_to_last_done_ns": last["done_ns"] - first["entered_ns"],
             "last_bucket": {k_: v for k_, v in last.items() if k_ not in ("entered_ns", "done_ns", "stamps_ns")},
             # per bucket (parameter order): entered, all gradients seen, own slice done, all slices seen, done -- ns after
             # the first bucket's entry
@@ -432,6 +434,8 @@ def bench_train(name, args, rank, world, headline):
             t_rep = 0.0
             for i in range(K):
                 flush.zero_()
+                if peer:
+                    opt.rank_barrier()   # the ranks leave the synchronize below together
                 torch.cuda.synchronize()
                 t0 = time.perf_counter()
                 step(hx[i % pool], hy[i % pool]).item()
@@ -805,7 +809,7 @@ def cpu_packed_baselines(threads):
 def train_config(world, exchange=None):
     return {"workload": WORKLOAD, "batch_per_gpu": TRAIN_BATCH, "global_batch": TRAIN_BATCH * world,
             "parallelism": "batch-sharded replicas x%d" % world,
-            "l2": "flushed between timed steps (256 MiB memset, untimed)"}
+            "l2": "flushed between timed steps (256 MiB memset, untimed; several ranks then meet in a device-side barrier, untimed)"}
 
 
 def reference_arm(args):
@@ -934,6 +938,8 @@ def main():
                     help="peer exchange: backward_w's last block tells the peers (default: the exchange kernel does)")
     ap.add_argument("--one-pass-bytes", type=int, default=8 << 20,
                     help="peer exchange: one-pass form for the last bucket up to this many bytes over NVLink per rank (0: never)")
+    ap.add_argument("--packet-bytes", type=int, default=2 << 20,
+                    help="peer exchange: buckets up to this many bytes go as packets with the flags inside the data (0: none)")
     ap.add_argument("--skip-packed", action="store_true")
     ap.add_argument("--skip-large", action="store_true", help="leave out the wide and deep configurations (`configs`)")
     ap.add_argument("--optimizer", default="flat", choices=["flat", "torch"],
@@ -1006,7 +1012,8 @@ def main():
             "config": train_config(world),
             "implementation": {
                 "exchange": "none" if world == 1 else ("one kernel per layer over peer memory (CUDA IPC, plain loads and stores): "
-                                                       "average, Adam and the new weights, launched beside the backward pass"
+                                                       "average, Adam and the new weights, launched beside the backward pass; "
+                                                       "small layers as 8-byte packets that carry their own flag"
                                                        if peer else "NCCL all-reduce" + fell_back),
                 "execution": "whole step replayed as one CUDA graph",
                 "loss": "CrossEntropy (%s)" % ("difflogic_b200.losses.CrossEntropyLoss" if args.loss == "fused"

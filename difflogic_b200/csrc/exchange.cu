@@ -299,6 +299,214 @@ __global__ void exchange_announce_kernel(ExchangePeers peers, int rank, int worl
     if ((int)threadIdx.x < world) st_release_sys(peers.flags[threadIdx.x] + flag_index(bucket, rank, 0), state[0] + 1);
 }
 
+// ---- the exchange with the flags inside the data ("packets") ------------------------------------------------------------
+// For small buckets the flag round trips of the kernel above cost more than the data: a flag store, the peer loads it
+// allows (a round trip over NVLink), another flag, more peer loads.  Here nothing is pulled and no flag is raised.  Every
+// float travels as an 8-byte packet {value, epoch} written with ONE store into the receiver's memory; 8-byte stores
+// arrive whole, so a receiver that reads a packet with this step's epoch has its value, and every packet announces
+// itself.  No fences, no tickets between the phases, no block waits for another block of its grid:
+//   1. push: each float4 of this rank's gradients outside its own slice goes, as 4 packets, into the OWNER's inbox;
+//   2. reduce: for its own slice the rank adds up -- in rank order, as the kernels above do -- its own gradients and the
+//      packets of the other ranks as they arrive, applies Adam, stores the new parameters and pushes them, as packets,
+//      into every peer's parameter inbox;
+//   3. collect: the other slices' new parameters are taken out of the inbox as they arrive.
+// One-way latencies only: push -> reduce -> push -> collect.  NVLink carries 4 (N-1)/N times the bucket per rank (the
+// packets double the bytes), which is why this is the form for SMALL buckets.  An inbox holds, per bucket, one region
+// per sending rank of `per` = ceil(n4 / world) float4 slots (32 bytes each, in two planes of 16).  It may be overwritten by the sender's next
+// step because the sender gets there only after it has collected this step's parameters from this rank, which this
+// rank sends after it has read the sender's gradient packets; and the parameter packets of the next step are sent only
+// after the receiver's gradient packets of the next step have arrived, which it sends after it has collected this
+// step's.  A packet that does not arrive within the limit sets the bucket's error word; unlike the kernels above this
+// form may then have updated part of the bucket.  The grid is small enough to be resident as a whole (blocks in phase 2
+// wait for OTHER ranks' phase 1, which waits for nothing).
+struct PacketPeers {
+    unsigned long long *grad_inbox[kMaxRanks];   // of each rank (index = rank); own entry: this rank's inbox
+    unsigned long long *param_inbox[kMaxRanks];
+};
+
+// A float4 slot is two 16-byte halves, {x, y} and {z, w} as two packets each, in two PLANES of the inbox `half` u64
+// apart, so that the 32 lanes of a warp write (and read) 512 contiguous bytes per instruction.
+__device__ __forceinline__ void st_packets(unsigned long long *dst, int64_t half, const float4 &v, unsigned epoch) {
+    const unsigned long long e = (unsigned long long)epoch << 32;
+    const unsigned long long p0 = e | __float_as_uint(v.x), p1 = e | __float_as_uint(v.y);
+    const unsigned long long p2 = e | __float_as_uint(v.z), p3 = e | __float_as_uint(v.w);
+    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(dst), "l"(p0), "l"(p1) : "memory");
+    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(dst + half), "l"(p2), "l"(p3) : "memory");
+}
+
+struct Packets4 {
+    unsigned long long p[4];
+    __device__ __forceinline__ void load(const unsigned long long *src, int64_t half) {
+        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(p[0]), "=l"(p[1]) : "l"(src) : "memory");
+        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(p[2]), "=l"(p[3]) : "l"(src + half) : "memory");
+    }
+    __device__ __forceinline__ bool complete(unsigned epoch) const {
+        return (unsigned)(p[0] >> 32) == epoch && (unsigned)(p[1] >> 32) == epoch && (unsigned)(p[2] >> 32) == epoch &&
+               (unsigned)(p[3] >> 32) == epoch;
+    }
+    __device__ __forceinline__ float4 value() const {
+        return make_float4(__uint_as_float((unsigned)p[0]), __uint_as_float((unsigned)p[1]), __uint_as_float((unsigned)p[2]),
+                           __uint_as_float((unsigned)p[3]));
+    }
+};
+
+// polls one slot until its four packets carry `epoch`; false when that took longer than limit_us (t0: the thread's first
+// look at the clock, shared by its waits of this launch)
+__device__ __forceinline__ bool wait_packets(Packets4 &pk, const unsigned long long *src, int64_t half, unsigned epoch,
+                                             unsigned limit_us, unsigned long long &t0) {
+    unsigned spin = 0;
+    for (;;) {
+        pk.load(src, half);
+        if (pk.complete(epoch)) return true;
+        if ((++spin & 63u) == 0u) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > (unsigned long long)limit_us * 1000ull) return false;
+        }
+    }
+}
+
+// inbox_off: first float4 slot of this bucket inside a sender's region; inbox_stride: float4 slots per sender's region
+// (the sum of `per` over all buckets).  WORLD as in exchange_bucket_kernel.
+template <int WORLD>
+__global__ void __launch_bounds__(kThreads)
+exchange_packets_kernel(PacketPeers peers, int rank, int world, float *__restrict__ param, const float *__restrict__ grad,
+                        float *__restrict__ m, float *__restrict__ v, int64_t off4, int64_t n4, int64_t inbox_off,
+                        int64_t inbox_stride, float lr, float beta1, float beta2, float eps, int *__restrict__ state,
+                        unsigned wait_us) {
+    __shared__ float s_step_size, s_bc2_sqrt;
+    unsigned long long *stamps = reinterpret_cast<unsigned long long *>(state + 4);
+    const int epoch_i = state[0] + 1;  // last written by this kernel one step ago: safe before the dependency wait
+    const unsigned epoch = (unsigned)epoch_i;
+    if (threadIdx.x == 0) {
+        const float t = (float)epoch_i;
+        s_step_size = lr / (1.f - powf(beta1, t));
+        s_bc2_sqrt = sqrtf(1.f - powf(beta2, t));
+    }
+    grid_dependency_wait();  // this rank's gradients come from the kernel just before (when launched right behind it)
+    __syncthreads();
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[0] = global_timer_ns();
+
+    const int64_t per = (n4 + world - 1) / world;  // float4 per slice
+    const int64_t my_lo = min((int64_t)rank * per, n4), my_hi = min(my_lo + per, n4);  // this rank's slice within the bucket
+    const int64_t stride = (int64_t)gridDim.x * kThreads, first = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    const float4 *g4 = reinterpret_cast<const float4 *>(grad) + off4;
+    float4 *p4 = reinterpret_cast<float4 *>(param) + off4;
+    float4 *m4 = reinterpret_cast<float4 *>(m) + off4, *v4 = reinterpret_cast<float4 *>(v) + off4;
+    unsigned long long t0 = 0;
+    bool ok = true;
+    const int64_t half = (int64_t)world * inbox_stride * 2;  // u64 between the two planes of an inbox
+    // first u64 of float4 slot k of this bucket in the region of rank `from`
+#define DL_SLOT(from, k) (((int64_t)(from) * inbox_stride + inbox_off + (k)) * 2)
+
+    // 1. push the gradients of the other ranks' slices into their owners' inboxes (this rank's region there)
+    const int64_t others = n4 - (my_hi - my_lo);
+    for (int64_t idx = first; idx < others; idx += stride) {
+        const int64_t i = idx < my_lo ? idx : idx + (my_hi - my_lo);  // position within the bucket, own slice skipped
+        const int owner = (int)(i / per);
+        const int64_t k = i - (int64_t)owner * per;
+        st_packets(peers.grad_inbox[owner] + DL_SLOT(rank, k), half, g4[i], epoch);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[1] = global_timer_ns();
+
+    // 2. own slice: sum in rank order, Adam, new parameters to every peer
+    const AdamConsts consts = {1.f - beta1, beta2, 1.f - beta2, s_step_size, s_bc2_sqrt, eps};
+    const float inv_world = 1.f / (float)world;
+    const unsigned long long *my_gin = peers.grad_inbox[rank];
+    for (int64_t k = first; k < my_hi - my_lo; k += stride) {
+        const int64_t i = my_lo + k;
+        const float4 own = g4[i];
+        float4 pp = p4[i], mm = m4[i], vv = v4[i];
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (WORLD > 0) {
+            // all peers' slots are read at once, then those that have not arrived yet are polled
+            Packets4 pk[WORLD > 0 ? WORLD : 1];
+#pragma unroll
+            for (int p = 0; p < WORLD; ++p)
+                if (p != rank) pk[p].load(my_gin + DL_SLOT(p, k), half);
+#pragma unroll
+            for (int p = 0; p < WORLD; ++p) {
+                float4 one = own;
+                if (p != rank) {
+                    if (!pk[p].complete(epoch)) ok = wait_packets(pk[p], my_gin + DL_SLOT(p, k), half, epoch, wait_us, t0) && ok;
+                    one = pk[p].value();
+                }
+                g.x += one.x; g.y += one.y; g.z += one.z; g.w += one.w;
+            }
+        } else {
+            for (int p = 0; p < world; ++p) {
+                float4 one = own;
+                if (p != rank) {
+                    Packets4 pk;
+                    ok = wait_packets(pk, my_gin + DL_SLOT(p, k), half, epoch, wait_us, t0) && ok;
+                    one = pk.value();
+                }
+                g.x += one.x; g.y += one.y; g.z += one.z; g.w += one.w;
+            }
+        }
+        if (!ok) break;  // a packet is missing: this element and the thread's later ones stay as they are
+        g.x = __fmul_rn(g.x, inv_world); g.y = __fmul_rn(g.y, inv_world);
+        g.z = __fmul_rn(g.z, inv_world); g.w = __fmul_rn(g.w, inv_world);
+        adam_update4(pp, g, mm, vv, consts);
+        m4[i] = mm;
+        v4[i] = vv;
+        p4[i] = pp;
+        for (int p = 0; p < world; ++p)
+            if (p != rank) st_packets(peers.param_inbox[p] + DL_SLOT(rank, k), half, pp, epoch);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[2] = global_timer_ns();
+
+    // 3. the other slices' new parameters, as they arrive
+    const unsigned long long *my_pin = peers.param_inbox[rank];
+    if (ok) {
+        for (int64_t idx = first; idx < others; idx += stride) {
+            const int64_t i = idx < my_lo ? idx : idx + (my_hi - my_lo);
+            const int owner = (int)(i / per);
+            const int64_t k = i - (int64_t)owner * per;
+            Packets4 pk;
+            if (!wait_packets(pk, my_pin + DL_SLOT(owner, k), half, epoch, wait_us, t0)) {
+                ok = false;
+                break;
+            }
+            p4[i] = pk.value();
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) stamps[4] = global_timer_ns();
+
+    // the last block to finish advances the bucket's step count -- only when no packet was missed anywhere
+    const bool block_ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    if (threadIdx.x == 0) {
+        if (!block_ok) atomicExch(state + 2, 1);
+        __threadfence();
+        const int add = block_ok ? 1 : 0x10001;
+        const int all = atomicAdd(state + 3, add) + add;
+        if ((all & 0xffff) == (int)gridDim.x) {
+            state[3] = 0;
+            if ((all >> 16) == 0) {
+                stamps[5] = global_timer_ns();
+                state[0] = epoch_i;
+            }
+        }
+    }
+#undef DL_SLOT
+}
+
+// All ranks meet on the device: this rank stores the barrier's next epoch into its word (bucket, rank, 0) of every rank's
+// flags and waits until all ranks' words in its own flags have reached it.  state: sixteen ints like a bucket's, of
+// which [0] counts the barriers passed and [2] is set when the wait ran out (the count then stays).  Like the exchange
+// kernels it waits only for OTHER GPUs.
+__global__ void rank_barrier_kernel(ExchangePeers peers, int rank, int world, int bucket, int *__restrict__ state, unsigned wait_us) {
+    const int epoch = state[0] + 1;
+    if ((int)threadIdx.x < world) st_release_sys(peers.flags[threadIdx.x] + flag_index(bucket, rank, 0), epoch);
+    const bool ok = wait_peers(peers.flags[rank], world, bucket, 0, epoch, wait_us);
+    if (threadIdx.x == 0) {
+        if (ok)
+            state[0] = epoch;
+        else
+            atomicExch(state + 2, 1);
+    }
+}
+
 }  // namespace dl
 
 using namespace dl;
@@ -413,6 +621,55 @@ extern "C" DL_API int dl_exchange_bucket_f32(void *const *param_ptrs, void *cons
     return launch_status("dl_exchange_bucket_f32");
 }
 
+// The exchange of one bucket with the flags inside the data (exchange_packets_kernel).  param, grad, exp_avg, exp_avg_sq:
+// THIS rank's flat buffers (ordinary device memory will do); grad_inbox_ptrs / param_inbox_ptrs: host arrays of `world`
+// device pointers, index = rank, to every rank's two inboxes (each 32 * world * inbox_stride bytes, zero at first).
+// offset, count: the bucket in floats; inbox_offset: its first float4 slot inside a sender's region of inbox_stride slots.
+extern "C" DL_API int dl_exchange_packets_f32(float *param, const float *grad, void *const *grad_inbox_ptrs,
+                                              void *const *param_inbox_ptrs, int rank, int world, float *exp_avg, float *exp_avg_sq,
+                                              int64_t offset, int64_t count, int64_t inbox_offset, int64_t inbox_stride, float lr,
+                                              float beta1, float beta2, float eps, int32_t *state, uint32_t wait_limit_us, int flags,
+                                              void *stream) {
+    const char *who = "dl_exchange_packets_f32";
+    DL_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, DL_ERR_INVALID_ARG, "%s: rank %d of %d (at most %d ranks)",
+               who, rank, world, kMaxRanks);
+    DL_REQUIRE(offset >= 0 && count >= 0 && offset % 4 == 0 && count % 4 == 0, DL_ERR_INVALID_ARG,
+               "%s: offset and count must be non-negative multiples of 4", who);
+    DL_REQUIRE(param && grad && exp_avg && exp_avg_sq && state && grad_inbox_ptrs && param_inbox_ptrs, DL_ERR_INVALID_ARG,
+               "%s: null pointer", who);
+    DL_REQUIRE(aligned_to(param, 16) && aligned_to(grad, 16) && aligned_to(exp_avg, 16) && aligned_to(exp_avg_sq, 16), DL_ERR_INVALID_ARG,
+               "%s: buffers must be 16-byte aligned", who);
+    const int64_t n4 = count / 4, per = ceil_div(n4, (int64_t)world);
+    DL_REQUIRE(inbox_offset >= 0 && inbox_stride > 0 && inbox_offset + per <= inbox_stride, DL_ERR_INVALID_ARG,
+               "%s: slots %lld + %lld outside a region of %lld", who, (long long)inbox_offset, (long long)per, (long long)inbox_stride);
+    PacketPeers peers;
+    for (int p = 0; p < world; ++p) {
+        DL_REQUIRE(grad_inbox_ptrs[p] && param_inbox_ptrs[p] && aligned_to(grad_inbox_ptrs[p], 16) && aligned_to(param_inbox_ptrs[p], 16),
+                   DL_ERR_INVALID_ARG, "%s: null or misaligned inbox pointer", who);
+        peers.grad_inbox[p] = reinterpret_cast<unsigned long long *>(grad_inbox_ptrs[p]);
+        peers.param_inbox[p] = reinterpret_cast<unsigned long long *>(param_inbox_ptrs[p]);
+    }
+    // one float4 per thread and phase where that fits; never more than 64 blocks: blocks wait for other ranks' blocks, so
+    // the grid must be resident as a whole
+    int64_t blocks = ceil_div(n4 > 0 ? n4 : 1, (int64_t)kThreads);
+    if (blocks > 64) blocks = 64;
+    const unsigned limit = wait_limit_us ? wait_limit_us : kExchangeWaitUs;
+    int *st = reinterpret_cast<int *>(state);
+    cudaStream_t cs = as_stream(stream);
+    const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
+#define DL_EXCHANGE_PACKETS(WW)                                                                                                       \
+    launch_dependent(overlap, exchange_packets_kernel<WW>, dim3((unsigned)blocks), dim3(kThreads), 0, cs, peers, rank, world, param,  \
+                     grad, exp_avg, exp_avg_sq, offset / 4, n4, inbox_offset, inbox_stride, lr, beta1, beta2, eps, st, limit)
+    switch (world) {
+        case 2: DL_EXCHANGE_PACKETS(2); break;
+        case 4: DL_EXCHANGE_PACKETS(4); break;
+        case 8: DL_EXCHANGE_PACKETS(8); break;
+        default: DL_EXCHANGE_PACKETS(0); break;
+    }
+#undef DL_EXCHANGE_PACKETS
+    return launch_status(who);
+}
+
 extern "C" DL_API int dl_exchange_announce(void *const *flag_ptrs, int rank, int world, int bucket, const int32_t *state, void *stream) {
     ExchangePeers peers;
     DL_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world && bucket >= 0 && bucket < kMaxBuckets && flag_ptrs && state,
@@ -423,6 +680,21 @@ extern "C" DL_API int dl_exchange_announce(void *const *flag_ptrs, int rank, int
     }
     exchange_announce_kernel<<<1, 32, 0, as_stream(stream)>>>(peers, rank, world, bucket, reinterpret_cast<const int *>(state));
     return launch_status("dl_exchange_announce");
+}
+
+// A barrier of the ranks on the device, on flag words of a bucket number that no exchange uses (see rank_barrier_kernel).
+extern "C" DL_API int dl_rank_barrier(void *const *flag_ptrs, int rank, int world, int bucket, int32_t *state, uint32_t wait_limit_us,
+                                      void *stream) {
+    ExchangePeers peers;
+    DL_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world && bucket >= 0 && bucket < kMaxBuckets && flag_ptrs && state,
+               DL_ERR_INVALID_ARG, "dl_rank_barrier: bad argument");
+    for (int p = 0; p < world; ++p) {
+        DL_REQUIRE(flag_ptrs[p], DL_ERR_INVALID_ARG, "dl_rank_barrier: null peer pointer");
+        peers.flags[p] = reinterpret_cast<int *>(flag_ptrs[p]);
+    }
+    rank_barrier_kernel<<<1, 32, 0, as_stream(stream)>>>(peers, rank, world, bucket, reinterpret_cast<int *>(state),
+                                                       wait_limit_us ? wait_limit_us : kExchangeWaitUs);
+    return launch_status("dl_rank_barrier");
 }
 
 // Word of a rank's flag array that rank `rank` raises for (bucket, which): for callers that announce from kernels of

@@ -55,7 +55,8 @@ class FlatAdam(torch.optim.Optimizer):
 
     # -- batch-sharded training: exchange and step over peer memory, bucket by bucket -------------------------------
 
-    def enable_exchange(self, group=None, buckets=None, wait_limit_us=0, announce_in_backward=False, one_pass_bytes=8 << 20):
+    def enable_exchange(self, group=None, buckets=None, wait_limit_us=0, announce_in_backward=False, one_pass_bytes=8 << 20,
+                        packet_bytes=2 << 20):
         """Switches to the peer-memory exchange (dl_backward_w_announce_f32 / dl_exchange_bucket_f32): the flat
         parameter and gradient buffers move into memory that the other ranks of `group` (one process per GPU on this
         machine) map through CUDA IPC.  The buffers are cut into buckets -- one per parameter, or `buckets` groups of
@@ -71,7 +72,9 @@ class FlatAdam(torch.optim.Optimizer):
         one_pass_bytes: the buckets whose gradients come LAST in the backward pass -- the ones whose exchange little or
         nothing hides -- are exchanged in one pass (every rank averages and updates all of the bucket: one flag round
         trip less): as many buckets from the end as keep (ranks - 1) x their total size within this many bytes;
-        0: never."""
+        0: never.
+        packet_bytes: buckets of at most this many bytes are exchanged with the flags inside the data
+        (dl_exchange_packets_f32: pushes only, no flag round trips, twice the bytes over NVLink); 0: none."""
         import ctypes
         import torch.distributed as dist
         lib = N.lib()
@@ -94,7 +97,19 @@ class FlatAdam(torch.optim.Optimizer):
             assert t.dtype == dtype and t.data_ptr() == ptr
             return t
 
+        # the bucket plan first: the inboxes of the packet exchange have one region per sending rank with
+        # ceil(bucket / ranks) float4 slots per bucket
+        self._plan_exchange_buckets(buckets)
+        self._inbox_off, slots = [], 0
+        for _, cnt, _ in self._buckets:
+            self._inbox_off.append(slots)
+            slots += -(-(cnt // 4) // world)
+        self._inbox_stride = max(slots, 1)
+        self._packet_form = {bi for bi, (_, cnt, _) in enumerate(self._buckets) if world > 1 and 0 < cnt * 4 <= int(packet_bytes)}
         ptrs = {"param": alloc(n * 4), "grad": alloc(n * 4), "flags": alloc(int(lib.dl_exchange_flag_bytes()))}
+        if self._packet_form:
+            ptrs["grad_inbox"] = alloc(32 * world * self._inbox_stride)
+            ptrs["param_inbox"] = alloc(32 * world * self._inbox_stride)
         handles = {}
         for name, ptr in ptrs.items():
             buf = (ctypes.c_ubyte * 64)()
@@ -144,12 +159,12 @@ class FlatAdam(torch.optim.Optimizer):
         # moments in the flat layout; a rank only ever touches its slices of them
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
-        self._plan_exchange_buckets(buckets)
         self.state_t = torch.zeros((len(self._buckets), 16), dtype=torch.int32, device=dev)
         self._bw_tickets = torch.zeros(len(self._params), dtype=torch.int32, device=dev)     # per parameter
         self._bucket_kernels = torch.zeros(len(self._buckets), dtype=torch.int32, device=dev)  # per bucket
         self._param_index = {p: i for i, p in enumerate(self._params)}
         self._exchange = (rank, world)
+        self._barrier_state = None      # rank_barrier's own count, made on first use
         self._wait_limit_us = int(wait_limit_us)   # 0: the library's default (20 s); ranks further apart than that fail the step
         self._announce_in_backward = bool(announce_in_backward)
         self._one_pass_bytes = int(one_pass_bytes)
@@ -168,10 +183,11 @@ class FlatAdam(torch.optim.Optimizer):
         return self
 
     def _plan_exchange_buckets(self, buckets):
-        """Buckets of consecutive parameters: [(offset, count, [params])]; at most 32 (the library's flag words)."""
+        """Buckets of consecutive parameters: [(offset, count, [params])]; at most 31 (the library has flag words for 32;
+        the last set is rank_barrier's)."""
         order = sorted(self._params, key=lambda p: self._slices[p][0])
         n_buckets = len(order) if buckets is None else max(1, min(int(buckets), len(order)))
-        n_buckets = min(n_buckets, 32)
+        n_buckets = min(n_buckets, 31)
         per = -(-len(order) // n_buckets)
         self._buckets, self._bucket_of = [], {}
         for bi in range(0, len(order), per):
@@ -196,7 +212,7 @@ class FlatAdam(torch.optim.Optimizer):
         from . import ops
         rank, world = self._exchange
         bi = self._bucket_of[p]
-        if self._announce_in_backward:
+        if self._announce_in_backward and bi not in self._packet_form:   # packets announce themselves
             out = ops.logic_backward_w_announce(x, a, b, grad_y, p, grad_out, rows_per_class, self._peer_ptrs["flags"], rank, world,
                                                 bi, self.state_t[bi], self._bw_tickets[self._param_index[p]:],
                                                 self._bucket_kernels[bi:], len(self._buckets[bi][2]))
@@ -211,7 +227,7 @@ class FlatAdam(torch.optim.Optimizer):
                     # and everything that is still to come.  (With two ranks that is every bucket: one pass then moves no
                     # more bytes than two.)
                     still = sum(b[1] for i, b in enumerate(self._buckets) if not self._bucket_launched[i])
-                    if world > 1 and (world - 1) * still * 4 <= self._one_pass_bytes:
+                    if world > 1 and (world - 1) * still * 4 <= self._one_pass_bytes and bi not in self._packet_form:
                         self._one_pass.add(bi)
                     self._forms_fixed = last
                 self._launch_bucket(bi, behind_backward_w=last, announce_here=not self._announce_in_backward)
@@ -231,16 +247,35 @@ class FlatAdam(torch.optim.Optimizer):
             ready = torch.cuda.Event()
             ready.record(current)
             stream.wait_event(ready)
+        how = N.LAUNCH_OVERLAP_SETUP if behind_backward_w else N.LAUNCH_PLAIN
         with torch.cuda.device(dev):
-            N.check(N.lib().dl_exchange_bucket_f32(
-                self._peer_ptrs["param"], self._peer_ptrs["grad"], self._peer_ptrs["flags"], rank, world, self.exp_avg.data_ptr(),
-                self.exp_avg_sq.data_ptr(), off, cnt, bi, float(g['lr']), float(beta1), float(beta2), float(g['eps']),
-                self.state_t[bi].data_ptr(), int(announce_here), int(bi in self._one_pass), self._wait_limit_us,
-                N.LAUNCH_OVERLAP_SETUP if behind_backward_w else N.LAUNCH_PLAIN, stream.cuda_stream))
+            if bi in self._packet_form:
+                N.check(N.lib().dl_exchange_packets_f32(
+                    self.flat_param.data_ptr(), self.flat_grad.data_ptr(), self._peer_ptrs["grad_inbox"], self._peer_ptrs["param_inbox"],
+                    rank, world, self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(), off, cnt, self._inbox_off[bi], self._inbox_stride,
+                    float(g['lr']), float(beta1), float(beta2), float(g['eps']), self.state_t[bi].data_ptr(), self._wait_limit_us, how,
+                    stream.cuda_stream))
+            else:
+                N.check(N.lib().dl_exchange_bucket_f32(
+                    self._peer_ptrs["param"], self._peer_ptrs["grad"], self._peer_ptrs["flags"], rank, world, self.exp_avg.data_ptr(),
+                    self.exp_avg_sq.data_ptr(), off, cnt, bi, float(g['lr']), float(beta1), float(beta2), float(g['eps']),
+                    self.state_t[bi].data_ptr(), int(announce_here), int(bi in self._one_pass), self._wait_limit_us, how,
+                    stream.cuda_stream))
         done = torch.cuda.Event()
         done.record(stream)
         self._bucket_done.append(done)
         self._bucket_launched[bi] = True
+
+    def rank_barrier(self):
+        """Launches, on the current stream, a kernel in which the ranks of the exchange wait for each other (bounded like
+        every wait of the exchange): what follows it on the stream starts at the same time on every rank, within a flag's
+        latency.  No host synchronisation.  Collective: every rank launches it equally often."""
+        rank, world = self._exchange
+        if getattr(self, "_barrier_state", None) is None:
+            self._barrier_state = torch.zeros(16, dtype=torch.int32, device=self.flat_param.device)
+        with torch.cuda.device(self.flat_param.device):
+            N.check(N.lib().dl_rank_barrier(self._peer_ptrs["flags"], rank, world, 31, self._barrier_state.data_ptr(),
+                                            self._wait_limit_us, N.stream_of(self.flat_param)))
 
     def full_exp_avg(self):
         """Adam's first moments of ALL parameters in the flat layout.  Under the peer-memory exchange a rank holds the
@@ -261,18 +296,24 @@ class FlatAdam(torch.optim.Optimizer):
     def exchange_error(self):
         """True when a wait for a peer ever ran out of its time limit (synchronises).  The step in which that happened
         left parameters, moments and step count as they were; training cannot go on from there."""
-        return bool(int(self.state_t[:, 2].max().item())) if getattr(self, "exchange_enabled", False) else False
+        if not getattr(self, "exchange_enabled", False):
+            return False
+        barrier = getattr(self, "_barrier_state", None)
+        return bool(int(self.state_t[:, 2].max().item())) or (barrier is not None and bool(int(barrier[2].item())))
 
     def exchange_timing(self):
         """Per bucket, nanoseconds inside the latest exchange on this rank (synchronises): waiting for all ranks'
         gradients, reduce + Adam on this rank's slice, waiting for all ranks' slices, fetching the other slices;
-        `total_ns` from the kernel's entry to its end."""
+        `total_ns` from the kernel's entry to its end.  For a bucket exchanged as packets the four spans are, on the
+        kernel's first block: pushing the gradients, reducing the own slice as the packets arrive, [nothing], taking the
+        other slices' parameters out of the inbox -- then until the last block is through."""
         if not getattr(self, "exchange_enabled", False):
             return None
         out = []
-        for row in self.state_t[:, 4:16].cpu().contiguous().view(torch.int64).tolist():
+        for bi, row in enumerate(self.state_t[:, 4:16].cpu().contiguous().view(torch.int64).tolist()):
             t = row
-            out.append({"wait_gradients_ns": t[1] - t[0], "slice_ns": t[2] - t[1], "wait_slices_ns": t[4] - t[2],
+            out.append({"form": "packets" if bi in self._packet_form else "one pass" if bi in self._one_pass else "two passes",
+                        "wait_gradients_ns": t[1] - t[0], "slice_ns": t[2] - t[1], "wait_slices_ns": t[4] - t[2],
                         "gather_ns": t[5] - t[4], "total_ns": t[5] - t[0], "entered_ns": t[0], "done_ns": t[5],
                         "stamps_ns": [t[0], t[1], t[2], t[4], t[5]]})
         return out
@@ -298,6 +339,7 @@ class FlatAdam(torch.optim.Optimizer):
                 p.grad = None
         self.flat_param, self.flat_grad = keep_param, keep_grad
         self.exchange_enabled = False
+        self._barrier_state = None
         self.state_t = torch.zeros(2, dtype=torch.int32, device=dev)
         torch.cuda.synchronize(dev)
         try:

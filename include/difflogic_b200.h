@@ -401,10 +401,30 @@ DL_API int dl_comm_close(void *ptr);
 DL_API size_t dl_exchange_flag_bytes(void);
 DL_API int dl_exchange_flag_word(int bucket, int rank, int which);
 DL_API int dl_exchange_announce(void *const *flag_ptrs, int rank, int world, int bucket, const int32_t *state, void *stream);
+/* A barrier of the ranks on the device: the kernel raises this rank's word (bucket, rank, 0) in every rank's flags to
+ * state[0] + 1 and waits (wait_limit_us, 0: 20 s) until all ranks' words in its own flags are there; then state[0]
+ * advances, else state[2] is set.  `bucket`: a bucket number that no exchange uses; state: sixteen int32, zero at first.
+ * For aligning the ranks in front of a timed step, or wherever a host-side barrier would stall the launch queue. */
+DL_API int dl_rank_barrier(void *const *flag_ptrs, int rank, int world, int bucket, int32_t *state, uint32_t wait_limit_us,
+                           void *stream);
 DL_API int dl_exchange_bucket_f32(void *const *param_ptrs, void *const *grad_ptrs, void *const *flag_ptrs, int rank, int world,
                                   float *exp_avg, float *exp_avg_sq, int64_t offset, int64_t count, int bucket, float lr,
                                   float beta1, float beta2, float eps, int32_t *state, int announce_here, int whole_bucket,
                                   uint32_t wait_limit_us, int flags, void *stream);
+/* The exchange of one SMALL bucket with the flags inside the data: every float crosses NVLink as an 8-byte packet
+ * {value, step number} stored into the receiver's inbox, so a packet announces itself and there is no flag round trip, no
+ * fence and no pull: gradients of the other ranks' slices are pushed to their owners; the owner adds up its slice in rank
+ * order (the same sums as dl_exchange_bucket_f32), applies Adam and pushes the new parameters to every peer; the peers take
+ * them out of their inboxes.  NVLink carries 4 (N-1)/N times the bucket per rank.  param, grad, exp_avg, exp_avg_sq: this
+ * rank's flat buffers; grad_inbox_ptrs / param_inbox_ptrs: host arrays of `world` device pointers (index = rank) to every
+ * rank's two inboxes, 32 * world * inbox_stride bytes each, zero at first, peer-mapped (dl_comm_*); inbox_offset: the
+ * bucket's first float4 slot inside a sender's region of inbox_stride slots (a bucket needs ceil(count / 4 / world)).
+ * state, wait_limit_us, flags: as for dl_exchange_bucket_f32 (no flag words are used); after a wait that ran out the
+ * error word is set and part of the bucket may have been updated. */
+DL_API int dl_exchange_packets_f32(float *param, const float *grad, void *const *grad_inbox_ptrs, void *const *param_inbox_ptrs,
+                                   int rank, int world, float *exp_avg, float *exp_avg_sq, int64_t offset, int64_t count,
+                                   int64_t inbox_offset, int64_t inbox_stride, float lr, float beta1, float beta2, float eps,
+                                   int32_t *state, uint32_t wait_limit_us, int flags, void *stream);
 DL_API int dl_backward_w_announce_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
                                       float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int64_t rows_per_class,
                                       void *const *flag_ptrs, int rank, int world, int bucket, const int32_t *bucket_state,

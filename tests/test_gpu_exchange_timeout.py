@@ -171,3 +171,38 @@ def test_exchange_kernel_for_every_world_size_with_the_peers_played_by_hand(worl
     # every rank was told about this rank's gradients and its finished slice
     for p in range(world):
         assert int(flags[p][_flag(bucket, rank, 0)]) == 1 and int(flags[p][_flag(bucket, rank, 1)]) == 1
+
+
+def test_rank_barrier_passes_when_the_peers_are_there_and_runs_out_when_not():
+    lib = N.lib()
+    words = lib.dl_exchange_flag_bytes() // 4
+    own_f = torch.zeros(words, dtype=torch.int32, device="cuda")
+    peer_f = [torch.zeros(words, dtype=torch.int32, device="cuda") for _ in range(2)]
+    flags = _ptrs(peer_f[0], own_f, peer_f[1])          # this is rank 1 of three
+    state = torch.zeros(16, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    slot = 31
+
+    def barrier(limit_us):
+        N.check(lib.dl_rank_barrier(flags, 1, 3, slot, state.data_ptr(), limit_us, stream))
+        torch.cuda.synchronize()
+
+    barrier(2000)                      # nobody else is there: the wait runs out after 2 ms
+    assert state.tolist()[:3] == [0, 0, 1]
+    # this rank did tell everybody that it had arrived
+    assert all(int(f[_flag(slot, 1, 0)]) == 1 for f in (own_f, peer_f[0], peer_f[1]))
+    state.zero_()
+    own_f[_flag(slot, 0, 0)] = 1       # the peers arrive (played by hand)
+    own_f[_flag(slot, 2, 0)] = 1
+    barrier(2000)
+    assert state.tolist()[:3] == [1, 0, 0]
+    own_f[_flag(slot, 0, 0)] = 2
+    barrier(2000)                      # second barrier: rank 2 has not arrived yet
+    assert state.tolist()[:3] == [1, 0, 1]
+    # a world of one has nobody to wait for
+    alone = torch.zeros(16, dtype=torch.int32, device="cuda")
+    N.check(lib.dl_rank_barrier(_ptrs(own_f), 0, 1, 30, alone.data_ptr(), 2000, stream))
+    torch.cuda.synchronize()
+    assert alone.tolist()[:3] == [1, 0, 0]
+    assert lib.dl_rank_barrier(flags, 3, 3, slot, state.data_ptr(), 0, stream) == N.DL_ERR_INVALID_ARG
+    assert lib.dl_rank_barrier(flags, 0, 3, 32, state.data_ptr(), 0, stream) == N.DL_ERR_INVALID_ARG

@@ -70,12 +70,16 @@ def _worker(rank, world, port, out_dir):
         ys = [torch.randint(0, 4, (64,), generator=g) for _ in range(3)]
         lo, hi = shard_range(64, rank, world)
         results = {}
-        for mode in ("nccl", "peer", "peer_graph", "peer_two_pass_announce"):
+        # peer, peer_graph: the default forms (these buckets are small: packets); peer_flags: the flag exchange, in one pass
+        # where the byte limit allows; peer_two_pass_announce: the flag exchange in two passes, announced by backward_w
+        for mode in ("nccl", "peer", "peer_graph", "peer_flags", "peer_two_pass_announce"):
             _, model = _make(dims, 4, 3.0, 11)
             model.train()
             opt = FlatAdam(model.parameters(), lr=0.01)
             if mode == "peer_two_pass_announce":   # every bucket in two passes, gradients announced by backward_w itself
-                opt.enable_exchange(dist.group.WORLD, announce_in_backward=True, one_pass_bytes=0)
+                opt.enable_exchange(dist.group.WORLD, announce_in_backward=True, one_pass_bytes=0, packet_bytes=0)
+            elif mode == "peer_flags":
+                opt.enable_exchange(dist.group.WORLD, packet_bytes=0)
             elif mode != "nccl":
                 opt.enable_exchange(dist.group.WORLD)
             step = TrainStep(model, opt, process_group=dist.group.WORLD, buckets=1)
@@ -83,6 +87,8 @@ def _worker(rank, world, port, out_dir):
                 step.capture(xs[0][lo:hi].cuda(), ys[0][lo:hi].cuda(), warmup=0)
             losses, first = [], None
             for x, y in zip(xs, ys):
+                if mode == "peer":
+                    opt.rank_barrier()     # the ranks meet on the device in front of the step; an error shows in "err"
                 losses.append(float(step(x[lo:hi].cuda(), y[lo:hi].cuda()).item()))
                 if first is None:
                     first = {"w": [l.weights.detach().cpu().clone() for l in logic_layers(model)]}
@@ -119,7 +125,7 @@ def test_peer_memory_exchange_matches_nccl_all_reduce(tmp_path):
             pytest.fail("a rank did not finish in time")
         assert p.exitcode == 0
     res = [torch.load(os.path.join(tmp_path, "rank%d.pt" % r)) for r in range(world)]
-    for mode in ("peer", "peer_graph", "peer_two_pass_announce"):
+    for mode in ("peer", "peer_graph", "peer_flags", "peer_two_pass_announce"):
         assert not res[0][mode]["err"] and not res[1][mode]["err"]
         for w0, w1 in zip(res[0][mode]["w"], res[1][mode]["w"]):
             assert torch.equal(w0, w1)                       # replicas stay identical
@@ -146,7 +152,7 @@ def test_peer_memory_exchange_matches_nccl_all_reduce(tmp_path):
             ref_first_grads = [w.grad.detach().clone() for w in net.weights]
         adam.step()
         ref_losses.append(float(loss))
-    for mode in ("peer", "peer_graph", "peer_two_pass_announce"):
+    for mode in ("peer", "peer_graph", "peer_flags", "peer_two_pass_announce"):
         mean_losses = [0.5 * (a + b) for a, b in zip(res[0][mode]["loss"], res[1][mode]["loss"])]   # equal shards
         assert torch.allclose(torch.tensor(mean_losses), torch.tensor(ref_losses), rtol=1e-4), (mode, mean_losses, ref_losses)
         for got, ref in zip(res[0][mode]["first"]["grad"], ref_first_grads):
