@@ -16,6 +16,8 @@
 // Only the bucket of the layer whose gradients come last is not hidden behind the backward pass.
 // Pulling instead of pushing the new parameters matters: after stores INTO peer memory a rank has to wait for their
 // system-wide visibility before it may raise its flag, and that fence measured 8 us.
+// Small buckets go another way (exchange_packets_kernel, further down): everything is pushed, as 8-byte packets that
+// carry their own flag, so that there is neither a fence nor a flag round trip; it moves twice the bytes.
 //
 // The peers are other GPUs of this machine mapped by plain peer-to-peer access; every access to their memory is an
 // ordinary ld/st instruction (no bulk copy, no TMA, no multicast).  Every wait is bounded (wait_limit_us microseconds); a kernel
