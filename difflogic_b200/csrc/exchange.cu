@@ -652,7 +652,8 @@ extern "C" DL_API int dl_exchange_packets_f32(float *param, const float *grad, v
         peers.param_inbox[p] = reinterpret_cast<unsigned long long *>(param_inbox_ptrs[p]);
     }
     // one float4 per thread and phase where that fits; never more than 64 blocks: blocks wait for other ranks' blocks, so
-    // the grid must be resident as a whole
+    // the grid must be resident as a whole (and 64 measured best for a 1 MB bucket with 2 ranks: 16, 32, 128 and 256 blocks
+    // made the step 7, 4, 3 and 2 us longer)
     int64_t blocks = ceil_div(n4 > 0 ? n4 : 1, (int64_t)kThreads);
     if (blocks > 64) blocks = 64;
     const unsigned limit = wait_limit_us ? wait_limit_us : kExchangeWaitUs;
