@@ -27,6 +27,7 @@ SIGNATURES = {
     "dl_version": (_int, []),
     "dl_last_error_string": (ctypes.c_char_p, []),
     "dl_async_error": (_int, []),
+    "dl_selftest_bounded_wait": (_int, [_ptr, ctypes.c_uint32, _ptr]),
     "dl_set_tuning": (_int, [_int, _int]),
     "dl_get_tuning": (_int, [_int]),
     "dl_forward_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _int, _ptr, _ptr, _i64, _i64, _i64, _int, _ptr]),

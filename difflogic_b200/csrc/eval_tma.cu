@@ -226,6 +226,31 @@ int launch_eval_tma(const void *x, const int64_t *a, const int64_t *b, const uin
 
 }  // namespace dl
 
+// Self-test of the bounded mbarrier wait that every staged kernel relies on: one thread waits, with mbar_wait() and a
+// poll limit given by the caller, for a barrier phase that nobody completes -- the wait must run out and the kernel must
+// return -- and then for a phase that its own arrival completes.  result[0]: 1 = the first wait ran out as it should,
+// 2 = it reported completion; result[1]: 1 = the second wait succeeded.  Touches none of the library's state.
+__global__ void bounded_wait_selftest_kernel(int *result, uint32_t polls) {
+    __shared__ uint64_t bar[2];
+    if (threadIdx.x == 0) {
+        dl::mbar_init(bar, 1);
+        dl::mbar_init(bar + 1, 1);
+        dl::mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        result[0] = dl::mbar_wait(bar, 0, polls) ? 2 : 1;
+        dl::mbar_arrive(bar + 1);
+        result[1] = dl::mbar_wait(bar + 1, 0, polls) ? 1 : 0;
+    }
+}
+
+extern "C" DL_API int dl_selftest_bounded_wait(int32_t *result, uint32_t polls, void *stream) {
+    DL_REQUIRE(result != nullptr && polls > 0 && polls <= dl::kSpinLimit, DL_ERR_INVALID_ARG, "dl_selftest_bounded_wait: bad argument");
+    bounded_wait_selftest_kernel<<<1, 32, 0, dl::as_stream(stream)>>>(reinterpret_cast<int *>(result), polls);
+    return dl::launch_status("dl_selftest_bounded_wait");
+}
+
 // 1 if a bounded wait inside a kernel of this library ever ran out on the current device (the affected
 // launch produced incomplete output), else 0; negative on a CUDA error.  Synchronises the device.
 extern "C" DL_API int dl_async_error(void) {

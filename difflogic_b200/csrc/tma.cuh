@@ -40,8 +40,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return done != 0;
 }
 // Bounded wait for the phase with the given parity; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+    for (uint32_t spin = 0; spin < limit; ++spin)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }

@@ -83,6 +83,12 @@ DL_API int dl_get_tuning(int key);
  * synchronises the device; it is a diagnostic, not part of the hot path.  The reference has no
  * counterpart: its kernels never wait on anything (difflogic_kernel.cu). */
 DL_API int dl_async_error(void);
+/* Self-test of the bounded mbarrier wait that the staged kernels rely on: one thread waits for a barrier phase that
+ * nobody completes, for at most `polls` polls (at most 2^24, the limit the kernels use); the wait must run out and the
+ * kernel return.  result (two int32 on the device): [0] = 1 when the wait ran out as it should (2: it reported
+ * completion), [1] = 1 when a second wait, which the thread's own arrival completes, succeeded.  Changes no state of the
+ * library.  No reference counterpart. */
+DL_API int dl_selftest_bounded_wait(int32_t *result, uint32_t polls, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Training forward.

@@ -206,3 +206,22 @@ def test_rank_barrier_passes_when_the_peers_are_there_and_runs_out_when_not():
     assert alone.tolist()[:3] == [1, 0, 0]
     assert lib.dl_rank_barrier(flags, 3, 3, slot, state.data_ptr(), 0, stream) == N.DL_ERR_INVALID_ARG
     assert lib.dl_rank_barrier(flags, 0, 3, 32, state.data_ptr(), 0, stream) == N.DL_ERR_INVALID_ARG
+
+
+def test_bounded_mbarrier_wait_of_the_staged_kernels_runs_out_and_returns():
+    """The wait helper of the bulk-copy kernels, on a barrier that nobody completes: it must give up after its poll limit
+    (2^16 here; the kernels use 2^24), the kernel must return, and the library must work afterwards."""
+    import time
+    lib = N.lib()
+    result = torch.zeros(2, dtype=torch.int32, device="cuda")
+    errors_before = lib.dl_async_error()
+    t0 = time.perf_counter()
+    N.check(lib.dl_selftest_bounded_wait(result.data_ptr(), 1 << 16, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 5.0
+    assert result.tolist() == [1, 1]
+    assert lib.dl_async_error() == errors_before
+    assert lib.dl_selftest_bounded_wait(result.data_ptr(), 0, None) == N.DL_ERR_INVALID_ARG
+    x = torch.arange(12, dtype=torch.float32, device="cuda").view(3, 4)
+    from difflogic_b200 import ops
+    assert torch.equal(ops.transpose(x), x.t().contiguous())
