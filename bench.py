@@ -308,7 +308,8 @@ def peer_exchange_usable(args, world):
     opt = FlatAdam(model.parameters(), lr=TRAIN_LR)
     try:
         opt.enable_exchange(dist.group.WORLD, buckets=args.exchange_buckets, announce_in_backward=args.announce_in_backward,
-                            one_pass_bytes=args.one_pass_bytes, packet_bytes=args.packet_bytes, wait_limit_us=3_000_000)
+                            one_pass_bytes=args.one_pass_bytes, packet_bytes=args.packet_bytes, wait_limit_us=3_000_000,
+                            push_in_backward=args.push_in_backward)
     except ExchangeUnavailable as e:      # raised on every rank
         why = str(e)
     if why is None:
@@ -345,7 +346,8 @@ def bench_train(name, args, rank, world, headline):
     peer = world > 1 and args.exchange == "peer" and args.optimizer == "flat" and peer_exchange_usable(args, world)[0]
     if peer:
         opt.enable_exchange(group, buckets=args.exchange_buckets, announce_in_backward=args.announce_in_backward,
-                            one_pass_bytes=args.one_pass_bytes, packet_bytes=args.packet_bytes)
+                            one_pass_bytes=args.one_pass_bytes, packet_bytes=args.packet_bytes,
+                            push_in_backward=args.push_in_backward)
     loss_fn = torch.nn.CrossEntropyLoss() if args.loss == "torch" else CrossEntropyLoss()
     step = TrainStep(model, opt, loss_fn, process_group=group, world_size=world, buckets=args.buckets)
 
@@ -940,6 +942,8 @@ def main():
                     help="peer exchange: one-pass form for the last bucket up to this many bytes over NVLink per rank (0: never)")
     ap.add_argument("--packet-bytes", type=int, default=2 << 20,
                     help="peer exchange: buckets up to this many bytes go as packets with the flags inside the data (0: none)")
+    ap.add_argument("--push-in-backward", action="store_true",
+                    help="peer exchange: backward_w's epilogue pushes the gradient packets (default: the exchange kernel does)")
     ap.add_argument("--skip-packed", action="store_true")
     ap.add_argument("--skip-large", action="store_true", help="leave out the wide and deep configurations (`configs`)")
     ap.add_argument("--optimizer", default="flat", choices=["flat", "torch"],

@@ -73,7 +73,9 @@ SIGNATURES = {
     "dl_exchange_flag_word": (_int, [_int, _int, _int]),
     "dl_exchange_announce": (_int, [_ptr, _int, _int, _int, _ptr, _ptr]),
     "dl_exchange_packets_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _int, _int, _ptr, _ptr, _i64, _i64, _i64, _i64, _f32, _f32, _f32, _f32,
-                                       _ptr, ctypes.c_uint32, _int, _ptr]),
+                                       _ptr, _int, ctypes.c_uint32, _int, _ptr]),
+    "dl_backward_w_push_f32": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _i64, _ptr, _int, _int, _i64, _i64, _i64,
+                                      _i64, _ptr, _int, _ptr]),
     "dl_rank_barrier": (_int, [_ptr, _int, _int, _int, _ptr, ctypes.c_uint32, _ptr]),
     "dl_exchange_bucket_f32": (_int, [_ptr, _ptr, _ptr, _int, _int, _ptr, _ptr, _i64, _i64, _int, _f32, _f32, _f32, _f32, _ptr, _int,
                                       _int, ctypes.c_uint32, _int, _ptr]),

@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(kThreads)
 exchange_packets_kernel(PacketPeers peers, int rank, int world, float *__restrict__ param, const float *__restrict__ grad,
                         float *__restrict__ m, float *__restrict__ v, int64_t off4, int64_t n4, int64_t inbox_off,
                         int64_t inbox_stride, float lr, float beta1, float beta2, float eps, int *__restrict__ state,
-                        unsigned wait_us) {
+                        int pushed, unsigned wait_us) {
     __shared__ float s_step_size, s_bc2_sqrt;
     unsigned long long *stamps = reinterpret_cast<unsigned long long *>(state + 4);
     const int epoch_i = state[0] + 1;  // last written by this kernel one step ago: safe before the dependency wait
@@ -401,9 +401,10 @@ exchange_packets_kernel(PacketPeers peers, int rank, int world, float *__restric
     // first u64 of float4 slot k of this bucket in the region of rank `from`
 #define DL_SLOT(from, k) (((int64_t)(from) * inbox_stride + inbox_off + (k)) * 2)
 
-    // 1. push the gradients of the other ranks' slices into their owners' inboxes (this rank's region there)
+    // 1. push the gradients of the other ranks' slices into their owners' inboxes (this rank's region there) -- unless
+    // the backward_w kernels that wrote them have done so (dl_backward_w_push_f32)
     const int64_t others = n4 - (my_hi - my_lo);
-    for (int64_t idx = first; idx < others; idx += stride) {
+    for (int64_t idx = first; idx < (pushed ? 0 : others); idx += stride) {
         const int64_t i = idx < my_lo ? idx : idx + (my_hi - my_lo);  // position within the bucket, own slice skipped
         const int owner = (int)(i / per);
         const int64_t k = i - (int64_t)owner * per;
@@ -627,11 +628,12 @@ extern "C" DL_API int dl_exchange_bucket_f32(void *const *param_ptrs, void *cons
 // THIS rank's flat buffers (ordinary device memory will do); grad_inbox_ptrs / param_inbox_ptrs: host arrays of `world`
 // device pointers, index = rank, to every rank's two inboxes (each 32 * world * inbox_stride bytes, zero at first).
 // offset, count: the bucket in floats; inbox_offset: its first float4 slot inside a sender's region of inbox_stride slots.
+// pushed: the gradients of the other ranks' slices have been pushed already, by dl_backward_w_push_f32.
 extern "C" DL_API int dl_exchange_packets_f32(float *param, const float *grad, void *const *grad_inbox_ptrs,
                                               void *const *param_inbox_ptrs, int rank, int world, float *exp_avg, float *exp_avg_sq,
                                               int64_t offset, int64_t count, int64_t inbox_offset, int64_t inbox_stride, float lr,
-                                              float beta1, float beta2, float eps, int32_t *state, uint32_t wait_limit_us, int flags,
-                                              void *stream) {
+                                              float beta1, float beta2, float eps, int32_t *state, int pushed, uint32_t wait_limit_us,
+                                              int flags, void *stream) {
     const char *who = "dl_exchange_packets_f32";
     DL_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, DL_ERR_INVALID_ARG, "%s: rank %d of %d (at most %d ranks)",
                who, rank, world, kMaxRanks);
@@ -662,7 +664,8 @@ extern "C" DL_API int dl_exchange_packets_f32(float *param, const float *grad, v
     const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
 #define DL_EXCHANGE_PACKETS(WW)                                                                                                       \
     launch_dependent(overlap, exchange_packets_kernel<WW>, dim3((unsigned)blocks), dim3(kThreads), 0, cs, peers, rank, world, param,  \
-                     grad, exp_avg, exp_avg_sq, offset / 4, n4, inbox_offset, inbox_stride, lr, beta1, beta2, eps, st, limit)
+                     grad, exp_avg, exp_avg_sq, offset / 4, n4, inbox_offset, inbox_stride, lr, beta1, beta2, eps, st, pushed ? 1 : 0,   \
+                     limit)
     switch (world) {
         case 2: DL_EXCHANGE_PACKETS(2); break;
         case 4: DL_EXCHANGE_PACKETS(4); break;

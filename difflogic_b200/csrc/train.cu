@@ -188,6 +188,21 @@ struct AnnounceGradients {
     int kernels;           // backward_w kernels per step that write into the bucket
 };
 
+// Optional push in the epilogue of backward_w (batch-sharded training, the packet form of the exchange, exchange.cu):
+// every gradient that belongs to ANOTHER rank's slice of the bucket goes straight from the registers into that rank's
+// inbox, as an 8-byte packet {value, step number} -- one store over NVLink, no fence, no flag -- while the kernel is still
+// working on its other neurons; the exchange kernel that follows then has nothing to push.  The gradient is stored
+// locally as well (grad_w): the owner of a slice reads its own part from there.  world <= 1: off.
+struct PushGradients {
+    unsigned long long *inbox[16];  // gradient inbox of every rank (index = rank)
+    int rank, world;
+    int per4;                       // float4 per slice of the bucket: ceil(float4 of the bucket / world)
+    int base4;                      // float4 of the bucket in front of this layer's gradients
+    long long region;               // first float4 slot of this bucket in THIS rank's region of an inbox
+    long long half;                 // u64 between the two planes of an inbox
+    const int *epoch_src;           // steps the bucket has done so far: the packets carry that + 1
+};
+
 // Row of grad_y that holds the gradient of output row j.  gy_group == 1: its own row.  gy_group == g > 1: the layer's
 // outputs are summed in classes of g consecutive rows (GroupSum) and grad_y has one row per CLASS -- the gradient of
 // every row of a class is the same, so it is not expanded to [n_out][batch] in memory.
@@ -199,7 +214,8 @@ template <int G, bool VEC4>
 __global__ void __launch_bounds__(kThreads)
 backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, const int64_t *__restrict__ b,
                   const float *__restrict__ gy, const float *w, int w_mode, float *__restrict__ grad_w,
-                  int64_t n_out, int64_t batch, int64_t ncols, int gy_group, AdamInBackward adam, AnnounceGradients ann) {
+                  int64_t n_out, int64_t batch, int64_t ncols, int gy_group, AdamInBackward adam, AnnounceGradients ann,
+                  PushGradients push) {
     using V = typename Vec<VEC4>::type;
     constexpr int R = kThreads / G;
     __shared__ float s_step_size, s_bc2_sqrt;
@@ -291,6 +307,21 @@ backward_w_kernel(const float *__restrict__ x, const int64_t *__restrict__ a, co
         if (grad_w != nullptr) {
 #pragma unroll
             for (int q = 0; q < K; ++q) grad_w[j * 16 + gl + q * P] = out[q];
+        }
+        if (push.world > 1) {
+            const unsigned long long e = (unsigned long long)(unsigned)(*push.epoch_src + 1) << 32;
+#pragma unroll
+            for (int q = 0; q < K; ++q) {
+                const int f = (int)j * 16 + gl + q * P;      // float within the layer
+                const int i = push.base4 + (f >> 2);         // float4 within the bucket
+                const int owner = i / push.per4;
+                if (owner != push.rank) {
+                    unsigned long long *dst = push.inbox[owner] + (push.region + (i - owner * push.per4)) * 2 + (f & 1) +
+                                              ((f >> 1) & 1) * push.half;
+                    const unsigned long long packet = e | __float_as_uint(out[q]);
+                    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(packet) : "memory");
+                }
+            }
         }
         if (adam.m != nullptr) {
             const AdamConsts consts = {1.f - adam.beta1, adam.beta2, 1.f - adam.beta2, s_step_size, s_bc2_sqrt, adam.eps};
@@ -537,11 +568,11 @@ static int launch_forward(bool overlap, int G, const float *x, const int64_t *a,
 template <bool VEC4>
 static int launch_backward_w(bool overlap, int G, const float *x, const int64_t *a, const int64_t *b, const float *gy, const float *w,
                              int w_mode, float *grad_w, int64_t n_out, int64_t batch, int64_t ncols, int gy_group,
-                             const AdamInBackward &adam, const AnnounceGradients &ann, cudaStream_t st) {
+                             const AdamInBackward &adam, const AnnounceGradients &ann, const PushGradients &push, cudaStream_t st) {
     const unsigned grid = (unsigned)ceil_div(n_out, kThreads / G);
 #define DL_BW(GG)                                                                                          \
     case GG:                                                                                               \
-        launch_dependent(overlap, backward_w_kernel<GG, VEC4>, dim3(grid), dim3(kThreads), 0, st, x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols, gy_group, adam, ann); \
+        launch_dependent(overlap, backward_w_kernel<GG, VEC4>, dim3(grid), dim3(kThreads), 0, st, x, a, b, gy, w, w_mode, grad_w, n_out, batch, ncols, gy_group, adam, ann, push); \
         break;
     switch (G) {
         DL_BW(1) DL_BW(2) DL_BW(4) DL_BW(8) DL_BW(16) DL_BW(32)
@@ -656,7 +687,7 @@ extern "C" DL_API int dl_forward_class_sums_f32(const float *x, const int64_t *a
 static int backward_w_entry(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w, int w_mode,
                             float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int64_t gy_group, int flags, void *stream,
                             const AdamInBackward &adam = AdamInBackward{nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, 0.f, 0.f},
-                            const AnnounceGradients &ann = AnnounceGradients{}) {
+                            const AnnounceGradients &ann = AnnounceGradients{}, const PushGradients &push = PushGradients{}) {
     DL_REQUIRE(gy_group >= 1 && gy_group <= INT32_MAX && n_out % gy_group == 0, DL_ERR_INVALID_ARG,
                "dl_backward_w_f32: n_out (%lld) is not a multiple of the rows per class (%lld)", (long long)n_out, (long long)gy_group);
     DL_REQUIRE(n_in >= 0 && n_out >= 0 && batch >= 0, DL_ERR_INVALID_ARG, "dl_backward_w_f32: negative size");
@@ -670,8 +701,8 @@ static int backward_w_entry(const float *x, const int64_t *a, const int64_t *b, 
     const int64_t ncols = vec ? batch / 4 : batch;
     const int G = pow2_at_least(ceil_div(ncols, 4), 32);
     const bool overlap = (flags & DL_LAUNCH_OVERLAP_SETUP) != 0;
-    return vec ? launch_backward_w<true>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, adam, ann, as_stream(stream))
-               : launch_backward_w<false>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, adam, ann, as_stream(stream));
+    return vec ? launch_backward_w<true>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, adam, ann, push, as_stream(stream))
+               : launch_backward_w<false>(overlap, G, x, a, b, grad_y, w, w_mode, grad_w, n_out, batch, ncols, (int)gy_group, adam, ann, push, as_stream(stream));
 }
 
 extern "C" DL_API int dl_backward_w_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
@@ -745,6 +776,41 @@ extern "C" DL_API int dl_backward_w_announce_f32(const float *x, const int64_t *
     }
     return backward_w_entry(x, a, b, grad_y, w, DL_W_LOGITS, grad_w, n_in, n_out, batch, rows_per_class, flags, stream,
                             AdamInBackward{nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, 0.f, 0.f}, ann);
+}
+
+// backward_w (DL_W_LOGITS) that also pushes the gradients of the other ranks' slices into their inboxes (PushGradients).
+// bucket_offset: floats of the bucket in front of this layer's gradients; bucket_count: floats of the whole bucket;
+// inbox_offset / inbox_stride, grad_inbox_ptrs, bucket_state: as for dl_exchange_packets_f32, which follows with pushed = 1.
+extern "C" DL_API int dl_backward_w_push_f32(const float *x, const int64_t *a, const int64_t *b, const float *grad_y, const float *w,
+                                             float *grad_w, int64_t n_in, int64_t n_out, int64_t batch, int64_t rows_per_class,
+                                             void *const *grad_inbox_ptrs, int rank, int world, int64_t bucket_offset,
+                                             int64_t bucket_count, int64_t inbox_offset, int64_t inbox_stride,
+                                             const int32_t *bucket_state, int flags, void *stream) {
+    const char *who = "dl_backward_w_push_f32";
+    DL_REQUIRE(world >= 1 && world <= 16 && rank >= 0 && rank < world, DL_ERR_INVALID_ARG, "%s: rank %d of %d", who, rank, world);
+    DL_REQUIRE(grad_inbox_ptrs && bucket_state && grad_w, DL_ERR_INVALID_ARG, "%s: null pointer", who);
+    DL_REQUIRE(bucket_offset >= 0 && bucket_offset % 4 == 0 && bucket_count % 4 == 0 && bucket_offset + n_out * 16 <= bucket_count &&
+                   bucket_count / 4 <= INT32_MAX,
+               DL_ERR_INVALID_ARG, "%s: the layer's %lld gradients at %lld do not fit a bucket of %lld floats", who,
+               (long long)(n_out * 16), (long long)bucket_offset, (long long)bucket_count);
+    PushGradients push = {};
+    const int64_t per = ceil_div(bucket_count / 4, (int64_t)world);
+    DL_REQUIRE(inbox_offset >= 0 && inbox_stride > 0 && inbox_offset + per <= inbox_stride, DL_ERR_INVALID_ARG,
+               "%s: slots %lld + %lld outside a region of %lld", who, (long long)inbox_offset, (long long)per, (long long)inbox_stride);
+    for (int p = 0; p < world; ++p) {
+        DL_REQUIRE(grad_inbox_ptrs[p] != nullptr && aligned_to(grad_inbox_ptrs[p], 16), DL_ERR_INVALID_ARG,
+                   "%s: null or misaligned inbox pointer", who);
+        push.inbox[p] = reinterpret_cast<unsigned long long *>(grad_inbox_ptrs[p]);
+    }
+    push.rank = rank;
+    push.world = world;
+    push.per4 = (int)(per > 0 ? per : 1);
+    push.base4 = (int)(bucket_offset / 4);
+    push.region = (long long)rank * inbox_stride + inbox_offset;
+    push.half = (long long)world * inbox_stride * 2;
+    push.epoch_src = reinterpret_cast<const int *>(bucket_state);
+    return backward_w_entry(x, a, b, grad_y, w, DL_W_LOGITS, grad_w, n_in, n_out, batch, rows_per_class, flags, stream,
+                            AdamInBackward{nullptr, nullptr, nullptr, 0.f, 0.f, 0.f, 0.f, 0.f}, AnnounceGradients{}, push);
 }
 
 extern "C" DL_API int dl_backward_x_f32(const float *x, const float *coef, const float *grad_y, const int64_t *start,

@@ -198,6 +198,30 @@ _VIOLATIONS = {1: "connection index outside [0, in_dim)", 2: "inverse-index offs
                5: "gather-plan entry does not match the connections"}
 
 
+def logic_backward_w_push(x, a, b, grad_y, w, out, rows_per_class, grad_inbox_ptrs, rank, world, bucket_offset, bucket_count,
+                          inbox_offset, inbox_stride, bucket_state):
+    """logic_backward_w (W_LOGITS) into `out` [n_out, 16] that also pushes the gradients of the other ranks' slices of the
+    exchange bucket into their inboxes as packets (dl_backward_w_push_f32).  grad_inbox_ptrs: ctypes array of the ranks'
+    gradient inboxes; bucket_offset / bucket_count: floats in front of this layer inside the bucket / of the bucket."""
+    _f32_matrix(x, "x")
+    _f32_matrix(grad_y, "grad_y")
+    _f32_matrix(w, "w")
+    _f32_matrix(out, "out")
+    n_in, batch = x.shape
+    rows_per_class = int(rows_per_class)
+    n_out = grad_y.shape[0] * rows_per_class
+    _need(grad_y.shape[1] == batch, "grad_y and x disagree on the batch size")
+    _need(tuple(w.shape) == (n_out, 16) and tuple(out.shape) == (n_out, 16), "w and out must be [n_out, 16]")
+    _index(a, "a", n_out)
+    _index(b, "b", n_out)
+    with torch.cuda.device(x.device):
+        N.check(N.lib().dl_backward_w_push_f32(x.data_ptr(), a.data_ptr(), b.data_ptr(), grad_y.data_ptr(), w.data_ptr(), out.data_ptr(),
+                                               n_in, n_out, batch, rows_per_class, grad_inbox_ptrs, int(rank), int(world),
+                                               int(bucket_offset), int(bucket_count), int(inbox_offset), int(inbox_stride),
+                                               bucket_state.data_ptr(), N.LAUNCH_OVERLAP_SETUP, N.stream_of(x)))
+    return out
+
+
 def check_connections(a, b, n_in, start=None, lst=None, plan=None):
     """Checks a layer's index tensors on the device (dl_check_connections) and raises ValueError with the first violation
     found.  Synchronises; meant for construction time and debugging, not for the hot path."""

@@ -56,7 +56,7 @@ class FlatAdam(torch.optim.Optimizer):
     # -- batch-sharded training: exchange and step over peer memory, bucket by bucket -------------------------------
 
     def enable_exchange(self, group=None, buckets=None, wait_limit_us=0, announce_in_backward=False, one_pass_bytes=8 << 20,
-                        packet_bytes=2 << 20):
+                        packet_bytes=2 << 20, push_in_backward=False):
         """Switches to the peer-memory exchange (dl_backward_w_announce_f32 / dl_exchange_bucket_f32): the flat
         parameter and gradient buffers move into memory that the other ranks of `group` (one process per GPU on this
         machine) map through CUDA IPC.  The buffers are cut into buckets -- one per parameter, or `buckets` groups of
@@ -74,7 +74,11 @@ class FlatAdam(torch.optim.Optimizer):
         trip less): as many buckets from the end as keep (ranks - 1) x their total size within this many bytes;
         0: never.
         packet_bytes: buckets of at most this many bytes are exchanged with the flags inside the data
-        (dl_exchange_packets_f32: pushes only, no flag round trips, twice the bytes over NVLink); 0: none."""
+        (dl_exchange_packets_f32: pushes only, no flag round trips, twice the bytes over NVLink); 0: none.
+        push_in_backward: the backward_w kernel of a layer whose bucket goes as packets pushes the gradients itself, beside
+        its arithmetic (dl_backward_w_push_f32), instead of the exchange kernel after it.  Off by default: the exchange
+        kernel gets shorter, but the stores over NVLink stretch every backward_w kernel by more (config 2, two ranks:
+        93.9 against 91.1 us per step)."""
         import ctypes
         import torch.distributed as dist
         lib = N.lib()
@@ -168,6 +172,7 @@ class FlatAdam(torch.optim.Optimizer):
         self._wait_limit_us = int(wait_limit_us)   # 0: the library's default (20 s); ranks further apart than that fail the step
         self._announce_in_backward = bool(announce_in_backward)
         self._one_pass_bytes = int(one_pass_bytes)
+        self._push_in_backward = bool(push_in_backward)
         self._one_pass = set()          # buckets exchanged in one pass; fixed by the first step
         self._forms_fixed = False
         # a few streams for the buckets' exchange kernels, so that a bucket does not queue behind the one before it
@@ -203,6 +208,7 @@ class FlatAdam(torch.optim.Optimizer):
         self._bucket_pending = [len(b[2]) for b in self._buckets]
         self._bucket_launched = [False] * len(self._buckets)
         self._bucket_done = []          # events: the buckets' exchange kernels of this step
+        self._bucket_pushes = [0] * len(self._buckets)   # backward_w kernels of this step that pushed their gradients
 
     def backward_w(self, p, x, a, b, grad_y, grad_out, rows_per_class=1):
         """backward_w of the layer whose weights are `p`, called by LogicLayer's backward in place of the plain kernel:
@@ -212,7 +218,13 @@ class FlatAdam(torch.optim.Optimizer):
         from . import ops
         rank, world = self._exchange
         bi = self._bucket_of[p]
-        if self._announce_in_backward and bi not in self._packet_form:   # packets announce themselves
+        if bi in self._packet_form and self._push_in_backward and grad_out is not None:
+            # the kernel sends the other ranks' slices of its gradients into their inboxes while it is still computing
+            off, cnt, _ = self._buckets[bi]
+            out = ops.logic_backward_w_push(x, a, b, grad_y, p, grad_out, rows_per_class, self._peer_ptrs["grad_inbox"], rank, world,
+                                            self._slices[p][0] - off, cnt, self._inbox_off[bi], self._inbox_stride, self.state_t[bi])
+            self._bucket_pushes[bi] += 1
+        elif self._announce_in_backward and bi not in self._packet_form:   # packets announce themselves
             out = ops.logic_backward_w_announce(x, a, b, grad_y, p, grad_out, rows_per_class, self._peer_ptrs["flags"], rank, world,
                                                 bi, self.state_t[bi], self._bw_tickets[self._param_index[p]:],
                                                 self._bucket_kernels[bi:], len(self._buckets[bi][2]))
@@ -253,8 +265,9 @@ class FlatAdam(torch.optim.Optimizer):
                 N.check(N.lib().dl_exchange_packets_f32(
                     self.flat_param.data_ptr(), self.flat_grad.data_ptr(), self._peer_ptrs["grad_inbox"], self._peer_ptrs["param_inbox"],
                     rank, world, self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(), off, cnt, self._inbox_off[bi], self._inbox_stride,
-                    float(g['lr']), float(beta1), float(beta2), float(g['eps']), self.state_t[bi].data_ptr(), self._wait_limit_us, how,
-                    stream.cuda_stream))
+                    float(g['lr']), float(beta1), float(beta2), float(g['eps']), self.state_t[bi].data_ptr(),
+                    int(self._bucket_pushes[bi] == len(self._buckets[bi][2])),   # every backward_w of the bucket has pushed
+                    self._wait_limit_us, how, stream.cuda_stream))
             else:
                 N.check(N.lib().dl_exchange_bucket_f32(
                     self._peer_ptrs["param"], self._peer_ptrs["grad"], self._peer_ptrs["flags"], rank, world, self.exp_avg.data_ptr(),

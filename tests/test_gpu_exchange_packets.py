@@ -87,7 +87,7 @@ def test_packet_exchange_equals_the_flag_exchange(world, rank):
         outside = param.clone()
         N.check(lib.dl_exchange_packets_f32(param.data_ptr(), grads[rank].data_ptr(), _ptrs(*[b.t for b in gin]),
                                             _ptrs(*[b.t for b in pin]), rank, world, m.data_ptr(), v.data_ptr(), off, n, inbox_off,
-                                            stride, lr, beta1, beta2, eps, state.data_ptr(), 0, N.LAUNCH_PLAIN, stream))
+                                            stride, lr, beta1, beta2, eps, state.data_ptr(), 0, 0, N.LAUNCH_PLAIN, stream))
         N.check(lib.dl_exchange_bucket_f32(_ptrs(*ref_params), _ptrs(*grads), _ptrs(*flags), rank, world, ref_m.data_ptr(),
                                            ref_v.data_ptr(), off, n, 0, lr, beta1, beta2, eps, ref_state.data_ptr(), 1, 0, 0,
                                            N.LAUNCH_PLAIN, stream))
@@ -122,7 +122,7 @@ def test_packet_exchange_gives_up_when_no_packet_arrives():
     before = param.clone()
     N.check(lib.dl_exchange_packets_f32(param.data_ptr(), grad.data_ptr(), _ptrs(*[b.t for b in gin]), _ptrs(*[b.t for b in pin]),
                                         rank, world, m.data_ptr(), v.data_ptr(), off, 4 * n4, 0, stride, 0.01, 0.9, 0.999, 1e-8,
-                                        state.data_ptr(), 2000, N.LAUNCH_PLAIN, torch.cuda.current_stream().cuda_stream))
+                                        state.data_ptr(), 0, 2000, N.LAUNCH_PLAIN, torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     s = state.tolist()
     assert s[2] == 1 and s[0] == 0 and s[3] == 0          # error word set, step count untouched, ticket re-armed
@@ -132,5 +132,69 @@ def test_packet_exchange_gives_up_when_no_packet_arrives():
     # arguments are checked before anything is launched
     bad = lib.dl_exchange_packets_f32(param.data_ptr(), grad.data_ptr(), _ptrs(*[b.t for b in gin]), _ptrs(*[b.t for b in pin]),
                                       rank, world, m.data_ptr(), v.data_ptr(), off, 4 * n4, 1, stride, 0.01, 0.9, 0.999, 1e-8,
-                                      state.data_ptr(), 2000, N.LAUNCH_PLAIN, None)
+                                      state.data_ptr(), 0, 2000, N.LAUNCH_PLAIN, None)
     assert bad == N.DL_ERR_INVALID_ARG                      # the bucket's slots do not fit the region
+
+
+@pytest.mark.parametrize("world,rank,n_out,bucket_offset", [(2, 1, 200, 0), (4, 0, 1000, 64), (3, 2, 77, 0), (8, 5, 512, 128)])
+def test_backward_w_pushes_the_other_ranks_slices_as_packets(world, rank, n_out, bucket_offset):
+    """dl_backward_w_push_f32: the same gradient as the plain kernel, and every element that belongs to another rank's
+    slice of the bucket sits in that rank's inbox (this rank's region) as a packet with the bucket's next epoch."""
+    from difflogic_b200 import ops
+    from tests.helpers import random_layer
+    n_in, batch = 96, 128
+    a, b, w = random_layer(n_in, n_out, seed=world * 10 + rank)
+    g = torch.Generator().manual_seed(5)
+    x, gy = torch.rand(n_in, batch, generator=g).cuda(), torch.randn(n_out, batch, generator=g).cuda()
+    a, b, w = a.cuda(), b.cuda(), w.cuda()
+    plain = ops.logic_backward_w(x, a, b, gy, w, ops.W_LOGITS)
+    bucket_count = bucket_offset + 16 * n_out + 32          # the layer is one of several parameters of the bucket
+    n4 = bucket_count // 4
+    per = -(-n4 // world)
+    inbox_off, stride = 3, per + 7
+    gin = [Inbox(world, stride) for _ in range(world)]
+    state = torch.zeros(16, dtype=torch.int32, device="cuda")
+    state[0] = 6                                            # six steps done: the packets carry 7
+    out = torch.empty_like(plain)
+    ops.logic_backward_w_push(x, a, b, gy, w, out, 1, _ptrs(*[bx.t for bx in gin]), rank, world, bucket_offset, bucket_count,
+                              inbox_off, stride, state)
+    torch.cuda.synchronize()
+    assert torch.equal(out, plain)
+    bucket = torch.zeros(bucket_count, device="cuda")
+    bucket[bucket_offset:bucket_offset + 16 * n_out] = plain.reshape(-1)
+    layer = torch.zeros(bucket_count, dtype=torch.bool, device="cuda")
+    layer[bucket_offset:bucket_offset + 16 * n_out] = True
+    for p in range(world):
+        lo, hi = min(p * per, n4), min(min(p * per, n4) + per, n4)
+        values, epochs = gin[p].get(rank, inbox_off, hi - lo)
+        mine = layer[4 * lo:4 * hi]
+        if p == rank:
+            assert not gin[p].t.any()                       # nothing is sent to oneself
+            continue
+        assert torch.equal(values[mine], bucket[4 * lo:4 * hi][mine]) and bool((epochs[mine] == 7).all())
+        assert bool((epochs[~mine] == 0).all())             # floats of the bucket outside this layer: not this kernel's
+        for q in range(world):
+            if q != rank:
+                assert not gin[p].get(q, 0, stride)[1].any()    # other senders' regions untouched
+
+
+def test_packet_exchange_after_a_push_does_not_push_again():
+    lib = N.lib()
+    world, rank, n4 = 2, 0, 512
+    per, stride = 256, 256
+    param, grad = torch.randn(4 * n4, device="cuda"), torch.randn(4 * n4, device="cuda")
+    m, v = torch.zeros(4 * n4, device="cuda"), torch.zeros(4 * n4, device="cuda")
+    state = torch.zeros(16, dtype=torch.int32, device="cuda")
+    gin = [Inbox(world, stride) for _ in range(world)]
+    pin = [Inbox(world, stride) for _ in range(world)]
+    peer_grad, peer_new = torch.randn(4 * per, device="cuda"), torch.randn(4 * per, device="cuda")
+    gin[0].put(1, 0, peer_grad, 1)
+    pin[0].put(1, 0, peer_new, 1)
+    N.check(lib.dl_exchange_packets_f32(param.data_ptr(), grad.data_ptr(), _ptrs(*[b.t for b in gin]), _ptrs(*[b.t for b in pin]),
+                                        rank, world, m.data_ptr(), v.data_ptr(), 0, 4 * n4, 0, stride, 0.01, 0.9, 0.999, 1e-8,
+                                        state.data_ptr(), 1, 2000, N.LAUNCH_PLAIN, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert state.tolist()[:4] == [1, 0, 0, 0]
+    assert not gin[1].t.any()                               # pushed = 1: the gradients were not sent (again)
+    assert torch.equal(param[4 * per:], peer_new)           # the peer's slice was collected
+    assert bool((pin[1].get(0, 0, per)[1] == 1).all())      # and this rank's new slice went out

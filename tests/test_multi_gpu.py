@@ -70,9 +70,10 @@ def _worker(rank, world, port, out_dir):
         ys = [torch.randint(0, 4, (64,), generator=g) for _ in range(3)]
         lo, hi = shard_range(64, rank, world)
         results = {}
-        # peer, peer_graph: the default forms (these buckets are small: packets); peer_flags: the flag exchange, in one pass
-        # where the byte limit allows; peer_two_pass_announce: the flag exchange in two passes, announced by backward_w
-        for mode in ("nccl", "peer", "peer_graph", "peer_flags", "peer_two_pass_announce"):
+        # peer, peer_graph: the default forms (these buckets are small: packets, pushed by the exchange kernel);
+        # peer_push: packets pushed by backward_w itself; peer_flags: the flag exchange, in one pass where the byte
+        # limit allows; peer_two_pass_announce: the flag exchange in two passes, announced by backward_w
+        for mode in ("nccl", "peer", "peer_graph", "peer_push", "peer_flags", "peer_two_pass_announce"):
             _, model = _make(dims, 4, 3.0, 11)
             model.train()
             opt = FlatAdam(model.parameters(), lr=0.01)
@@ -80,6 +81,8 @@ def _worker(rank, world, port, out_dir):
                 opt.enable_exchange(dist.group.WORLD, announce_in_backward=True, one_pass_bytes=0, packet_bytes=0)
             elif mode == "peer_flags":
                 opt.enable_exchange(dist.group.WORLD, packet_bytes=0)
+            elif mode == "peer_push":
+                opt.enable_exchange(dist.group.WORLD, push_in_backward=True)
             elif mode != "nccl":
                 opt.enable_exchange(dist.group.WORLD)
             step = TrainStep(model, opt, process_group=dist.group.WORLD, buckets=1)
@@ -125,7 +128,7 @@ def test_peer_memory_exchange_matches_nccl_all_reduce(tmp_path):
             pytest.fail("a rank did not finish in time")
         assert p.exitcode == 0
     res = [torch.load(os.path.join(tmp_path, "rank%d.pt" % r)) for r in range(world)]
-    for mode in ("peer", "peer_graph", "peer_flags", "peer_two_pass_announce"):
+    for mode in ("peer", "peer_graph", "peer_push", "peer_flags", "peer_two_pass_announce"):
         assert not res[0][mode]["err"] and not res[1][mode]["err"]
         for w0, w1 in zip(res[0][mode]["w"], res[1][mode]["w"]):
             assert torch.equal(w0, w1)                       # replicas stay identical
@@ -152,7 +155,7 @@ def test_peer_memory_exchange_matches_nccl_all_reduce(tmp_path):
             ref_first_grads = [w.grad.detach().clone() for w in net.weights]
         adam.step()
         ref_losses.append(float(loss))
-    for mode in ("peer", "peer_graph", "peer_flags", "peer_two_pass_announce"):
+    for mode in ("peer", "peer_graph", "peer_push", "peer_flags", "peer_two_pass_announce"):
         mean_losses = [0.5 * (a + b) for a, b in zip(res[0][mode]["loss"], res[1][mode]["loss"])]   # equal shards
         assert torch.allclose(torch.tensor(mean_losses), torch.tensor(ref_losses), rtol=1e-4), (mode, mean_losses, ref_losses)
         for got, ref in zip(res[0][mode]["first"]["grad"], ref_first_grads):
