@@ -291,6 +291,10 @@ def replica_checksum(opt, world):
 _PEER_EXCHANGE = {}
 
 
+class ExchangeFailed(RuntimeError):
+    """A wait of the peer-memory exchange ran out during the bench (raised on every rank alike)."""
+
+
 def peer_exchange_usable(args, world):
     """Whether this box lets every rank map every other rank's buffers and two trial steps of the headline network get
     through the peer-memory exchange with no wait running out (a short limit, so a box without working peer access
@@ -347,7 +351,7 @@ def bench_train(name, args, rank, world, headline):
     if peer:
         opt.enable_exchange(group, buckets=args.exchange_buckets, announce_in_backward=args.announce_in_backward,
                             one_pass_bytes=args.one_pass_bytes, packet_bytes=args.packet_bytes,
-                            push_in_backward=args.push_in_backward)
+                            push_in_backward=args.push_in_backward, wait_limit_us=5_000_000)
     loss_fn = torch.nn.CrossEntropyLoss() if args.loss == "torch" else CrossEntropyLoss()
     step = TrainStep(model, opt, loss_fn, process_group=group, world_size=world, buckets=args.buckets)
 
@@ -375,9 +379,20 @@ def bench_train(name, args, rank, world, headline):
     # ---- device-resident: the batches are already in HBM and every step reads its batch where it is (one captured
     # graph per batch of the pool), the step replayed K times, L2 flushed (untimed) between steps; `reps` repetitions of
     # that loop, each reduced to the max over the ranks, the median repetition is reported
+    def give_up_if_the_exchange_failed(where):
+        # a wait that ran out (5 s each here) would otherwise be paid for again in every step that follows
+        if peer and args.inject_exchange_error and rank == world - 1 and not _PEER_EXCHANGE.get("injected"):
+            opt.state_t[0, 2] = 1        # as if a wait of the first bucket had run out on this rank
+        _PEER_EXCHANGE["injected"] = True
+        if peer and all_max(1.0 if opt.exchange_error() else 0.0, world) > 0:
+            sampler.__exit__(None, None, None)
+            step.close()
+            raise ExchangeFailed("a wait for a peer ran out %s" % where)
+
     for i in range(W):
         step.replay_resident(i % pool)
     barrier(world)
+    give_up_if_the_exchange_failed("in the warm-up steps of %s" % name)
     sampler.__enter__()          # clocks are sampled over both timed loops (device-resident and end to end)
     rep_times = []
     for _ in range(reps):
@@ -396,6 +411,7 @@ def bench_train(name, args, rank, world, headline):
             pairs.append((s, e))
         barrier(world)
         rep_times.append(sum(s.elapsed_time(e) for s, e in pairs) * 1e-3)
+        give_up_if_the_exchange_failed("in a timed repetition of %s" % name)
     rep_times = all_reduce_list(rep_times, world, dist.ReduceOp.MAX)
     t_dev = median(rep_times)
     final_loss = float(loss.item())
@@ -431,6 +447,7 @@ def bench_train(name, args, rank, world, headline):
         for i in range(W):
             step(hx[i % pool], hy[i % pool]).item()
         barrier(world)
+        give_up_if_the_exchange_failed("in the warm-up steps of the end-to-end loop")
         e2e_times = []
         for _ in range(max(3, reps // 2)):
             t_rep = 0.0
@@ -459,8 +476,8 @@ def bench_train(name, args, rank, world, headline):
         out["exchange_error"] = err
         out["replicas_identical"] = replica_checksum(opt, world) if args.optimizer == "flat" else None
         if err or out["replicas_identical"] is False:
-            raise RuntimeError("bench: the gradient exchange failed (error %s, replicas identical %s)" % (
-                err, out["replicas_identical"]))
+            step.close()
+            raise ExchangeFailed("the gradient exchange failed (error %s, replicas identical %s)" % (err, out["replicas_identical"]))
 
     # ---- roofline of the three layer kernels at the hidden-layer shape (rank 0 only)
     if headline and rank == 0 and not args.skip_kernel_timing:
@@ -944,6 +961,8 @@ def main():
                     help="peer exchange: buckets up to this many bytes go as packets with the flags inside the data (0: none)")
     ap.add_argument("--push-in-backward", action="store_true",
                     help="peer exchange: backward_w's epilogue pushes the gradient packets (default: the exchange kernel does)")
+    ap.add_argument("--inject-exchange-error", action="store_true",
+                    help="N > 1, for testing the fallback: the last rank reports an expired wait after the warm-up steps")
     ap.add_argument("--skip-packed", action="store_true")
     ap.add_argument("--skip-large", action="store_true", help="leave out the wide and deep configurations (`configs`)")
     ap.add_argument("--optimizer", default="flat", choices=["flat", "torch"],
@@ -985,13 +1004,28 @@ def main():
         __graft_entry__.build()
     barrier(world)
 
-    train = bench_train("c2", args, rank, world, headline=True)
+    def train_bench(name, headline):
+        """bench_train; when the peer-memory exchange fails under it (every rank sees that alike), once more over NCCL's
+        all-reduce, and the JSON line says so."""
+        try:
+            return bench_train(name, args, rank, world, headline)
+        except ExchangeFailed as e:
+            if _PEER_EXCHANGE.get("usable") is False:
+                raise
+            _PEER_EXCHANGE["usable"], _PEER_EXCHANGE["why"] = False, str(e)
+            if rank == 0:
+                print("bench: %s; running %s again with NCCL" % (e, name), file=sys.stderr)
+            gc.collect()
+            torch.cuda.empty_cache()
+            return bench_train(name, args, rank, world, headline)
+
+    train = train_bench("c2", True)
     packed = None if args.skip_packed else bench_packed(args, rank, world)
     large = None
     if not args.skip_large:
         large = {}
         for name in ("c4", "c5"):
-            r = bench_train(name, args, rank, world, headline=False)
+            r = train_bench(name, False)
             cfg = CONFIGS[name]
             large[name] = {
                 "workload": "train step: %d -> %d x %d -> GroupSum(%d, tau=%g), batch %d per GPU, grad_factor %g, CrossEntropy, Adam" % (
