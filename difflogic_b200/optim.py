@@ -16,6 +16,17 @@ import torch
 from . import _native as N
 
 
+def plan_inboxes(bucket_counts, world):
+    """Where each exchange bucket lies inside a sender's region of a packet inbox (dl_exchange_packets_f32).
+    bucket_counts: floats per bucket (multiples of 4).  Returns (first float4 slot of every bucket, slots per region): a
+    bucket takes ceil(float4 of the bucket / world) slots, the slice one rank owns."""
+    offsets, slots = [], 0
+    for count in bucket_counts:
+        offsets.append(slots)
+        slots += -(-(int(count) // 4) // int(world))
+    return offsets, max(slots, 1)
+
+
 class ExchangeUnavailable(RuntimeError):
     """enable_exchange could not map a peer's buffers; raised on EVERY rank of the group, with the optimizer untouched."""
 
@@ -104,11 +115,7 @@ class FlatAdam(torch.optim.Optimizer):
         # the bucket plan first: the inboxes of the packet exchange have one region per sending rank with
         # ceil(bucket / ranks) float4 slots per bucket
         self._plan_exchange_buckets(buckets)
-        self._inbox_off, slots = [], 0
-        for _, cnt, _ in self._buckets:
-            self._inbox_off.append(slots)
-            slots += -(-(cnt // 4) // world)
-        self._inbox_stride = max(slots, 1)
+        self._inbox_off, self._inbox_stride = plan_inboxes([cnt for _, cnt, _ in self._buckets], world)
         self._packet_form = {bi for bi, (_, cnt, _) in enumerate(self._buckets) if world > 1 and 0 < cnt * 4 <= int(packet_bytes)}
         ptrs = {"param": alloc(n * 4), "grad": alloc(n * 4), "flags": alloc(int(lib.dl_exchange_flag_bytes()))}
         if self._packet_form:

@@ -139,3 +139,27 @@ def test_gates_match_reference(golden_dir):
     for i in range(16):
         assert torch.equal(D.functional.bin_op(a, b, i), torch.tensor(g["gates"][i]))
     assert torch.equal(D.functional.bin_op_s(a, b, w), torch.tensor(g["mix"]))
+
+
+def test_packet_inbox_plan_gives_every_bucket_its_own_slots():
+    """plan_inboxes: a bucket's slots hold the largest slice any rank owns, regions of different buckets do not overlap,
+    and every float4 of a bucket maps to exactly one (owner, slot) -- the addressing of exchange_packets_kernel."""
+    from difflogic_b200.optim import plan_inboxes
+    for world in (1, 2, 3, 4, 8):
+        counts = [16000 * 16, 4 * 1237, 4, 64, 4 * 999]
+        offsets, stride = plan_inboxes(counts, world)
+        assert offsets[0] == 0 and len(offsets) == len(counts)
+        end = 0
+        for count, off in zip(counts, offsets):
+            n4 = count // 4
+            per = -(-n4 // world)
+            assert off >= end                      # behind the bucket before it
+            end = off + per
+            seen = set()
+            for i in range(0, n4, max(1, n4 // 97)):           # a sample of the bucket's float4
+                owner, k = i // per, i % per
+                assert owner < world and off + k < end
+                seen.add((owner, k))
+            assert len(seen) == len(range(0, n4, max(1, n4 // 97)))
+        assert stride >= end
+    assert plan_inboxes([], 4) == ([], 1)
